@@ -1,0 +1,378 @@
+"""
+Benchmark of the SVDQuant W4A4 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass of the path over one batch of synthetic input: activation quantizer with fused
+LoRA-down, then the fused QKV projection (W4A4 GEMM + rank-32 branch + bias + per-head RMSNorm + RoPE) at
+M=4608 tokens, K=3072, N=9216 -- the FLUX.1 joint-attention QKV shape.  The metric is the GEMM's
+integer throughput, 2*M*N*K operations per step divided by the step time, summed over GPUs (each rank
+runs an independent replica on its own batch: weak scaling, no collective in the data path).
+
+Rank 0 prints ONE JSON line.  ``value`` is measured with inputs resident in HBM; ``e2e`` is the same
+metric through the public operator API starting from pinned host memory and ending with the result back
+on the host.  ``roofline`` describes the GEMM kernel alone (CUDA events around each launch inside the
+timed region); ``cpu_baseline`` is the CPU restatement of the reference's PyTorch path timed on the
+host cores on a bounded sample of the same workload.  ``--impl reference`` times only that CPU path.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M_TOK, K_IN, N_OUT, RANK = 4608, 3072, 9216, 32
+TXT, GRID = 512, 64
+N_SETS = 4  # rotating buffer sets: 4 x ~106 MB > 126 MB of L2
+
+
+def make_cfg_inputs(M: int, K: int, N: int, R: int, device, seed: int = 0) -> dict:
+    """
+    Seeded synthetic tensors with the shapes and value distributions of the benchmark configuration:
+    int4 weights uniform in [-8, 7] with per-64 bf16 scales U(0.005, 0.02); activations N(0, 1) with 8 outlier
+    channels x20; rank-R branch N(0, 0.02); bf16 bias; smooth U(0.5, 1.5); RMSNorm weights 1 + N(0, 0.05);
+    FLUX rotary table for 512 text rows + a 64 x 64 grid (when M matches).
+    """
+    from nunchaku_rocm_b200.models.embeddings import flux_image_ids, flux_pos_embed
+
+    g = torch.Generator(device=device).manual_seed(seed)
+    T = torch.bfloat16
+
+    def rnd(*s):
+        return torch.rand(*s, generator=g, device=device)
+
+    def nrm(*s):
+        return torch.randn(*s, generator=g, device=device)
+
+    x = nrm(M, K)
+    outliers = torch.randperm(K, generator=g, device=device)[:8]
+    x[:, outliers] *= 20
+    p = {
+        "x": x.to(T),
+        "qweight": torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g, device=device),
+        "wscales": (rnd(K // 64, N) * 0.015 + 0.005).to(T),
+        "bias": (nrm(N) * 0.1).to(T),
+        "proj_down": (nrm(K, R) * 0.02).to(T),
+        "proj_up": (nrm(N, R) * 0.02).to(T),
+        "smooth": (rnd(K) + 0.5).to(T),
+        "norm_q": (1 + nrm(128) * 0.05).to(T),
+        "norm_k": (1 + nrm(128) * 0.05).to(T),
+    }
+    if M == TXT + GRID * GRID:
+        p["rotary_emb"] = flux_pos_embed(flux_image_ids(TXT, GRID, GRID, device=device))
+    else:
+        th = rnd(M, 64) * 6.28
+        p["rotary_emb"] = torch.stack([torch.sin(th), torch.cos(th)], -1).reshape(M, 64, 1, 2).float().contiguous()
+    return p
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {
+                "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+                "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                "hw_power_brake": getattr(nv, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80),
+            }
+            while not self._stop_evt.is_set():
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+                time.sleep(0.002)
+        except Exception as e:  # NVML missing: report that instead of clocks
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def stop(self) -> dict:
+        self._stop_evt.set()
+        self.join(timeout=2)
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return json.load(open(path)), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU baseline: the oracle (a port of the reference's PyTorch path) on the host cores
+# --------------------------------------------------------------------------------------------------
+def cpu_step(p_cpu: dict, rows: int) -> None:
+    from oracle import w4a4
+
+    x = p_cpu["x"][:rows]
+    q, s, l, _ = w4a4.quantize_act(x, p_cpu["proj_down"], p_cpu["smooth"])
+    lin = w4a4.gemm_w4a4(q, p_cpu["qweight"], s, p_cpu["wscales"], p_cpu["bias"], l, p_cpu["proj_up"])
+    out = w4a4.qk_norm_rope(lin, p_cpu["norm_q"], p_cpu["norm_k"], p_cpu["rotary_emb"][:rows].reshape(rows, 128))
+    out.to(torch.bfloat16)
+
+
+def cpu_baseline(budget_s: float, steps: int, warmup: int) -> dict:
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    p = {k: v for k, v in make_cfg_inputs(M_TOK, K_IN, N_OUT, RANK, "cpu").items()}
+    # calibrate on 64 rows, then size the sample so that warmup + steps fit the budget
+    t0 = time.perf_counter()
+    cpu_step(p, 64)
+    t64 = time.perf_counter() - t0
+    rows = int(64 * budget_s / max(t64 * (steps + warmup), 1e-9))
+    rows = max(8, min(M_TOK, rows // 8 * 8))
+    for _ in range(warmup):
+        cpu_step(p, rows)
+    ts = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        cpu_step(p, rows)
+        ts.append(time.perf_counter() - t0)
+    t = statistics.median(ts)
+    return {
+        "value": 2.0 * rows * N_OUT * K_IN / t / 1e12,
+        "unit": "TOPS",
+        "cores": cores,
+        "kind": "port",
+        "sample": f"first {rows} of {M_TOK} rows of the same workload, {steps} steps, median",
+        "ms_per_step": t * 1e3,
+        "rows": rows,
+    }
+
+
+def config_dict(n_gpus: int) -> dict:
+    return {
+        "workload": "fused_qkv_w4a4: quantize(4608x3072, rank-32 LoRA-down) + W4A4 GEMM 4608x9216x3072 "
+        "(group 64, rank 32, bias) + per-head RMSNorm + RoPE (24 heads x 128, 512 text + 64x64 image tokens)",
+        "M": M_TOK,
+        "K": K_IN,
+        "N": N_OUT,
+        "rank": RANK,
+        "parallelism": f"dp{n_gpus} (independent replica per GPU, no collective)",
+        "l2": f"{N_SETS} rotating buffer sets (~{N_SETS * 106} MB > 126 MB L2)",
+    }
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cb = cpu_baseline(budget_s=90.0, steps=args.steps, warmup=args.warmup)
+    line = {
+        "impl": "reference",
+        "metric": "w4a4_gemm_tops",
+        "value": cb["value"],
+        "unit": "TOPS",
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": cb["ms_per_step"],
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "int4xint4->int32, fp32 scaling",
+        "data": "synthetic",
+        "config": config_dict(args.gpus),
+        "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": cb["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args) -> None:
+    import torch.distributed as dist
+
+    from nunchaku_rocm_b200.ops.quantize import svdq_quantize_w4a4_act_fuse_lora_cuda as quantize
+    from nunchaku_rocm_b200.ops.triton.gemm_w4a4 import gemm_w4a4
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path for the product kernels)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    sets = []
+    for i in range(N_SETS):
+        p = make_cfg_inputs(M_TOK, K_IN, N_OUT, RANK, dev, seed=rank * 100 + i)
+        p["out"] = torch.empty(M_TOK, N_OUT, dtype=torch.bfloat16, device=dev)
+        m_pad = (M_TOK + 255) // 256 * 256
+        p["q"] = torch.empty(m_pad, K_IN // 2, dtype=torch.uint8, device=dev)
+        p["s"] = torch.empty(K_IN // 64, m_pad, dtype=torch.bfloat16, device=dev)
+        p["l"] = torch.zeros(m_pad, RANK, dtype=torch.float32, device=dev)
+        sets.append(p)
+
+    def step(p, ev=None):
+        quantize(p["x"], p["q"], p["s"], p["proj_down"], p["l"], p["smooth"])
+        if ev is not None:
+            ev[0].record()
+        gemm_w4a4(p["q"], p["qweight"], p["out"], p["s"], p["wscales"], p["bias"], p["l"], p["proj_up"],
+                  norm_q=p["norm_q"], norm_k=p["norm_k"], rotary_emb=p["rotary_emb"])
+        if ev is not None:
+            ev[1].record()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(sets[i % N_SETS])
+    barrier()
+
+    # ---- device-resident throughput ------------------------------------------------------------------
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    sampler.start()
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(sets[i % N_SETS], evs[i])
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms_total = e0.elapsed_time(e1)
+    gemm_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+    t = torch.tensor([ms_total], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    ops = 2.0 * M_TOK * N_OUT * K_IN
+
+    # ---- end to end through the operator API, host buffers in and out --------------------------------
+    hx = [s["x"].cpu().pin_memory() for s in sets[:2]]
+    hout = [torch.empty(M_TOK, N_OUT, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    dx = torch.empty_like(sets[0]["x"])
+
+    def e2e_step(i):
+        p = sets[i % N_SETS]
+        dx.copy_(hx[i % 2], non_blocking=True)
+        quantize(dx, p["q"], p["s"], p["proj_down"], p["l"], p["smooth"])
+        gemm_w4a4(p["q"], p["qweight"], p["out"], p["s"], p["wscales"], p["bias"], p["l"], p["proj_up"],
+                  norm_q=p["norm_q"], norm_k=p["norm_k"], rotary_emb=p["rotary_emb"])
+        hout[i % 2].copy_(p["out"], non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 50))
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    e0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / e2e_steps
+
+    from nunchaku_rocm_b200 import _lib
+
+    status = _lib.device_status(dev)
+    if status:
+        raise SystemExit(f"a kernel gave up on a bounded wait (status {status:#x}); numbers are void")
+
+    if rank == 0:
+        peaks, src = measured_peaks()
+        # the int8 tensor pipe runs at twice the bf16 rate; the measured bf16 burst figure x 2 is the denominator
+        peak = 2.0 * float(peaks["bf16_tflops"])
+        achieved = ops / (gemm_ms * 1e-3) / 1e12
+        line = {
+            "metric": "w4a4_gemm_tops",
+            "value": world * ops / (ms_step * 1e-3) / 1e12,
+            "unit": "TOPS",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "int4xint4->int32 (tcgen05 kind::i8), fp32 scaling, bf16 out",
+            "data": "synthetic",
+            "config": config_dict(world),
+            "clocks": clocks,
+            "e2e": {
+                "value": world * ops / (e2e_ms * 1e-3) / 1e12,
+                "unit": "TOPS",
+                "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": hx[0].numel() * hx[0].element_size(),
+                "d2h_bytes_per_step": hout[0].numel() * hout[0].element_size(),
+            },
+            "gpu_launches": 2 * args.steps,
+            "roofline": {
+                "kernel": "gemm_tc_kernel<256, QK_NORM_ROPE, bf16>",
+                "bound": "tensor",
+                "achieved": achieved,
+                "peak": peak,
+                "unit": "TFLOP/s",
+                "frac": achieved / peak,
+                "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+                "peak_source": f"2 x bf16_tflops of MEASURED_PEAKS.json ({src}); int8 pipe = 2 x bf16 rate",
+                "gemm_ms": gemm_ms,
+                "algorithmic_ops_per_launch": ops,
+            },
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cb = cpu_baseline(budget_s=20.0, steps=3, warmup=1)
+            line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch from the ncu capture summarised under
+# profiles/ (None until a capture exists)
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

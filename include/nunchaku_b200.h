@@ -1,0 +1,186 @@
+/*
+ * C ABI of libnunchaku_b200.so: hand-written sm_100a kernels for the SVDQuant hot path
+ * (W4A4 GEMM + low-rank branch + fused epilogues, activation quantizer, AWQ W4A16, attention).
+ *
+ * Every entry point takes plain device pointers, sizes and strides (strides in ELEMENTS of the
+ * tensor they index unless a field says bytes), launches on the given CUDA stream of the
+ * CURRENT device and returns an nb_status.  Nothing here synchronises the device or throws.
+ * All tensors use the reference's natural layouts (nunchaku/ops/triton/gemm_w4a4.py:4-19):
+ * packed 4-bit rows are (rows, K/2) bytes with element k in the low nibble of byte k/2 when k is
+ * even; scales are group-major (K/G, rows).
+ *
+ * Each declaration names the reference interface it replaces (paths inside the nunchaku-rocm
+ * project).
+ */
+#ifndef NUNCHAKU_B200_H
+#define NUNCHAKU_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum nb_status {
+    NB_OK = 0,
+    NB_ERR_INVALID = 1,     /* argument contract violated (shape, alignment, null pointer) */
+    NB_ERR_UNSUPPORTED = 2, /* valid call that no kernel here implements */
+    NB_ERR_LAUNCH = 3,      /* CUDA reported an error at launch; nb_last_cuda_error() has the code */
+    NB_ERR_DEVICE = 4,      /* a kernel gave up on a bounded wait and set its status word */
+    NB_ERR_TOO_LARGE = 5    /* size beyond the limit of a fixed-capacity entry point */
+} nb_status;
+
+enum { NB_DTYPE_BF16 = 0, NB_DTYPE_FP16 = 1 };
+
+/* epilogue selector of nb_gemm_w4a4 */
+enum {
+    NB_EPI_STORE = 0,       /* 16-bit store of the fp32 tile                                  */
+    NB_EPI_QK_NORM_ROPE = 1,/* + per-head RMSNorm and RoPE on the Q and K thirds              */
+    NB_EPI_GELU_QUANT = 2,  /* + GELU, next-layer LoRA-down, unsigned int4 re-quantisation    */
+    NB_EPI_SWIGLU_QUANT = 3 /* + silu(gate)*up on interleaved rows, signed int4 re-quantisation */
+};
+
+/* kernel selector (nb_gemm_args.impl) */
+enum {
+    NB_IMPL_AUTO = 0,    /* tcgen05 kernel when the call meets its alignment rules, else the generic kernel */
+    NB_IMPL_TCGEN05 = 1, /* tcgen05 kernel or NB_ERR_UNSUPPORTED */
+    NB_IMPL_GENERIC = 2  /* CUDA-core kernel that takes every shape the op accepts */
+};
+
+/*
+ * Mirrors `struct GemmArgs` of nunchaku/ops/triton/native/w4a4_gfx11.hip:69-82 (ctypes twin
+ * `_GemmArgs`, nunchaku/ops/triton/native/w4a4.py:80-103) and adds what the Triton entry
+ * `gemm_w4a4` takes beyond it (nunchaku/ops/triton/gemm_w4a4.py:1003-1027): wcscales, alpha,
+ * fp4, fuse_silu.
+ */
+typedef struct nb_gemm_args {
+    const void* act;      /* (M, K/2) u8                                                     */
+    const void* wgt;      /* (N, K/2) u8                                                     */
+    void* out;            /* (actual_m, N) T, may be null when the epilogue writes no 16-bit tile */
+    const void* ascales;  /* (K/G, >=M) T, or e4m3 when fp4                                   */
+    const void* wscales;  /* (K/G, >=N) T, or e4m3 when fp4                                   */
+    const void* bias;     /* (N) T or null                                                   */
+    const void* lora_act; /* (>=M, R) f32 or null                                            */
+    const void* lora_up;  /* (>=N, R) T or null                                              */
+    const void* wcscales; /* (N) T or null (NVFP4 per-channel scale)                         */
+    int32_t M, N, K;      /* rows of act, rows of wgt, logical K                             */
+    int32_t actual_m;     /* rows of out (<= M); rows >= actual_m are computed but not stored */
+    int32_t R;            /* LoRA-up rank, multiple of 16, 0 = none                          */
+    int32_t dtype;        /* NB_DTYPE_*: T                                                   */
+    int32_t act_unsigned; /* activations are 0..15 instead of -8..7 (int4 only)              */
+    int32_t fp4;          /* nibbles are e2m1, G = 16, scales e4m3                            */
+    int32_t fuse_silu;
+    int32_t impl;         /* NB_IMPL_*                                                       */
+    float alpha;          /* NVFP4 per-tensor scale                                          */
+    int64_t stride_am, stride_wn;   /* row strides of act / wgt in BYTES                      */
+    int64_t stride_asg, stride_wsg; /* group strides of ascales / wscales                     */
+    int64_t stride_om, stride_lam, stride_lun;
+    void* status;         /* device int32 the kernel sets non-zero if a bounded wait expires; may be null */
+    void* scratch;        /* device scratch, see nb_gemm_w4a4_scratch_bytes(); may be null when that is 0 */
+    int64_t scratch_bytes;
+} nb_gemm_args;
+
+/* Mirrors `QKNormRopeEpilogue::Args` (w4a4_gfx11.hip:440-446; ctypes `_QKArgs`, w4a4.py:106-115). */
+typedef struct nb_qk_args {
+    const void* norm_q;   /* (128) T */
+    const void* norm_k;   /* (128) T */
+    const float* rot;     /* (rot_rows, 128) f32: (sin, cos) per channel pair */
+    int64_t stride_rm;
+    int32_t rot_rows;     /* actual_m, or a divisor S of it: row m then reads rot[m % S] (one table for a batch) */
+    float eps;
+} nb_qk_args;
+
+/* Mirrors `QuantArgs` (w4a4_gfx11.hip:585-594; ctypes `_GQArgs`, w4a4.py:118-124). */
+typedef struct nb_requant_args {
+    void* qout;            /* (>=M, Nq/2) u8, Nq = N (GELU) or N/2 (SwiGLU)                  */
+    void* oscales;         /* (Nq/64, >=M) T                                                 */
+    const void* smooth;    /* (Nq) T or null                                                 */
+    const void* lora_down; /* (Nq, R2) T or null                                             */
+    float* lora_act_out;   /* (>=M, R2) f32 or null                                          */
+    int32_t R2;
+    float shift;           /* 0.171875 for the GELU path                                     */
+    int64_t stride_qm, stride_osg, stride_ld, stride_lom;
+} nb_requant_args;
+
+/*
+ * W4A4 GEMM.  Replaces `gemm_w4a4` (nunchaku/ops/triton/gemm_w4a4.py:1003-1314) and the native
+ * launchers `try_gemm` / `try_gemm_qk` / `try_gemm_gelu_quant` / `try_gemm_swiglu_quant`
+ * (nunchaku/ops/triton/native/w4a4.py:969-1060).  `epi` points at nb_qk_args (NB_EPI_QK_NORM_ROPE),
+ * nb_requant_args (NB_EPI_GELU_QUANT, NB_EPI_SWIGLU_QUANT) or is null.
+ */
+int nb_gemm_w4a4(const nb_gemm_args* args, const void* epi, int epi_kind, void* stream);
+
+/* Bytes of device scratch nb_gemm_w4a4 needs for this call (0 for most). */
+int64_t nb_gemm_w4a4_scratch_bytes(const nb_gemm_args* args, const void* epi, int epi_kind);
+
+/*
+ * Debug: the exact int32 group sums p_g[m, n] = sum_{k in g} a[m,k] * w[n,k] as the tensor-core
+ * kernel accumulates them, (K/64, M, N) int32.  The reference's integer contract
+ * (nunchaku/ops/triton/gemm_w4a4.py:477-483) is checked against this.
+ */
+int nb_gemm_w4a4_group_sums(const nb_gemm_args* args, int32_t* p_out, void* stream);
+
+/*
+ * Activation quantizer with fused LoRA-down.  Replaces `quantize_w4a4_act_fuse_lora` /
+ * `_launch_quantize` (nunchaku/ops/triton/gemm_w4a4.py:1465-1565).
+ */
+typedef struct nb_quant_args {
+    const void* input;     /* (M, K) T, or (M, 2K) when fuse_glu                            */
+    void* output;          /* (>=M, K/2) u8                                                 */
+    void* oscales;         /* (K/G, >=M) T, e4m3 when fp4                                   */
+    const void* lora_down; /* (K, R) T or null                                              */
+    float* lora_act_out;   /* (>=M, R) f32 or null                                          */
+    const void* smooth;    /* (K) T or null                                                 */
+    int32_t M, K, R;
+    int32_t dtype;
+    int32_t fuse_glu, fuse_gelu, fp4, is_unsigned;
+    float shift;
+    int64_t stride_im, stride_om, stride_sg, stride_ld, stride_lam;
+} nb_quant_args;
+int nb_quantize_w4a4(const nb_quant_args* args, void* stream);
+
+/*
+ * Unfused per-head RMSNorm + RoPE on the Q/K thirds of a stored (M, N) tile, in place.
+ * Replaces `_apply_rmsnorm_rope_qk` (nunchaku/ops/triton/gemm_w4a4.py:834-866).
+ */
+int nb_qk_norm_rope(void* out, int32_t M, int32_t N, int64_t stride_om, int32_t dtype, const nb_qk_args* qk,
+                    void* stream);
+
+/*
+ * AWQ W4A16.  `nb_awq_gemv` replaces `awq_gemv_w4a16` (nunchaku/ops/triton/awq.py:186-229) for
+ * group 64; `nb_awq_dequant` replaces `awq_dequantize` (awq.py:83-118).  `kernel` is the TinyChat
+ * int16 (n/4, k) packing (awq.py:8-18).
+ */
+int nb_awq_gemv(const void* x, const void* kernel, const void* scales, const void* zeros, void* out, int32_t m,
+                int32_t n, int32_t k, int64_t stride_xm, int64_t stride_kn, int64_t stride_sg, int64_t stride_om,
+                int32_t dtype, void* stream);
+int nb_awq_dequant(const void* kernel, const void* scales, const void* zeros, void* out, int32_t n, int32_t k,
+                   int32_t group, int64_t stride_kn, int64_t stride_sg, int64_t stride_on, int32_t dtype,
+                   void* stream);
+
+/*
+ * Unmasked flash attention, (B,H,T,D) strided inputs with unit last stride -> (B,Tq,H*D).
+ * Replaces `attention_fp16` (nunchaku/ops/triton/attention.py:120-169).  D in {64, 128}.
+ */
+typedef struct nb_attn_args {
+    const void* q; const void* k; const void* v; void* o;
+    int32_t B, H, Tq, Tkv, D, dtype;
+    float scale;  /* softmax scale before the log2(e) fold */
+    int64_t stride_qb, stride_qh, stride_qm;
+    int64_t stride_kb, stride_kh, stride_kn;
+    int64_t stride_vb, stride_vh, stride_vn;
+    int64_t stride_ob, stride_om;
+} nb_attn_args;
+int nb_attention(const nb_attn_args* args, void* stream);
+
+/* Diagnostics (the reference's `status()` / error plumbing, nunchaku/ops/triton/native/hip.py:110-116). */
+const char* nb_strerror(int status);
+int nb_last_cuda_error(void);          /* cudaError_t of the last NB_ERR_LAUNCH, cleared by reading */
+const char* nb_last_cuda_error_string(void);
+int nb_version(void);
+int nb_num_sms(void);                  /* SM count of the current device, <= 0 on error */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NUNCHAKU_B200_H */

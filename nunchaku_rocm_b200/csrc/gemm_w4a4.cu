@@ -1,0 +1,121 @@
+// Entry point of the W4A4 GEMM: argument contract, kernel choice, and the generic path's scratch.
+#include "nb_common.cuh"
+
+namespace nb {
+
+struct GenericParams {
+    const uint8_t* act;
+    const uint8_t* wgt;
+    void* out;
+    float* acc_out;
+    int32_t* p_out;
+    const void* ascales;
+    const void* wscales;
+    const void* bias;
+    const float* lora_act;
+    const void* lora_up;
+    const void* wcscales;
+    int M, N, K, actual_m, R;
+    int act_unsigned, fp4, fuse_silu;
+    float alpha;
+    long long stride_am, stride_wn, stride_asg, stride_wsg, stride_om, stride_lam, stride_lun;
+};
+
+int launch_generic(const GenericParams& p, int dtype, cudaStream_t s);
+int launch_qk_rows(const float* src_f, void* out, long long stride_om, int M, int N, int dtype, const nb_qk_args* qk,
+                   cudaStream_t s);
+int launch_requant_rows(const float* lin, int M, int N, int mode, int dtype, const nb_requant_args* q, cudaStream_t s);
+const char* tc_unsupported_reason(const nb_gemm_args* a, const void* epi, int epi_kind);
+int launch_tc(const nb_gemm_args* a, const void* epi, int epi_kind, int32_t* p_out, cudaStream_t s);
+
+static int validate(const nb_gemm_args* a, const void* epi, int epi_kind) {
+    NB_REQUIRE(a && a->act && a->wgt && a->ascales && a->wscales);
+    NB_REQUIRE(a->dtype == NB_DTYPE_BF16 || a->dtype == NB_DTYPE_FP16);
+    NB_REQUIRE(a->M >= 0 && a->N > 0 && a->K > 0 && a->actual_m >= 0 && a->actual_m <= a->M);
+    NB_REQUIRE(a->K % (a->fp4 ? 16 : 64) == 0);
+    NB_REQUIRE(a->R >= 0 && (a->R == 0 || (a->lora_act && a->lora_up)));
+    NB_REQUIRE(epi_kind >= NB_EPI_STORE && epi_kind <= NB_EPI_SWIGLU_QUANT);
+    NB_REQUIRE(epi_kind == NB_EPI_STORE || epi != nullptr);
+    if (epi_kind == NB_EPI_STORE || epi_kind == NB_EPI_QK_NORM_ROPE) NB_REQUIRE(a->out != nullptr);
+    if (epi_kind == NB_EPI_QK_NORM_ROPE) {
+        const nb_qk_args* q = static_cast<const nb_qk_args*>(epi);
+        NB_REQUIRE(q->norm_q && q->norm_k && q->rot && q->rot_rows > 0);
+        NB_REQUIRE(a->N % 3 == 0 && (a->N / 3) % 128 == 0);
+        NB_REQUIRE(a->actual_m % q->rot_rows == 0 || q->rot_rows >= a->actual_m);
+    }
+    if (epi_kind == NB_EPI_GELU_QUANT || epi_kind == NB_EPI_SWIGLU_QUANT) {
+        const nb_requant_args* q = static_cast<const nb_requant_args*>(epi);
+        NB_REQUIRE(q->qout && q->oscales && !a->fp4);
+        NB_REQUIRE(a->N % (epi_kind == NB_EPI_GELU_QUANT ? 64 : 128) == 0);
+        NB_REQUIRE((q->lora_down == nullptr) == (q->lora_act_out == nullptr));
+    }
+    return NB_OK;
+}
+
+static bool needs_scratch(const nb_gemm_args* a, const void* epi, int epi_kind) {
+    if (epi_kind == NB_EPI_STORE) return false;
+    if (a->impl == NB_IMPL_GENERIC) return true;
+    return tc_unsupported_reason(a, epi, epi_kind) != nullptr;
+}
+
+static GenericParams to_generic(const nb_gemm_args* a) {
+    GenericParams p = {};
+    p.act = static_cast<const uint8_t*>(a->act); p.wgt = static_cast<const uint8_t*>(a->wgt);
+    p.ascales = a->ascales; p.wscales = a->wscales; p.bias = a->bias;
+    p.lora_act = static_cast<const float*>(a->lora_act); p.lora_up = a->lora_up; p.wcscales = a->wcscales;
+    p.M = a->M; p.N = a->N; p.K = a->K; p.actual_m = a->actual_m; p.R = a->R;
+    p.act_unsigned = a->act_unsigned; p.fp4 = a->fp4; p.fuse_silu = a->fuse_silu; p.alpha = a->alpha;
+    p.stride_am = a->stride_am; p.stride_wn = a->stride_wn; p.stride_asg = a->stride_asg; p.stride_wsg = a->stride_wsg;
+    p.stride_om = a->stride_om; p.stride_lam = a->stride_lam; p.stride_lun = a->stride_lun;
+    return p;
+}
+
+}  // namespace nb
+
+extern "C" int64_t nb_gemm_w4a4_scratch_bytes(const nb_gemm_args* a, const void* epi, int epi_kind) {
+    if (!a || nb::validate(a, epi, epi_kind) != NB_OK) return 0;
+    return nb::needs_scratch(a, epi, epi_kind) ? (int64_t)a->M * a->N * 4 : 0;
+}
+
+extern "C" int nb_gemm_w4a4(const nb_gemm_args* a, const void* epi, int epi_kind, void* stream) {
+    using namespace nb;
+    int st = validate(a, epi, epi_kind);
+    if (st != NB_OK) return st;
+    if (a->M == 0) return NB_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const char* reason = tc_unsupported_reason(a, epi, epi_kind);
+    if (a->impl == NB_IMPL_TCGEN05 && reason) return NB_ERR_UNSUPPORTED;
+    if (a->impl != NB_IMPL_GENERIC && !reason) return launch_tc(a, epi, epi_kind, nullptr, s);
+
+    GenericParams p = to_generic(a);
+    if (epi_kind == NB_EPI_STORE) {
+        p.out = a->out;
+        return launch_generic(p, a->dtype, s);
+    }
+    NB_REQUIRE(a->scratch && a->scratch_bytes >= (int64_t)a->M * a->N * 4);
+    p.acc_out = static_cast<float*>(a->scratch);
+    p.out = epi_kind == NB_EPI_GELU_QUANT ? a->out : nullptr;  // optional pre-GELU 16-bit tile
+    st = launch_generic(p, a->dtype, s);
+    if (st != NB_OK) return st;
+    if (epi_kind == NB_EPI_QK_NORM_ROPE)
+        return launch_qk_rows(p.acc_out, a->out, a->stride_om, a->actual_m, a->N, a->dtype,
+                              static_cast<const nb_qk_args*>(epi), s);
+    return launch_requant_rows(p.acc_out, a->M, a->N, epi_kind == NB_EPI_GELU_QUANT ? 0 : 1, a->dtype,
+                               static_cast<const nb_requant_args*>(epi), s);
+}
+
+extern "C" int nb_gemm_w4a4_group_sums(const nb_gemm_args* a, int32_t* p_out, void* stream) {
+    using namespace nb;
+    int st = validate(a, nullptr, NB_EPI_STORE);
+    if (st != NB_OK) return st;
+    NB_REQUIRE(p_out && !a->fp4);
+    if (a->M == 0) return NB_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const char* reason = tc_unsupported_reason(a, nullptr, NB_EPI_STORE);
+    if (a->impl == NB_IMPL_TCGEN05 && reason) return NB_ERR_UNSUPPORTED;
+    if (a->impl != NB_IMPL_GENERIC && !reason) return launch_tc(a, nullptr, NB_EPI_STORE, p_out, s);
+    GenericParams p = to_generic(a);
+    p.out = a->out;
+    p.p_out = p_out;
+    return launch_generic(p, a->dtype, s);
+}

@@ -1,0 +1,335 @@
+// Activation quantizer with fused LoRA-down (HBM-bound).
+//
+// Semantics follow `_quantize_tile_kernel` of the reference (nunchaku/ops/triton/gemm_w4a4.py:1338-1462):
+// optional GLU / GELU, LoRA-down from the un-shifted, un-smoothed row rounded to the 16-bit dtype,
+// then shift, reciprocal-multiply by smooth, per-group max, scale = max / qmax (stored rounded,
+// transposed (K/G, M)), codes from the unrounded scale with round-half-even, low nibble first.
+//
+// Work split: a CTA of 8 warps owns 32 rows.  Warp w owns the 16-row block (w & 1) and the 64-wide
+// K groups g = (w >> 1) mod 4.  A lane holds rows {gid, gid + 8} x columns {8 tig .. 8 tig + 7} and
+// {32 + 8 tig ..}, read with 128-bit loads; the per-group maximum is a 2-step warp shuffle over
+// the 4 lanes that share a row.  The same registers are the A fragments of the LoRA-down
+// mma.sync.m16n8k16 (a dot product does not care about a permutation of k applied to both
+// operands, so the B fragments are fetched with ldmatrix.trans from the matching rows of the
+// lora_down chunk, staged in shared memory by cp.async).  The four K-quarter partial sums are added
+// in a fixed order through shared memory, so the result is run-to-run identical.
+#include <cuda_fp8.h>
+
+#include "nb_common.cuh"
+
+namespace nb {
+namespace {
+
+constexpr int QT_WARPS = 8;
+constexpr int QT_ROWS = 32;
+constexpr int QT_RCHUNK = 64;  // LoRA ranks per grid.y slice
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                                        uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+struct QParams {
+    const void* input;
+    uint8_t* output;
+    void* oscales;
+    const void* lora_down;
+    float* lora_act_out;
+    const void* smooth;
+    int M, K, R;
+    int fuse_glu, fuse_gelu, fp4, is_unsigned, do_lora;
+    float shift;
+    long long stride_im, stride_om, stride_sg, stride_ld, stride_lam;
+};
+
+// One 16-byte load of 8 T values -> fp32, zero when the row is out of range.
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, bool ok, float (&v)[8]) {
+    uint4 raw = ok ? __ldg(reinterpret_cast<const uint4*>(p)) : make_uint4(0, 0, 0, 0);
+    float2 f;
+    f = unpack2<T>(raw.x); v[0] = f.x; v[1] = f.y;
+    f = unpack2<T>(raw.y); v[2] = f.x; v[3] = f.y;
+    f = unpack2<T>(raw.z); v[4] = f.x; v[5] = f.y;
+    f = unpack2<T>(raw.w); v[6] = f.x; v[7] = f.y;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(QT_WARPS * 32) quantize_kernel(const QParams p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int rb = warp & 1, kq = warp >> 1;
+    const int m0 = blockIdx.x * QT_ROWS + rb * 16;
+    const int r0 = blockIdx.y * QT_RCHUNK;                  // first LoRA rank of this slice
+    const int rn = p.do_lora ? min(QT_RCHUNK, p.R - r0) : 0;  // ranks in this slice (multiple of 16)
+    const bool quantize = blockIdx.y == 0;
+    const int G = p.K / 64;  // 64-wide column blocks; an NVFP4 block holds four 16-groups
+
+    // per-warp double buffer for the lora_down chunk: 64 k-rows x 128 bytes; the 16-byte unit u of row k
+    // lives at unit u ^ f(k), f(k) = (k & 1) | ((k >> 3) & 3) << 1, which spreads the eight rows one
+    // ldmatrix 8x8 tile reads (k = 8 t + e + const, t < 4, e < 2) over all eight bank groups
+    constexpr int ld_pitch = QT_RCHUNK * 2;
+    uint8_t* ld_buf = smem + warp * (2 * 64 * ld_pitch);
+    const T* x = static_cast<const T*>(p.input);
+    const T* ldw = static_cast<const T*>(p.lora_down);
+    const T* smooth = static_cast<const T*>(p.smooth);
+
+    const int row_a = m0 + gid, row_b = m0 + gid + 8;
+    const bool ok_a = row_a < p.M, ok_b = row_b < p.M;
+
+    float acc[QT_RCHUNK / 8][4];
+#pragma unroll
+    for (int i = 0; i < QT_RCHUNK / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+    auto stage_ld = [&](int g, int buf) {
+        // 64 rows x rn*2 bytes, 16-byte units
+        const int units_per_row = rn / 8;
+        uint32_t dst0 = smem_u32(ld_buf + buf * 64 * ld_pitch);
+        for (int u = lane; u < 64 * units_per_row; u += 32) {
+            int kr = u / units_per_row, c = u % units_per_row;
+            const int f = (kr & 1) | (((kr >> 3) & 3) << 1);
+            cp_async16(dst0 + kr * ld_pitch + ((c ^ f) << 4), ldw + (long long)(g * 64 + kr) * p.stride_ld + r0 + c * 8);
+        }
+    };
+
+    int it = 0;
+    if (rn > 0 && kq < G) stage_ld(kq, 0);
+    cp_async_commit();
+
+    for (int g = kq; g < G; g += 4, ++it) {
+        if (rn > 0 && g + 4 < G) stage_ld(g + 4, (it + 1) & 1);
+        cp_async_commit();
+
+        // ---- load the 16 x 64 block: rows {gid, gid+8}, columns {8 tig.., 32 + 8 tig..}
+        float v[2][16];
+        const int c0 = g * 64 + 8 * tig;
+        load8<T>(x + (long long)row_a * p.stride_im + c0, ok_a, *reinterpret_cast<float(*)[8]>(&v[0][0]));
+        load8<T>(x + (long long)row_a * p.stride_im + c0 + 32, ok_a, *reinterpret_cast<float(*)[8]>(&v[0][8]));
+        load8<T>(x + (long long)row_b * p.stride_im + c0, ok_b, *reinterpret_cast<float(*)[8]>(&v[1][0]));
+        load8<T>(x + (long long)row_b * p.stride_im + c0 + 32, ok_b, *reinterpret_cast<float(*)[8]>(&v[1][8]));
+        if (p.fuse_glu) {
+            float gate[2][16];
+            load8<T>(x + (long long)row_a * p.stride_im + p.K + c0, ok_a, *reinterpret_cast<float(*)[8]>(&gate[0][0]));
+            load8<T>(x + (long long)row_a * p.stride_im + p.K + c0 + 32, ok_a,
+                     *reinterpret_cast<float(*)[8]>(&gate[0][8]));
+            load8<T>(x + (long long)row_b * p.stride_im + p.K + c0, ok_b, *reinterpret_cast<float(*)[8]>(&gate[1][0]));
+            load8<T>(x + (long long)row_b * p.stride_im + p.K + c0 + 32, ok_b,
+                     *reinterpret_cast<float(*)[8]>(&gate[1][8]));
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[r][i] = v[r][i] * silu(gate[r][i]);
+        }
+        if (p.fuse_gelu) {
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[r][i] = gelu_tanh(v[r][i]);
+        }
+
+        // ---- LoRA-down on the un-shifted, un-smoothed values rounded to T
+        if (rn > 0) {
+            cp_async_wait<1>();
+            __syncwarp();
+            const uint32_t base = smem_u32(ld_buf + (it & 1) * 64 * ld_pitch);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                // A fragment i: k-slots (2 tig, 2 tig + 1) = elements 4i, 4i+1; slots (2 tig + 8, +9) = 4i+2, 4i+3
+                uint32_t a[4];
+                a[0] = pack2<T>(v[0][4 * i], v[0][4 * i + 1]);
+                a[1] = pack2<T>(v[1][4 * i], v[1][4 * i + 1]);
+                a[2] = pack2<T>(v[0][4 * i + 2], v[0][4 * i + 3]);
+                a[3] = pack2<T>(v[1][4 * i + 2], v[1][4 * i + 3]);
+                // k-slot s of fragment i is column (i < 2 ? 0 : 32) + 8 (s % 8 / 2) + 4 (i % 2) + 2 (s / 8) + s % 2
+                // ldmatrix.x4: lanes 0-7 give the rows of matrix 0 (slots 0-7, ranks +0), 8-15 matrix 1
+                // (slots 8-15, ranks +0), 16-23 matrix 2 (slots 0-7, ranks +8), 24-31 matrix 3 (slots 8-15, +8)
+                const int s = (lane & 7) + ((lane >> 3) & 1) * 8;
+                const int krow = (i < 2 ? 0 : 32) + 8 * ((s & 7) >> 1) + 4 * (i & 1) + 2 * (s >> 3) + (s & 1);
+                const int f = (krow & 1) | (((krow >> 3) & 3) << 1);
+#pragma unroll
+                for (int nt = 0; nt < QT_RCHUNK / 8; nt += 2) {
+                    if (nt * 8 < rn) {
+                        uint32_t b[4];
+                        ldmatrix_x4_trans(b, base + krow * ld_pitch + (((nt + (lane >> 4)) ^ f) << 4));
+                        mma16816<T>(acc[nt], a, b[0], b[1]);
+                        mma16816<T>(acc[nt + 1], a, b[2], b[3]);
+                    }
+                }
+            }
+            __syncwarp();
+        }
+
+        if (!quantize) continue;
+
+        // ---- shift, smooth, per-group max, codes
+        if (p.shift != 0.f) {
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[r][i] += p.shift;
+        }
+        if (smooth) {
+            float s[16];
+            load8<T>(smooth + c0, true, *reinterpret_cast<float(*)[8]>(&s[0]));
+            load8<T>(smooth + c0 + 32, true, *reinterpret_cast<float(*)[8]>(&s[8]));
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                float inv = 1.0f / s[i];
+                v[0][i] *= inv;
+                v[1][i] *= inv;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = r ? row_b : row_a;
+            const bool ok = r ? ok_b : ok_a;
+            uint8_t* orow = p.output + (long long)row * p.stride_om;
+            if (!p.fp4) {
+                float mx = p.is_unsigned ? v[r][0] : fabsf(v[r][0]);
+#pragma unroll
+                for (int i = 1; i < 16; ++i) mx = fmaxf(mx, p.is_unsigned ? v[r][i] : fabsf(v[r][i]));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                mx = fmaxf(mx, 0.f);
+                const float scale = mx / (p.is_unsigned ? 15.0f : 7.0f);
+                const float inv = 1.0f / (scale == 0.f ? 1.0f : scale);
+                const float lo = p.is_unsigned ? 0.f : -8.f, hi = p.is_unsigned ? 15.f : 7.f;
+                uint32_t w[2] = {0, 0};
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float q = fminf(fmaxf(rint_small(v[r][i] * inv), lo), hi);
+                    w[i >> 3] |= ((uint32_t)(int)q & 0xFu) << (4 * (i & 7));
+                }
+                if (ok) {
+                    *reinterpret_cast<uint32_t*>(orow + (c0 >> 1)) = w[0];
+                    *reinterpret_cast<uint32_t*>(orow + ((c0 + 32) >> 1)) = w[1];
+                    if (tig == 0) static_cast<T*>(p.oscales)[(long long)g * p.stride_sg + row] = from_f32<T>(scale);
+                }
+            } else {
+                // four 16-groups per 64 block: lanes (tig 0,1) share group 0 / 2, lanes (2,3) group 1 / 3
+                uint32_t w[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float mx = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(v[r][8 * h + i]));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                    const float scale = mx / 6.0f;
+                    const float inv = 1.0f / (scale == 0.f ? 1.0f : scale);
+                    uint32_t ww = 0;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) ww |= e2m1_encode(v[r][8 * h + i] * inv) << (4 * i);
+                    w[h] = ww;
+                    if (ok && (tig & 1) == 0) {
+                        const int g16 = g * 4 + 2 * h + (tig >> 1);
+                        static_cast<uint8_t*>(p.oscales)[(long long)g16 * p.stride_sg + row] =
+                            (uint8_t)__nv_cvt_float_to_fp8(scale, __NV_SATFINITE, __NV_E4M3);
+                    }
+                }
+                if (ok) {
+                    *reinterpret_cast<uint32_t*>(orow + (c0 >> 1)) = w[0];
+                    *reinterpret_cast<uint32_t*>(orow + ((c0 + 32) >> 1)) = w[1];
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    // ---- fixed-order sum of the four K-quarter partials of each row block
+    if (rn > 0) {
+        __syncthreads();  // lora_down buffers are dead; reuse shared memory: [kq][rb][16 rows][QT_RCHUNK]
+        float* red = reinterpret_cast<float*>(smem);
+        float* mine = red + ((kq * 2 + rb) * 16) * QT_RCHUNK;
+#pragma unroll
+        for (int nt = 0; nt < QT_RCHUNK / 8; ++nt) {
+            const int c = nt * 8 + 2 * tig;
+            mine[gid * QT_RCHUNK + c] = acc[nt][0];
+            mine[gid * QT_RCHUNK + c + 1] = acc[nt][1];
+            mine[(gid + 8) * QT_RCHUNK + c] = acc[nt][2];
+            mine[(gid + 8) * QT_RCHUNK + c + 1] = acc[nt][3];
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < QT_ROWS * rn; e += QT_WARPS * 32) {
+            const int row = e / rn, c = e % rn;
+            const int rrb = row >> 4, rr = row & 15;
+            float s = 0.f;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) s += red[((q * 2 + rrb) * 16 + rr) * QT_RCHUNK + c];
+            const int m = blockIdx.x * QT_ROWS + row;
+            if (m < p.M) p.lora_act_out[(long long)m * p.stride_lam + r0 + c] = s;
+        }
+    }
+}
+
+}  // namespace
+}  // namespace nb
+
+extern "C" int nb_quantize_w4a4(const nb_quant_args* a, void* stream) {
+    using namespace nb;
+    NB_REQUIRE(a && a->input && a->output && a->oscales);
+    NB_REQUIRE(a->M >= 0 && a->K > 0 && a->K % 64 == 0);
+    NB_REQUIRE(a->dtype == NB_DTYPE_BF16 || a->dtype == NB_DTYPE_FP16);
+    const bool lora = a->lora_down != nullptr && a->lora_act_out != nullptr && a->R > 0;
+    if (lora) NB_REQUIRE(a->R % 16 == 0 && a->stride_ld % 8 == 0 && aligned16(a->lora_down));
+    NB_REQUIRE(aligned16(a->input) && a->stride_im % 8 == 0);
+    NB_REQUIRE((reinterpret_cast<uintptr_t>(a->output) & 3) == 0 && a->stride_om % 4 == 0);
+    if (a->smooth) NB_REQUIRE(aligned16(a->smooth));
+    if (a->M == 0) return NB_OK;
+
+    QParams p;
+    p.input = a->input;
+    p.output = static_cast<uint8_t*>(a->output);
+    p.oscales = a->oscales;
+    p.lora_down = a->lora_down;
+    p.lora_act_out = a->lora_act_out;
+    p.smooth = a->smooth;
+    p.M = a->M; p.K = a->K; p.R = lora ? a->R : 0;
+    p.fuse_glu = a->fuse_glu; p.fuse_gelu = a->fuse_gelu; p.fp4 = a->fp4; p.is_unsigned = a->is_unsigned;
+    p.do_lora = lora;
+    p.shift = a->shift;
+    p.stride_im = a->stride_im; p.stride_om = a->stride_om; p.stride_sg = a->stride_sg;
+    p.stride_ld = a->stride_ld; p.stride_lam = a->stride_lam;
+
+    dim3 grid((a->M + QT_ROWS - 1) / QT_ROWS, lora ? (a->R + QT_RCHUNK - 1) / QT_RCHUNK : 1);
+    const int ld_pitch = QT_RCHUNK * 2;
+    const size_t smem = (size_t)QT_WARPS * 2 * 64 * ld_pitch;  // 128 KB; also covers the 32 KB reduction buffer
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (a->dtype == NB_DTYPE_BF16) {
+        NB_CUDA_CHECK(cudaFuncSetAttribute(quantize_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)smem));
+        quantize_kernel<__nv_bfloat16><<<grid, QT_WARPS * 32, smem, s>>>(p);
+    } else {
+        NB_CUDA_CHECK(
+            cudaFuncSetAttribute(quantize_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        quantize_kernel<__half><<<grid, QT_WARPS * 32, smem, s>>>(p);
+    }
+    NB_CUDA_CHECK(cudaGetLastError());
+    return NB_OK;
+}
