@@ -16,7 +16,7 @@ import threading
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libnunchaku_b200.so")
+LIB_PATH = os.environ.get("NUNCHAKU_B200_LIB") or os.path.join(_HERE, "libnunchaku_b200.so")
 
 NB_OK, NB_ERR_INVALID, NB_ERR_UNSUPPORTED, NB_ERR_LAUNCH, NB_ERR_DEVICE, NB_ERR_TOO_LARGE = range(6)
 DTYPE_CODE = {torch.bfloat16: 0, torch.float16: 1}

@@ -259,8 +259,8 @@ __global__ void __launch_bounds__(128) requant_rows_kernel(const float* lin, int
         const float scale = mx / (mode == 0 ? 15.0f : 7.0f);
         const float inv = 1.0f / (scale == 0.f ? 1.0f : scale);
         const float lo = mode == 0 ? 0.f : -8.f, hi = mode == 0 ? 15.f : 7.f;
-        const int q0 = (int)fminf(fmaxf(rint_small(v0 * inv), lo), hi);
-        const int q1 = (int)fminf(fmaxf(rint_small(v1 * inv), lo), hi);
+        const int q0 = (int)fminf(fmaxf(rint_small(__fmul_rn(v0, inv)), lo), hi);
+        const int q1 = (int)fminf(fmaxf(rint_small(__fmul_rn(v1, inv)), lo), hi);
         qout[(long long)m * stride_qm + g * 32 + lane] = (uint8_t)((q0 & 0xF) | ((q1 & 0xF) << 4));
         if (lane == 0) oscales[(long long)g * stride_osg + m] = from_f32<T>(scale);
     }

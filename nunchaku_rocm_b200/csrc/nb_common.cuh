@@ -95,7 +95,7 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 
 // round-half-even of |x| < 2^22 by the magic-number add (gemm_w4a4.py:1317-1325)
-__device__ __forceinline__ float rint_small(float x) { return (x + 12582912.0f) - 12582912.0f; }
+__device__ __forceinline__ float rint_small(float x) { return __fsub_rn(__fadd_rn(x, 12582912.0f), 12582912.0f); }
 
 // e2m1 encode with the reference's thresholds: ties go to the larger magnitude (gemm_w4a4.py:116-135)
 __device__ __forceinline__ uint32_t e2m1_encode(float x) {
@@ -143,10 +143,14 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 }
 // Bounded wait: gives up after ~2 s (or as soon as another thread of the CTA has given up), records
 // `code` in *abort_flag and returns false.  The caller must then unwind without touching the data.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+// Between polls the thread sleeps `backoff_ns`, so that warps waiting on a full pipeline do not take issue
+// slots and shared-memory bandwidth from the warps that are working.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                          unsigned backoff_ns = 32) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = 0;
     for (uint32_t spin = 1;; ++spin) {
+        __nanosleep(backoff_ns);
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 255u) == 0) {
             if (*abort_flag) return false;
@@ -226,6 +230,46 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         : "memory");
 }
 
+// 16 lanes x 64 columns in the accumulator-fragment layout: with gid = lane / 4, tig = lane % 4, register
+// 4 j + 2 r + e is TMEM lane (lane field) + 8 r + gid, column 8 j + 2 tig + e
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+// packed pairs of fp32 in one 64-bit register (low word = first element) and the sm_100 packed FMA / ADD
+__device__ __forceinline__ uint64_t pack_u32x2(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    return pack_u32x2(__float_as_uint(lo), __float_as_uint(hi));
+}
+__device__ __forceinline__ float2 unpack_f32x2(uint64_t v) {
+    uint32_t lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+    return make_float2(__uint_as_float(lo), __uint_as_float(hi));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 // Shared-memory matrix descriptor, K-major operand without swizzle: 8-row x 16-byte core matrices,
 // `lbo` bytes between the core matrices of consecutive 16-byte K chunks, `sbo` bytes between
 // consecutive 8-row groups.
@@ -243,7 +287,7 @@ __device__ __host__ constexpr uint32_t umma_idesc(uint32_t c_fmt, uint32_t a_fmt
     return (c_fmt << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
-__device__ __forceinline__ void setmaxnreg_inc_200() { asm volatile("setmaxnreg.inc.sync.aligned.u32 200;"); }
-__device__ __forceinline__ void setmaxnreg_dec_56() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
+__device__ __forceinline__ void setmaxnreg_inc_176() { asm volatile("setmaxnreg.inc.sync.aligned.u32 176;"); }
+__device__ __forceinline__ void setmaxnreg_dec_80() { asm volatile("setmaxnreg.dec.sync.aligned.u32 80;"); }
 
 }  // namespace nb

@@ -224,7 +224,7 @@ __global__ void __launch_bounds__(QT_WARPS * 32) quantize_kernel(const QParams p
                 uint32_t w[2] = {0, 0};
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    float q = fminf(fmaxf(rint_small(v[r][i] * inv), lo), hi);
+                    float q = fminf(fmaxf(rint_small(__fmul_rn(v[r][i], inv)), lo), hi);
                     w[i >> 3] |= ((uint32_t)(int)q & 0xFu) << (4 * (i & 7));
                 }
                 if (ok) {
@@ -245,7 +245,7 @@ __global__ void __launch_bounds__(QT_WARPS * 32) quantize_kernel(const QParams p
                     const float inv = 1.0f / (scale == 0.f ? 1.0f : scale);
                     uint32_t ww = 0;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) ww |= e2m1_encode(v[r][8 * h + i] * inv) << (4 * i);
+                    for (int i = 0; i < 8; ++i) ww |= e2m1_encode(__fmul_rn(v[r][8 * h + i], inv)) << (4 * i);
                     w[h] = ww;
                     if (ok && (tig & 1) == 0) {
                         const int g16 = g * 4 + 2 * h + (tig >> 1);

@@ -1,3 +1,3 @@
 """Operator API with the signatures of the reference's ``nunchaku/ops`` package."""
 
-from . import backend, gemm, quantize  # noqa: F401
+from . import backend, dispatch, gemm, gemv, quantize  # noqa: F401

@@ -16,7 +16,7 @@ def test_library_exports_every_declared_symbol():
 
     lib = _lib.lib()
     header = open(os.path.join(ROOT, "include", "nunchaku_b200.h")).read()
-    declared = sorted(set(re.findall(r"\b(nb_[a-z0-9_]+)\s*\(", header)))
+    declared = sorted(set(re.findall(r"^(?:int|int64_t|const char\*)\s+(nb_[a-z0-9_]+)\s*\(", header, re.M)))
     assert len(declared) >= 10
     for sym in declared:
         assert hasattr(lib, sym), f"{sym} is declared in the header but not exported"
