@@ -110,8 +110,15 @@ typedef struct nb_requant_args {
  */
 int nb_gemm_w4a4(const nb_gemm_args* args, const void* epi, int epi_kind, void* stream);
 
-/* Bytes of device scratch nb_gemm_w4a4 needs for this call (0 for most). */
+/*
+ * Bytes of device scratch nb_gemm_w4a4 needs for this call: the tensor-core kernel keeps the operands widened
+ * to int8 and the scales converted to fp32 there, the generic kernel the fp32 tile of a fused row epilogue.
+ * The buffer must be 256-byte aligned; its contents are dead when the call's kernels have run.
+ */
 int64_t nb_gemm_w4a4_scratch_bytes(const nb_gemm_args* args, const void* epi, int epi_kind);
+
+/* 1 when nb_gemm_w4a4 would run this call on the tcgen05 kernel, 0 when on the generic kernel. */
+int64_t nb_gemm_w4a4_uses_tcgen05(const nb_gemm_args* args, const void* epi, int epi_kind);
 
 /*
  * Debug: the exact int32 group sums p_g[m, n] = sum_{k in g} a[m,k] * w[n,k] as the tensor-core

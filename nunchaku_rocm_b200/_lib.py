@@ -110,6 +110,8 @@ def lib() -> C.CDLL:
                 l.nb_gemm_w4a4_scratch_bytes.restype = C.c_int64
                 l.nb_gemm_w4a4.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_int, C.c_void_p]
                 l.nb_gemm_w4a4_scratch_bytes.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_int]
+                l.nb_gemm_w4a4_uses_tcgen05.restype = C.c_int64
+                l.nb_gemm_w4a4_uses_tcgen05.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_int]
                 l.nb_gemm_w4a4_group_sums.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_void_p]
                 l.nb_quantize_w4a4.argtypes = [C.POINTER(QuantArgs), C.c_void_p]
                 l.nb_qk_norm_rope.argtypes = [

@@ -5,25 +5,28 @@
 // 64-wide K group g one EXACT int32 dot p_g[m,n]; acc += float(p_g) * as[g,m] * ws[g,n] in fp32;
 // then + T(lora_act) . lora_up^T (16-bit operands, fp32 accumulate), + bias, one rounding to T.
 //
-// Pipeline of one persistent CTA (512 threads, one CTA per SM, static contiguous range of 128 x 128 tiles):
-//   warp 0      TMA producer: packed int4 rows of A and W (128 x 32 B each, 32-byte swizzle) of one K group,
-//               plus that group's scale rows, into a ring (no multicast, no cluster).
-//   warps 2-7   widen: nibble n -> int8 16*n (n << 4 keeps the sign in the top bit; the factor 256 on the
-//               product is folded into the activation scale) written in the K-major no-swizzle UMMA layout
-//               (8-row x 16-byte core matrices, one 16-byte K chunk after another); scales converted to
-//               fp32.  The same permutation of k inside the group is applied to A and W, which a dot
-//               product does not see.  For the low-rank branch they stage T(lora_act) and lora_up as
-//               bf16/fp16 operands through the same buffers.
-//   warp 1      MMA issuer: two 128 x 128 x 32 kind::i8 MMAs per group into one of FOUR tensor-memory
-//               slots, so the tensor pipe runs up to three groups ahead of the drain; tcgen05.commit
-//               releases the operand buffer and publishes the slot.  The low-rank product is kind::f16
-//               into an fp32 slot of the same ring.
-//   warps 8-15  drain: a warp owns 32 rows x 64 columns.  tcgen05.ld.16x256b gives a thread the
-//               accumulator-fragment layout (4 rows x 16 columns), so it needs 4 row scales and 16 column
-//               scales per group; int -> float by the magic-number add, then two packed fp32x2 FMAs per
-//               column pair.  Loads of the next 16-lane chunk (of this or the next group) are in flight
-//               while a chunk is scaled.  After the last group: bias, optional per-head RMSNorm + RoPE,
-//               rounding, and a coalesced store through a padded per-warp staging tile.
+// Two launches per call:
+//  1. `prepack_kernel` (HBM-bound, a few microseconds): packed nibbles -> int8 rows holding 16 * value
+//     (n << 4 keeps the sign in the top bit; the factor 256 on a product is undone by the magic constant
+//     of the drain), with the same permutation of k inside every 8-element run for activations and
+//     weights, which a dot product does not see; scales -> fp32 in the order the drain reads them;
+//     lora_act -> T.  Measured on B200: widening inside the GEMM through shared memory costs a
+//     generic->async proxy fence of ~3000 cycles per K group and competes with the drain for issue slots and
+//     shared-memory bandwidth; with the operands pre-widened every byte the tensor core reads is written by
+//     TMA and the SM's CUDA cores only do the per-group scaling.
+//  2. `gemm_tc_kernel`: one persistent CTA per SM (320 threads) walks a static contiguous range of
+//     128 x 128 output tiles.  A stage of the shared-memory ring holds two K groups (128 k):
+//       warp 0    TMA producer: A and W rows (128 x 128 B each, 128-byte swizzle) and the two groups' scale
+//                 rows (no multicast, no cluster); low-rank chunks of 32 ranks travel through the same ring.
+//       warp 1    MMA issuer: per group two 128 x 128 x 32 kind::i8 MMAs into one of FOUR tensor-memory slots,
+//                 so the tensor pipe runs up to three groups ahead of the drain; tcgen05.commit publishes the
+//                 slot and, per stage, releases the operands.  The low-rank product is kind::f16 into an
+//                 fp32 slot of the same ring.
+//       warps 2-9 drain: a warp owns 32 rows x 64 columns.  tcgen05.ld.16x256b gives a thread the
+//                 accumulator-fragment layout (4 rows x 16 columns), so it needs 4 row scales and 16 column
+//                 scales per group; int -> float by the magic-number add, then two packed fp32x2 FMAs per
+//                 column pair.  After the last group: bias, optional per-head RMSNorm + RoPE, rounding, and a
+//                 coalesced store through a padded per-warp staging tile.
 // Every wait on an mbarrier is bounded (~2 s); on expiry the CTA records a code in the status word,
 // unwinds without touching more data and frees its tensor memory.
 #include <cuda.h>
@@ -38,60 +41,50 @@ namespace tc {
 
 constexpr int BM = 128;
 constexpr int BN = 128;
-constexpr int PK_STAGES = 6;
-constexpr int WD_STAGES = 4;
-constexpr int SC_STAGES = 6;
+constexpr int STAGES = 4;
 constexpr int NSLOT = 4;            // tensor-memory accumulator slots of BN columns
-constexpr int NTHREADS = 512;
-constexpr int WIDEN_THREADS = 192;  // warps 2..7
-constexpr int WIDEN_WARPS = 6;
-constexpr int DRAIN_WARPS = 8;      // warps 8..15
+constexpr int DRAIN_WARPS = 8;      // warps 2..9
+constexpr int NTHREADS = 64 + DRAIN_WARPS * 32;
 constexpr int COLS = BN / 2;        // columns one drain warp owns
-constexpr uint32_t MAGIC_BITS = 0x4B400000u;  // 1.5 * 2^23
-constexpr float MAGIC_F = 12582912.0f;
+// 1.5 * 2^15: one unit in the last place is 2^-8, so adding 256 * p to the bit pattern gives 49152 + p
+constexpr uint32_t MAGIC_BITS = 0x47400000u;
+constexpr float MAGIC_F = 49152.0f;
 
 struct Cfg {
-    static constexpr int PK_A = BM * 32, PK_W = BN * 32, PK_AS = BM * 2, PK_WS = BN * 2;
-    static constexpr int PK_BYTES = PK_A + PK_W + PK_AS + PK_WS;
-    static constexpr int WD_A = BM * 64, WD_W = BN * 64;
-    static constexpr int WD_BYTES = WD_A + WD_W;
-    static constexpr int SC_BYTES = BN * 4 + BM * 4 * 2;
+    static constexpr int ST_A = BM * 128, ST_W = BN * 128;  // two K groups of int8 per row
+    static constexpr int ST_AS = 2 * BM * 8;                // per group and row: (as, -MAGIC * as)
+    static constexpr int ST_WS = 2 * BN * 4;                // per group and column: ws, in drain order
+    static constexpr int ST_BYTES = ST_A + ST_W + ST_AS + ST_WS;
     static constexpr int STG_PITCH = COLS * 2 + 16;
     static constexpr int STG_BYTES = DRAIN_WARPS * 32 * STG_PITCH;
     static constexpr int XCH_BYTES = DRAIN_WARPS * 32 * 4;  // per-row partial sums exchanged between column halves
-    static constexpr int OFF_PK = 0;
-    static constexpr int OFF_WD = OFF_PK + PK_STAGES * PK_BYTES;
-    static constexpr int OFF_SC = OFF_WD + WD_STAGES * WD_BYTES;
-    static constexpr int OFF_STG = OFF_SC + SC_STAGES * SC_BYTES;
+    static constexpr int OFF_ST = 0;
+    static constexpr int OFF_STG = OFF_ST + STAGES * ST_BYTES;
     static constexpr int OFF_XCH = OFF_STG + STG_BYTES;
     static constexpr int OFF_BAR = OFF_XCH + XCH_BYTES;
     static constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;  // + slack to align the base to 1 KB
     static constexpr int TMEM_COLS = NSLOT * BN;             // 512
 };
-static_assert(Cfg::OFF_WD % 1024 == 0 && Cfg::PK_BYTES % 256 == 0, "TMA destinations must stay 256-byte aligned");
+static_assert(Cfg::ST_BYTES % 1024 == 0, "stage buffers must stay 1 KB aligned for the 128-byte swizzle");
+static_assert(Cfg::SMEM_BYTES <= 232448, "shared memory budget");
 
 enum {  // barrier indices
-    B_PK_FULL = 0,
-    B_PK_EMPTY = B_PK_FULL + PK_STAGES,
-    B_WD_FULL = B_PK_EMPTY + PK_STAGES,
-    B_WD_EMPTY = B_WD_FULL + WD_STAGES,
-    B_SC_FULL = B_WD_EMPTY + WD_STAGES,
-    B_SC_EMPTY = B_SC_FULL + SC_STAGES,
-    B_ACC_FULL = B_SC_EMPTY + SC_STAGES,
+    B_FULL = 0,
+    B_EMPTY = B_FULL + STAGES,      // tcgen05.commit: the stage's MMAs have read their operands
+    B_SCDONE = B_EMPTY + STAGES,    // one arrival per drain warp: the stage's scales have been read (int8 stages only)
+    B_ACC_FULL = B_SCDONE + STAGES,
     B_ACC_EMPTY = B_ACC_FULL + NSLOT,
-    B_XCH = B_ACC_EMPTY + NSLOT,  // one per TMEM lane quarter: the two warps that share rows
+    B_XCH = B_ACC_EMPTY + NSLOT,    // one per TMEM lane quarter: the two warps that share rows
     B_COUNT = B_XCH + 4
 };
 
 struct TcParams {
     void* out;
     const void* bias;
-    const float* lora_act;
-    const void* lora_up;
     int32_t* p_out;  // debug: (K/64, M, N) group sums
     int M, N, K, actual_m, R;
     int act_unsigned;
-    long long stride_om, stride_lam, stride_lun;
+    long long stride_om;
     int* status;
     // QK epilogue
     const void* norm_q;
@@ -102,26 +95,47 @@ struct TcParams {
     float eps;
 };
 
-#ifdef NB_TRACE
-// Timeline instrumentation (debug builds only): CTA 0 records clock64() per pipeline event and step.
-__device__ unsigned long long* g_trace = nullptr;
-#define NB_TR(step, ev)                                                                      \
-    do {                                                                                     \
-        if (g_trace && blockIdx.x == 0 && (step) < 256) g_trace[(step)*16 + (ev)] = clock64(); \
-    } while (0)
+#ifdef NB_PROF
+// Cycle accounting (debug builds only): every warp of CTA 0 adds up the clock() ticks it spends per phase.
+__device__ unsigned long long* g_prof = nullptr;
+#define NB_PF_DECL unsigned pf_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; unsigned pf_t_ = clock();
+#define NB_PF(i) do { unsigned n_ = clock(); pf_[i] += n_ - pf_t_; pf_t_ = n_; } while (0)
+#define NB_PF_DUMP() do { if (g_prof && blockIdx.x == 0 && (threadIdx.x & 31) == 0) for (int i_ = 0; i_ < 8; ++i_) g_prof[(threadIdx.x >> 5) * 8 + i_] = pf_[i_]; } while (0)
 #else
-#define NB_TR(step, ev) \
-    do {                \
-    } while (0)
+#define NB_PF_DECL
+#define NB_PF(i) do {} while (0)
+#define NB_PF_DUMP() do {} while (0)
 #endif
 
 // error codes written to *status: role * 16 + barrier kind
-enum { E_PROD = 0x10, E_WIDEN = 0x20, E_MMA = 0x30, E_DRAIN = 0x40 };
+enum { E_PROD = 0x10, E_MMA = 0x30, E_DRAIN = 0x40 };
+
+// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+    d |= (uint64_t)1 << 16;              // leading byte offset: unused for swizzled K-major
+    d |= (uint64_t)(1024 >> 4) << 32;    // stride byte offset
+    d |= (uint64_t)1 << 46;              // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;              // SWIZZLE_128B
+    return d;
+}
+// K-major operand, 64-byte swizzle: rows of 64 bytes, 8-row groups 512 bytes apart
+__device__ __forceinline__ uint64_t umma_desc_sw64(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(512 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)4 << 61;              // SWIZZLE_64B
+    return d;
+}
 
 template <int EPI, typename T, bool DEBUG_P>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                const __grid_constant__ CUtensorMap tm_as, const __grid_constant__ CUtensorMap tm_ws,
+               const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lu,
                const TcParams p) {
     using C = Cfg;
     extern __shared__ uint8_t smem_raw[];
@@ -135,9 +149,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     auto bar = [&](int i) { return s_bar + 8u * i; };
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < PK_STAGES; ++i) { mbar_init(bar(B_PK_FULL + i), 1); mbar_init(bar(B_PK_EMPTY + i), WIDEN_WARPS); }
-        for (int i = 0; i < WD_STAGES; ++i) { mbar_init(bar(B_WD_FULL + i), WIDEN_WARPS); mbar_init(bar(B_WD_EMPTY + i), 1); }
-        for (int i = 0; i < SC_STAGES; ++i) { mbar_init(bar(B_SC_FULL + i), WIDEN_WARPS); mbar_init(bar(B_SC_EMPTY + i), DRAIN_WARPS); }
+        for (int i = 0; i < STAGES; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); mbar_init(bar(B_SCDONE + i), DRAIN_WARPS); }
         for (int i = 0; i < NSLOT; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), DRAIN_WARPS); }
         for (int i = 0; i < 4; ++i) mbar_init(bar(B_XCH + i), 2);
         *abort_s = 0;
@@ -158,324 +170,222 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const int per = (total + gridDim.x - 1) / gridDim.x;
     const int t_begin = min(total, (int)blockIdx.x * per), t_end = min(total, t_begin + per);
     const int G = p.K / 64;
-    const int LCH = (p.R + 31) / 32;  // low-rank chunks of 32 ranks
+    const int GS = (G + 1) / 2;       // int8 stages per tile (two K groups each)
+    const int LCH = (p.R + 31) / 32;  // low-rank stages per tile (32 ranks each)
 
-    if (warp < 8) {
-        setmaxnreg_dec_80();
-        if (warp == 0) {
-            // ================================ TMA producer ================================
-            if (lane == 0) {
-                tma_prefetch_desc(&tm_a); tma_prefetch_desc(&tm_w); tma_prefetch_desc(&tm_as); tma_prefetch_desc(&tm_ws);
-                uint32_t it = 0;
-                bool ok = true;
-                for (int t = t_begin; t < t_end && ok; ++t) {
-                    const int m0 = (t / NT) * BM, n0 = (t % NT) * BN;
-                    for (int g = 0; g < G; ++g, ++it) {
-                        const int s = it % PK_STAGES;
-                        if (!mbar_wait(bar(B_PK_EMPTY + s), ((it / PK_STAGES) & 1) ^ 1, abort_s, E_PROD | 1, 128)) { ok = false; break; }
-                        NB_TR(it, 0);
-                        const uint32_t dst = s_base + C::OFF_PK + s * C::PK_BYTES;
-                        mbar_expect_tx(bar(B_PK_FULL + s), C::PK_BYTES);
-                        tma_load_2d(dst, &tm_a, bar(B_PK_FULL + s), g * 32, m0);
-                        tma_load_2d(dst + C::PK_A, &tm_w, bar(B_PK_FULL + s), g * 32, n0);
-                        tma_load_2d(dst + C::PK_A + C::PK_W, &tm_as, bar(B_PK_FULL + s), m0, g);
-                        tma_load_2d(dst + C::PK_A + C::PK_W + C::PK_AS, &tm_ws, bar(B_PK_FULL + s), n0, g);
-                    }
-                }
-                if (!ok) {
-                    // let copies already in flight land before the CTA goes away (bounded)
-                    for (int s = 0; s < PK_STAGES; ++s) {
-                        const uint32_t issued = it > (uint32_t)s ? (it - 1 - s) / PK_STAGES + 1 : 0;  // fills of stage s
-                        if (issued) {
-                            uint64_t t0 = globaltimer_ns();
-                            while (!mbar_try_wait(bar(B_PK_FULL + s), (issued - 1) & 1) && globaltimer_ns() - t0 < 200000000ull) {}
-                        }
-                    }
-                }
-            }
-        } else if (warp == 1) {
-            // ================================ MMA issuer ================================
-            if (lane == 0) {
-                const uint32_t idesc_i8 = umma_idesc(2u, p.act_unsigned ? 0u : 1u, 1u, BN);
-                const uint32_t f16fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-                const uint32_t idesc_lr = umma_idesc(1u, f16fmt, f16fmt, BN);
-                uint32_t wit = 0, ait = 0;
-                bool ok = true;
-                for (int t = t_begin; t < t_end && ok; ++t) {
-                    for (int g = 0; g < G && ok; ++g, ++wit, ++ait) {
-                        const int w = wit % WD_STAGES, slot = ait % NSLOT;
-                        if (!mbar_wait(bar(B_WD_FULL + w), (wit / WD_STAGES) & 1, abort_s, E_MMA | 1)) { ok = false; break; }
-                        NB_TR(ait, 4);
-                        if (!mbar_wait(bar(B_ACC_EMPTY + slot), ((ait / NSLOT) & 1) ^ 1, abort_s, E_MMA | 2)) { ok = false; break; }
-                        NB_TR(ait, 5);
-                        tc_fence_after();
-                        const uint32_t a_addr = s_base + C::OFF_WD + w * C::WD_BYTES;
-                        const uint32_t w_addr = a_addr + C::WD_A;
-                        const uint32_t d = tmem_base + slot * BN;
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const uint64_t ad = umma_desc_kmajor(a_addr + h * 2 * (BM * 16), BM * 16, 128);
-                            const uint64_t bd = umma_desc_kmajor(w_addr + h * 2 * (BN * 16), BN * 16, 128);
-                            mma_i8(d, ad, bd, idesc_i8, h);
-                        }
-                        tc_commit(bar(B_WD_EMPTY + w));
-                        tc_commit(bar(B_ACC_FULL + slot));
-                    }
-                    if (ok && LCH > 0) {
-                        const int slot = ait % NSLOT;
-                        if (!mbar_wait(bar(B_ACC_EMPTY + slot), ((ait / NSLOT) & 1) ^ 1, abort_s, E_MMA | 3)) { ok = false; break; }
-                        for (int c = 0; c < LCH && ok; ++c, ++wit) {
-                            const int w = wit % WD_STAGES;
-                            if (!mbar_wait(bar(B_WD_FULL + w), (wit / WD_STAGES) & 1, abort_s, E_MMA | 4)) { ok = false; break; }
-                            tc_fence_after();
-                            const uint32_t a_addr = s_base + C::OFF_WD + w * C::WD_BYTES;
-                            const uint32_t w_addr = a_addr + C::WD_A;
-                            const uint32_t d = tmem_base + slot * BN;
-#pragma unroll
-                            for (int h = 0; h < 2; ++h) {
-                                const uint64_t ad = umma_desc_kmajor(a_addr + h * 2 * (BM * 16), BM * 16, 128);
-                                const uint64_t bd = umma_desc_kmajor(w_addr + h * 2 * (BN * 16), BN * 16, 128);
-                                mma_f16(d, ad, bd, idesc_lr, (c | h) ? 1u : 0u);
-                            }
-                            tc_commit(bar(B_WD_EMPTY + w));
-                        }
-                        if (ok) { tc_commit(bar(B_ACC_FULL + slot)); ++ait; }
-                    }
-                }
-            }
-        } else {
-            // ================================ widen warps ================================
-            const int wt = threadIdx.x - 64;
-            uint32_t it = 0, wit = 0, sit = 0;
+    if (warp == 0) {
+        // ================================ TMA producer ================================
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_a); tma_prefetch_desc(&tm_w); tma_prefetch_desc(&tm_as); tma_prefetch_desc(&tm_ws);
+            if (LCH) { tma_prefetch_desc(&tm_la); tma_prefetch_desc(&tm_lu); }
+            uint32_t it = 0;
+            uint32_t sc_uses = 0;  // 8 bits per stage: how many int8 fills the stage has had (mod 256)
             bool ok = true;
+            NB_PF_DECL
             for (int t = t_begin; t < t_end && ok; ++t) {
                 const int m0 = (t / NT) * BM, n0 = (t % NT) * BN;
-                for (int g = 0; g < G; ++g, ++it, ++wit, ++sit) {
-                    const int s = it % PK_STAGES, w = wit % WD_STAGES, c = sit % SC_STAGES;
-                    if (!mbar_wait(bar(B_PK_FULL + s), (it / PK_STAGES) & 1, abort_s, E_WIDEN | 1, 128)) { ok = false; break; }
-                    if (wt == 0) NB_TR(sit, 1);
-                    if (!mbar_wait(bar(B_WD_EMPTY + w), ((wit / WD_STAGES) & 1) ^ 1, abort_s, E_WIDEN | 2, 128)) { ok = false; break; }
-                    if (!mbar_wait(bar(B_SC_EMPTY + c), ((sit / SC_STAGES) & 1) ^ 1, abort_s, E_WIDEN | 3, 128)) { ok = false; break; }
-                    if (wt == 0) NB_TR(sit, 2);
-                    const uint8_t* pk = smem + C::OFF_PK + s * C::PK_BYTES;
-                    uint8_t* wd = smem + C::OFF_WD + w * C::WD_BYTES;
-                    // 16-byte units: unit u = 32 blk + l -> row 16 blk + (l & 15), half l >> 4.  The TMA wrote the
-                    // rows with the 32-byte swizzle: the two 16-byte halves of a row swap when bit 2 of the row is
-                    // set, which makes the 16 rows a half-warp reads hit 16 different bank groups.
-#ifdef NB_EXP_NOWIDEN
-                    for (int u = wt; u < 0; u += WIDEN_THREADS) {
-#else
-                    for (int u = wt; u < (BM + BN) * 2; u += WIDEN_THREADS) {
-#endif
-                        const int blk = u >> 5, l = u & 31;
-                        const int row_all = blk * 16 + (l & 15), half = l >> 4;
-                        const bool is_w = row_all >= BM;
-                        const int row = is_w ? row_all - BM : row_all;
-                        const int phys_half = half ^ ((row >> 2) & 1);
-                        const uint4 v = *reinterpret_cast<const uint4*>(pk + (is_w ? C::PK_A : 0) + row * 32 + phys_half * 16);
-                        uint4 lo, hi;
-                        lo.x = (v.x << 4) & 0xF0F0F0F0u; hi.x = v.x & 0xF0F0F0F0u;
-                        lo.y = (v.y << 4) & 0xF0F0F0F0u; hi.y = v.y & 0xF0F0F0F0u;
-                        lo.z = (v.z << 4) & 0xF0F0F0F0u; hi.z = v.z & 0xF0F0F0F0u;
-                        lo.w = (v.w << 4) & 0xF0F0F0F0u; hi.w = v.w & 0xF0F0F0F0u;
-                        const int rows = is_w ? BN : BM;
-                        uint8_t* dst = wd + (is_w ? C::WD_A : 0) + (2 * half) * rows * 16 + row * 16;
-#ifndef NB_EXP_NOSTS
-                        *reinterpret_cast<uint4*>(dst) = lo;
-                        *reinterpret_cast<uint4*>(dst + rows * 16) = hi;
-#else
-                        if (lo.x == 0x12345 && hi.y == 0x777) *reinterpret_cast<uint4*>(dst) = lo;
-#endif
-                    }
-                    // scales -> fp32: ws[n] (permuted for the drain's fragment layout); as' = as / 256; cm = -MAGIC * as'
+                for (int j = 0; j < GS + LCH; ++j, ++it) {
+                    const int s = it % STAGES;
+                    NB_PF(7);
+                    if (!mbar_wait(bar(B_EMPTY + s), ((it / STAGES) & 1) ^ 1, abort_s, E_PROD | 1, 500)) { ok = false; break; }
                     {
-                        const T* as_t = reinterpret_cast<const T*>(pk + C::PK_A + C::PK_W);
-                        const T* ws_t = reinterpret_cast<const T*>(pk + C::PK_A + C::PK_W + C::PK_AS);
-                        float* ws_f = reinterpret_cast<float*>(smem + C::OFF_SC + c * C::SC_BYTES);
-                        float* as_f = ws_f + BN;
-                        float* cm_f = as_f + BM;
-                        if (wt < BN) {
-                            // column i of the tile -> [warp half][pair of 8-col blocks][tig][4]: one 128-bit load of a
-                            // drain thread is (cols c, c+1 of block j, cols c, c+1 of block j+1)
-                            const int i = wt;
-                            const int hf = i / COLS, cc = i % COLS;
-                            const int blk = cc >> 3, tg = (cc >> 1) & 3, e = cc & 1;
-                            ws_f[hf * COLS + (blk >> 1) * 16 + tg * 4 + (blk & 1) * 2 + e] = to_f32<T>(ws_t[i]);
-                        }
-                        if (wt < BM) {
-                            const float a = to_f32<T>(as_t[wt]) * (1.0f / 256.0f);
-                            as_f[wt] = a;
-                            cm_f[wt] = -MAGIC_F * a;
-                        }
+                        // the drain must also be done with the scales of the stage's last int8 fill
+                        const uint32_t n = (sc_uses >> (8 * s)) & 0xFFu;
+                        if (!mbar_wait(bar(B_SCDONE + s), (n & 1) ^ 1, abort_s, E_PROD | 2, 500)) { ok = false; break; }
+                        if (j < GS) sc_uses = (sc_uses & ~(0xFFu << (8 * s))) | (((n + 1) & 0xFFu) << (8 * s));
                     }
-#ifndef NB_EXP_NOFENCE
-                    fence_proxy_async_smem();
-#endif
-                    __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive(bar(B_WD_FULL + w));
-                        mbar_arrive(bar(B_SC_FULL + c));
-                        mbar_arrive(bar(B_PK_EMPTY + s));
+                    NB_PF(0);
+                    const uint32_t dst = s_base + C::OFF_ST + s * C::ST_BYTES;
+                    if (j < GS) {
+                        mbar_expect_tx(bar(B_FULL + s), C::ST_BYTES);
+                        tma_load_2d(dst, &tm_a, bar(B_FULL + s), j * 128, m0);
+                        tma_load_2d(dst + C::ST_A, &tm_w, bar(B_FULL + s), j * 128, n0);
+                        tma_load_2d(dst + C::ST_A + C::ST_W, &tm_as, bar(B_FULL + s), m0 * 2, j * 2);
+                        tma_load_2d(dst + C::ST_A + C::ST_W + C::ST_AS, &tm_ws, bar(B_FULL + s), n0, j * 2);
+                    } else {
+                        // 32 ranks of T(lora_act) rows m0.. and lora_up rows n0..: 128 x 64 B each, 64-byte swizzle
+                        mbar_expect_tx(bar(B_FULL + s), 2 * 128 * 64);
+                        tma_load_2d(dst, &tm_la, bar(B_FULL + s), (j - GS) * 32, m0);
+                        tma_load_2d(dst + C::ST_A, &tm_lu, bar(B_FULL + s), (j - GS) * 32, n0);
                     }
-                    if (wt == 0) NB_TR(sit, 3);
-                }
-                if (!ok) break;
-                // ---- low-rank operands: T(lora_act[m0.., 32 ranks]) and lora_up[n0.., 32 ranks]
-                for (int lc = 0; lc < LCH; ++lc, ++wit) {
-                    const int w = wit % WD_STAGES;
-                    if (!mbar_wait(bar(B_WD_EMPTY + w), ((wit / WD_STAGES) & 1) ^ 1, abort_s, E_WIDEN | 4, 128)) { ok = false; break; }
-                    uint8_t* wd = smem + C::OFF_WD + w * C::WD_BYTES;
-                    const int r0 = lc * 32, rw = min(32, p.R - r0);
-                    for (int u = wt; u < BM * 4; u += WIDEN_THREADS) {
-                        const int ch = u / BM, row = u % BM;
-                        const int m = m0 + row;
-                        uint4 o = make_uint4(0, 0, 0, 0);
-                        if (m < p.M && ch * 8 < rw) {
-                            const float4* src = reinterpret_cast<const float4*>(p.lora_act + (long long)m * p.stride_lam + r0 + ch * 8);
-                            const float4 x = __ldg(src), y = __ldg(src + 1);
-                            o.x = pack2<T>(x.x, x.y); o.y = pack2<T>(x.z, x.w);
-                            o.z = pack2<T>(y.x, y.y); o.w = pack2<T>(y.z, y.w);
-                        }
-                        *reinterpret_cast<uint4*>(wd + ch * (BM * 16) + row * 16) = o;
-                    }
-                    for (int u = wt; u < BN * 4; u += WIDEN_THREADS) {
-                        const int ch = u / BN, row = u % BN;
-                        const int n = n0 + row;
-                        uint4 o = make_uint4(0, 0, 0, 0);
-                        if (n < p.N && ch * 8 < rw)
-                            o = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.lora_up) + (long long)n * p.stride_lun + r0 + ch * 8));
-                        *reinterpret_cast<uint4*>(wd + C::WD_A + ch * (BN * 16) + row * 16) = o;
-                    }
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(B_WD_FULL + w));
                 }
             }
+            NB_PF_DUMP();
+            if (!ok) {
+                // let copies already in flight land before the CTA goes away (bounded)
+                for (int s = 0; s < STAGES; ++s) {
+                    const uint32_t issued = it > (uint32_t)s ? (it - 1 - s) / STAGES + 1 : 0;  // fills of stage s
+                    if (issued) {
+                        uint64_t t0 = globaltimer_ns();
+                        while (!mbar_try_wait(bar(B_FULL + s), (issued - 1) & 1) && globaltimer_ns() - t0 < 200000000ull) {}
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================================ MMA issuer ================================
+        if (lane == 0) {
+            const uint32_t idesc_i8 = umma_idesc(2u, p.act_unsigned ? 0u : 1u, 1u, BN);
+            const uint32_t f16fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+            const uint32_t idesc_lr = umma_idesc(1u, f16fmt, f16fmt, BN);
+            uint32_t it = 0, ait = 0;
+            bool ok = true;
+            NB_PF_DECL
+            for (int t = t_begin; t < t_end && ok; ++t) {
+                for (int j = 0; j < GS && ok; ++j, ++it) {
+                    const int s = it % STAGES;
+                    NB_PF(7);
+                    if (!mbar_wait(bar(B_FULL + s), (it / STAGES) & 1, abort_s, E_MMA | 1, 100)) { ok = false; break; }
+                    NB_PF(0);
+                    const uint32_t a_addr = s_base + C::OFF_ST + s * C::ST_BYTES, w_addr = a_addr + C::ST_A;
+                    const int ng = min(2, G - 2 * j);
+                    for (int i = 0; i < ng; ++i, ++ait) {
+                        const int slot = ait % NSLOT;
+                        if (!mbar_wait(bar(B_ACC_EMPTY + slot), ((ait / NSLOT) & 1) ^ 1, abort_s, E_MMA | 2, 100)) { ok = false; break; }
+                        NB_PF(1);
+                        tc_fence_after();
+                        const uint32_t d = tmem_base + slot * BN;
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+                            mma_i8(d, umma_desc_sw128(a_addr + (2 * i + h) * 32), umma_desc_sw128(w_addr + (2 * i + h) * 32),
+                                   idesc_i8, h);
+                        tc_commit(bar(B_ACC_FULL + slot));
+                        NB_PF(2);
+                    }
+                    tc_commit(bar(B_EMPTY + s));
+                }
+                if (ok && LCH > 0) {
+                    const int slot = ait % NSLOT;
+                    if (!mbar_wait(bar(B_ACC_EMPTY + slot), ((ait / NSLOT) & 1) ^ 1, abort_s, E_MMA | 3, 100)) { ok = false; break; }
+                    for (int c = 0; c < LCH && ok; ++c, ++it) {
+                        const int s = it % STAGES;
+                        if (!mbar_wait(bar(B_FULL + s), (it / STAGES) & 1, abort_s, E_MMA | 4, 100)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t a_addr = s_base + C::OFF_ST + s * C::ST_BYTES, w_addr = a_addr + C::ST_A;
+                        const uint32_t d = tmem_base + slot * BN;
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+                            mma_f16(d, umma_desc_sw64(a_addr + h * 32), umma_desc_sw64(w_addr + h * 32), idesc_lr, (c | h) ? 1u : 0u);
+                        tc_commit(bar(B_EMPTY + s));
+                    }
+                    if (ok) { tc_commit(bar(B_ACC_FULL + slot)); ++ait; }
+                    NB_PF(3);
+                }
+            }
+            NB_PF_DUMP();
         }
     } else {
         // ================================ drain + epilogue ================================
         // A warp owns 32 rows (its TMEM lane quarter) x 64 columns.  tcgen05.ld.16x256b.x8 hands a thread, for one
         // 16-lane block, rows {gid, gid + 8} and the column pairs 8 j + 2 tig + {0, 1}, j = 0..7: register
-        // 4 j + 2 rs + e.  The two 16-lane blocks of a group are two "chunks"; while one is scaled the load of the
-        // next chunk (of this group or, when the tensor pipe is ahead, of the next group) is in flight.
-        setmaxnreg_inc_176();
-        const int dw = warp - 8;
-        const int q = dw & 3;       // TMEM lane quarter this warp may read
+        // 4 j + 2 rs + e.
+        const int dw = warp - 2;
+        const int q = warp & 3;     // TMEM lane quarter this warp may read (warp id mod 4)
         const int half = dw >> 2;   // column half of the tile
+        const int pw = half * 4 + q;             // index used for staging / exchange buffers
         const int gid = lane >> 2, tig = lane & 3;
-        uint8_t* stg = smem + C::OFF_STG + dw * 32 * C::STG_PITCH;
+        uint8_t* stg = smem + C::OFF_STG + pw * 32 * C::STG_PITCH;
         float* xch = reinterpret_cast<float*>(smem + C::OFF_XCH);
         const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16) + half * COLS;
-        uint32_t ait = 0, sit = 0, xph = 0;
+        uint32_t it = 0, ait = 0, xph = 0;
         bool ok = true;
-        uint64_t acc[32];  // [chunk lb][j][row select] pairs of fp32
+        uint64_t acc[32];  // [lane block lb][j][row select] pairs of fp32
         uint32_t v[2][32];
+        NB_PF_DECL
 
         for (int t = t_begin; t < t_end && ok; ++t) {
             const int m0 = (t / NT) * BM, n0 = (t % NT) * BN;
             const int nc0 = n0 + half * COLS;  // first global column of this warp
 #pragma unroll
             for (int i = 0; i < 32; ++i) acc[i] = 0ull;
-            const int nsteps = G + (LCH > 0 ? 1 : 0);
 
-            // chunk 0 of the tile's first group
-            if (!mbar_wait(bar(B_ACC_FULL + ait % NSLOT), (ait / NSLOT) & 1, abort_s, E_DRAIN | 1)) { ok = false; break; }
-            tc_fence_after();
-            tmem_ld_16x256b_x8(lane_base + (ait % NSLOT) * BN, v[0]);
-
-            for (int g = 0; g < nsteps; ++g, ++ait) {
-                const bool lowrank = g >= G;
-                const int slot = ait % NSLOT;
-                const int c = sit % SC_STAGES;
-                if (dw == 0 && lane == 0) NB_TR(ait, 6);
-                if (!lowrank && !mbar_wait(bar(B_SC_FULL + c), (sit / SC_STAGES) & 1, abort_s, E_DRAIN | 2)) { ok = false; break; }
-                if (dw == 0 && lane == 0) NB_TR(ait, 7);
-                const float* sc_f = reinterpret_cast<const float*>(smem + C::OFF_SC + c * C::SC_BYTES);
-                const float4* ws4 = reinterpret_cast<const float4*>(sc_f + half * COLS) + tig;
-                bool prefetched = false;
+            for (int j = 0; j < GS && ok; ++j, ++it) {
+                const int s = it % STAGES;
+                const uint8_t* st = smem + C::OFF_ST + s * C::ST_BYTES;
+                const int ng = min(2, G - 2 * j);
+                for (int i = 0; i < ng; ++i, ++ait) {
+                    const int slot = ait % NSLOT;
+                    NB_PF(7);
+                    if (!mbar_wait_warp(bar(B_ACC_FULL + slot), (ait / NSLOT) & 1, abort_s, E_DRAIN | 1, 100)) { ok = false; break; }
+                    NB_PF(0);
+                    tc_fence_after();
+                    tmem_ld_16x256b_x8(lane_base + slot * BN, v[0]);
+                    tmem_ld_16x256b_x8(lane_base + (16u << 16) + slot * BN, v[1]);
+                    // scales of this group while the loads are in flight
+                    const float2* as_s = reinterpret_cast<const float2*>(st + C::ST_A + C::ST_W) + i * BM + q * 32 + gid;
+                    const ulonglong2* ws_s = reinterpret_cast<const ulonglong2*>(st + C::ST_A + C::ST_W + C::ST_AS + i * BN * 4 + half * COLS * 4) + tig;
+                    uint64_t as2[4], cm2[4];
 #pragma unroll
-                for (int lb = 0; lb < 2; ++lb) {
-                    tmem_wait_ld();  // chunk lb of this group is in v[lb]
-                    if (dw == 0 && lane == 0) NB_TR(ait, 9 + 3 * lb);
-                    if (lb == 0) {
-                        tmem_ld_16x256b_x8(lane_base + (16u << 16) + slot * BN, v[1]);
-                    } else {
-                        // both chunks of the slot are in registers: hand it back, then start on the next group if
-                        // its accumulator is already complete
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + slot));
-                        if (g + 1 < nsteps) {
-                            const uint32_t nx = ait + 1;
-                            prefetched = mbar_try_wait(bar(B_ACC_FULL + nx % NSLOT), (nx / NSLOT) & 1);
-                            if (prefetched) {
-                                tc_fence_after();
-                                tmem_ld_16x256b_x8(lane_base + (nx % NSLOT) * BN, v[0]);
-                            }
-                        }
+                    for (int r = 0; r < 4; ++r) {
+                        const float2 ac = as_s[r * 8];  // rows gid, gid + 8, gid + 16, gid + 24
+                        as2[r] = pack_f32x2(ac.x, ac.x);
+                        cm2[r] = pack_f32x2(ac.y, ac.y);
                     }
-                    if (dw == 0 && lane == 0) NB_TR(ait, 10 + 3 * lb);
-                    uint32_t(&vv)[32] = v[lb];
-#ifdef NB_EXP_NOMATH
-                    if (false) {
-#else
-                    if (!lowrank) {
-#endif
-                        uint64_t as2[2], cm2[2];
+                    ulonglong2 w[4];
 #pragma unroll
-                        for (int rs = 0; rs < 2; ++rs) {
-                            const int row = q * 32 + lb * 16 + rs * 8 + gid;
-                            as2[rs] = pack_f32x2(sc_f[BN + row], sc_f[BN + row]);
-                            cm2[rs] = pack_f32x2(sc_f[BN + BM + row], sc_f[BN + BM + row]);
-                        }
+                    for (int jj = 0; jj < 4; ++jj) w[jj] = ws_s[jj * 4];
+                    NB_PF(1);
+                    tmem_wait_ld();
+                    NB_PF(2);
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + slot));
+                    NB_PF(3);
 #pragma unroll
-                        for (int j = 0; j < 8; j += 2) {
-                            const float4 w = ws4[(j >> 1) * 4];
-                            const uint64_t w0 = pack_f32x2(w.x, w.y), w1 = pack_f32x2(w.z, w.w);
+                    for (int lb = 0; lb < 2; ++lb) {
+                        uint32_t(&vv)[32] = v[lb];
 #pragma unroll
-                            for (int jj = 0; jj < 2; ++jj) {
+                        for (int jx = 0; jx < 8; ++jx) {
+                            const uint64_t wj = (jx & 1) ? w[jx >> 1].y : w[jx >> 1].x;
 #pragma unroll
-                                for (int rs = 0; rs < 2; ++rs) {
-                                    const int vi = 4 * (j + jj) + 2 * rs;
-                                    const uint64_t x = pack_u32x2(vv[vi] + MAGIC_BITS, vv[vi + 1] + MAGIC_BITS);
-                                    const uint64_t tt = fma_f32x2(x, as2[rs], cm2[rs]);
-                                    uint64_t& a = acc[(lb * 8 + j + jj) * 2 + rs];
-                                    a = fma_f32x2(tt, jj ? w1 : w0, a);
-                                }
+                            for (int rs = 0; rs < 2; ++rs) {
+                                const int vi = 4 * jx + 2 * rs;
+                                const uint64_t x = pack_u32x2(vv[vi] + MAGIC_BITS, vv[vi + 1] + MAGIC_BITS);
+                                const uint64_t tt = fma_f32x2(x, as2[lb * 2 + rs], cm2[lb * 2 + rs]);
+                                uint64_t& a = acc[(lb * 8 + jx) * 2 + rs];
+                                a = fma_f32x2(tt, wj, a);
                             }
                         }
                         if (DEBUG_P) {
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                const int m = m0 + q * 32 + lb * 16 + ((i >> 1) & 1) * 8 + gid;
-                                const int n = nc0 + (i >> 2) * 8 + 2 * tig + (i & 1);
-                                if (m < p.M && n < p.N) p.p_out[((long long)g * p.M + m) * p.N + n] = ((int)vv[i]) >> 8;
+                            for (int e = 0; e < 32; ++e) {
+                                const int m = m0 + q * 32 + lb * 16 + ((e >> 1) & 1) * 8 + gid;
+                                const int n = nc0 + (e >> 2) * 8 + 2 * tig + (e & 1);
+                                if (m < p.M && n < p.N) p.p_out[((long long)(2 * j + i) * p.M + m) * p.N + n] = ((int)vv[e]) >> 8;
                             }
                         }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-#pragma unroll
-                            for (int rs = 0; rs < 2; ++rs) {
-                                uint64_t& a = acc[(lb * 8 + j) * 2 + rs];
-                                a = add_f32x2(a, pack_u32x2(vv[4 * j + 2 * rs], vv[4 * j + 2 * rs + 1]));
-                            }
                     }
                 }
-                if (!lowrank) {
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(B_SC_EMPTY + c));
-                    ++sit;
-                }
-                if (g + 1 < nsteps && !prefetched) {
-                    const uint32_t nx = ait + 1;
-                    if (!mbar_wait(bar(B_ACC_FULL + nx % NSLOT), (nx / NSLOT) & 1, abort_s, E_DRAIN | 3)) { ok = false; break; }
-                    tc_fence_after();
-                    tmem_ld_16x256b_x8(lane_base + (nx % NSLOT) * BN, v[0]);
-                }
-                if (dw == 0 && lane == 0) NB_TR(ait, 8);
+                if (!ok) break;
+                NB_PF(4);
+                // this warp has read the stage's scales
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(B_SCDONE + s));
+                NB_PF(5);
             }
             if (!ok) break;
+            if (LCH > 0) {
+                const int slot = ait % NSLOT;
+                if (!mbar_wait_warp(bar(B_ACC_FULL + slot), (ait / NSLOT) & 1, abort_s, E_DRAIN | 3, 100)) { ok = false; break; }
+                tc_fence_after();
+                tmem_ld_16x256b_x8(lane_base + slot * BN, v[0]);
+                tmem_ld_16x256b_x8(lane_base + (16u << 16) + slot * BN, v[1]);
+                tmem_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + slot));
+                it += LCH;  // the low-rank stages carry nothing for the drain
+                ++ait;
+#pragma unroll
+                for (int lb = 0; lb < 2; ++lb)
+#pragma unroll
+                    for (int jx = 0; jx < 8; ++jx)
+#pragma unroll
+                        for (int rs = 0; rs < 2; ++rs) {
+                            uint64_t& a = acc[(lb * 8 + jx) * 2 + rs];
+                            a = add_f32x2(a, pack_u32x2(v[lb][4 * jx + 2 * rs], v[lb][4 * jx + 2 * rs + 1]));
+                        }
+            }
 
             // ---------------- epilogue: bias, optional RMSNorm + RoPE, rounding, staged store ----------------
             // element (lb, j, rs, e): row q*32 + lb*16 + rs*8 + gid, column nc0 + 8j + 2 tig + e
@@ -498,7 +408,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 }
             if (EPI == NB_EPI_QK_NORM_ROPE) {
                 // the 128-column tile is one head: the 4 lanes of a quad share a row inside the warp, and the
-                // warp that owns the other 64 columns of the same rows is dw ^ 4
+                // warp that owns the other 64 columns of the same rows is the one with the other `half`
                 const int part = n0 / (p.N / 3);
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
@@ -506,17 +416,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     s += __shfl_xor_sync(0xffffffffu, s, 1);
                     s += __shfl_xor_sync(0xffffffffu, s, 2);
                     sumsq[r] = s;
-                    if (tig == 0) xch[dw * 32 + (r >> 1) * 16 + (r & 1) * 8 + gid] = s;
+                    if (tig == 0) xch[pw * 32 + (r >> 1) * 16 + (r & 1) * 8 + gid] = s;
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_XCH + q));
-                if (!mbar_wait(bar(B_XCH + q), xph & 1, abort_s, E_DRAIN | 4)) { ok = false; break; }
+                if (!mbar_wait_warp(bar(B_XCH + q), xph & 1, abort_s, E_DRAIN | 4, 100)) { ok = false; break; }
                 ++xph;
                 if (part < 2) {
                     float rstd[4];
 #pragma unroll
                     for (int r = 0; r < 4; ++r)
-                        rstd[r] = rsqrtf((sumsq[r] + xch[(dw ^ 4) * 32 + (r >> 1) * 16 + (r & 1) * 8 + gid]) / 128.0f + p.eps);
+                        rstd[r] = rsqrtf((sumsq[r] + xch[(pw ^ 4) * 32 + (r >> 1) * 16 + (r & 1) * 8 + gid]) / 128.0f + p.eps);
                     const T* wn = static_cast<const T*>(part == 0 ? p.norm_q : p.norm_k);
 #pragma unroll
                     for (int lb = 0; lb < 2; ++lb)
@@ -538,7 +448,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 // the partner must have read this warp's sums before the next tile overwrites them
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_XCH + q));
-                if (!mbar_wait(bar(B_XCH + q), xph & 1, abort_s, E_DRAIN | 5)) { ok = false; break; }
+                if (!mbar_wait_warp(bar(B_XCH + q), xph & 1, abort_s, E_DRAIN | 5, 100)) { ok = false; break; }
                 ++xph;
             }
             // round, transpose through the per-warp staging tile, store whole 128-byte row segments
@@ -566,7 +476,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         *reinterpret_cast<uint4*>(static_cast<T*>(p.out) + (long long)mm * p.stride_om + nn) = o;
                 }
             }
+            NB_PF(6);
         }
+        NB_PF_DUMP();
     }
 
     // ---------------- teardown ----------------
@@ -576,6 +488,73 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// pre-pass: nibbles -> int8 (16 * value), scales -> fp32 in drain order, lora_act -> T
+// ------------------------------------------------------------------------------------------------
+struct PrepackParams {
+    const uint8_t* act; const uint8_t* wgt;
+    const void* ascales; const void* wscales; const float* lora_act;
+    int8_t* a8; int8_t* w8; float* asf; float* wsf; void* la16;
+    int M, N, K, R, Np;  // Np: N rounded up to 128
+    long long stride_am, stride_wn, stride_asg, stride_wsg, stride_lam;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) prepack_kernel(const PrepackParams p) {
+    const long long tid = (long long)blockIdx.x * 256 + threadIdx.x;
+    const int upr = p.K / 32;  // 16-byte packed units per row
+    const long long a_units = (long long)p.M * upr, w_units = (long long)p.N * upr;
+    const int G = p.K / 64;
+    const long long as_units = (long long)G * p.M, ws_units = (long long)G * p.Np;
+    const long long la_units = p.R ? (long long)p.M * (p.R / 8) : 0;
+    if (tid < a_units + w_units) {
+        const bool is_w = tid >= a_units;
+        const long long u = is_w ? tid - a_units : tid;
+        const long long row = u / upr;
+        const int c = (int)(u % upr);
+        const uint8_t* src = (is_w ? p.wgt + row * p.stride_wn : p.act + row * p.stride_am) + c * 16;
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+        // per packed word: even-k nibbles then odd-k nibbles, each moved to the top of its byte
+        uint4 o0, o1;
+        o0.x = (v.x << 4) & 0xF0F0F0F0u; o0.y = v.x & 0xF0F0F0F0u; o0.z = (v.y << 4) & 0xF0F0F0F0u; o0.w = v.y & 0xF0F0F0F0u;
+        o1.x = (v.z << 4) & 0xF0F0F0F0u; o1.y = v.z & 0xF0F0F0F0u; o1.z = (v.w << 4) & 0xF0F0F0F0u; o1.w = v.w & 0xF0F0F0F0u;
+        uint4* dst = reinterpret_cast<uint4*>((is_w ? p.w8 : p.a8) + row * p.K + c * 32);
+        dst[0] = o0;
+        dst[1] = o1;
+        return;
+    }
+    long long u = tid - (a_units + w_units);
+    if (u < as_units) {
+        const int g = (int)(u / p.M), m = (int)(u % p.M);
+        const float a = to_f32<T>(static_cast<const T*>(p.ascales)[(long long)g * p.stride_asg + m]);
+        reinterpret_cast<float2*>(p.asf)[u] = make_float2(a, -MAGIC_F * a);
+        return;
+    }
+    u -= as_units;
+    if (u < ws_units) {
+        // column n of its 128-wide tile -> [tile][warp half][pair of 8-col blocks][tig][4]: one 128-bit load of a drain
+        // thread is (cols c, c+1 of block j, cols c, c+1 of block j+1)
+        const int g = (int)(u / p.Np), n = (int)(u % p.Np);
+        const float w = n < p.N ? to_f32<T>(static_cast<const T*>(p.wscales)[(long long)g * p.stride_wsg + n]) : 0.f;
+        const int tile = n / BN, i = n % BN;
+        const int hf = i / COLS, cc = i % COLS;
+        const int blk = cc >> 3, tg = (cc >> 1) & 3, e = cc & 1;
+        p.wsf[(long long)g * p.Np + tile * BN + hf * COLS + (blk >> 1) * 16 + tg * 4 + (blk & 1) * 2 + e] = w;
+        return;
+    }
+    u -= ws_units;
+    if (u < la_units) {
+        const int rpr = p.R / 8;
+        const long long m = u / rpr;
+        const int c = (int)(u % rpr);
+        const float4* src = reinterpret_cast<const float4*>(p.lora_act + m * p.stride_lam + c * 8);
+        const float4 x = __ldg(src), y = __ldg(src + 1);
+        uint4 o;
+        o.x = pack2<T>(x.x, x.y); o.y = pack2<T>(x.z, x.w); o.z = pack2<T>(y.x, y.y); o.w = pack2<T>(y.z, y.w);
+        reinterpret_cast<uint4*>(static_cast<T*>(p.la16) + m * p.R)[c] = o;
     }
 }
 
@@ -611,16 +590,62 @@ static bool make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, u
               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+static inline size_t up256(size_t x) { return (x + 255) & ~size_t(255); }
+
+struct Scratch {
+    size_t a8, w8, asf, wsf, la16, total;
+    int Np;
+};
+static Scratch scratch_layout(const nb_gemm_args* a) {
+    Scratch s;
+    const size_t G = a->K / 64;
+    s.Np = (a->N + BN - 1) / BN * BN;
+    size_t off = 0;
+    s.a8 = off; off += up256((size_t)a->M * a->K);
+    s.w8 = off; off += up256((size_t)a->N * a->K);
+    s.asf = off; off += up256(G * a->M * 8);
+    s.wsf = off; off += up256(G * s.Np * 4);
+    s.la16 = off; off += up256((size_t)a->M * a->R * 2);
+    s.total = off;
+    return s;
+}
+
 template <int EPI, typename T, bool DEBUG_P>
 static int launch_t(const nb_gemm_args* a, const TcParams& p, cudaStream_t s) {
     using C = Cfg;
-    CUtensorMap tm_a, tm_w, tm_as, tm_ws;
-    const CUtensorMapDataType sdt = CU_TENSOR_MAP_DATA_TYPE_UINT16;  // scales move as opaque 16-bit words
-    if (!make_map(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->act, a->K / 2, a->M, a->stride_am, 32, BM, CU_TENSOR_MAP_SWIZZLE_32B) ||
-        !make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->wgt, a->K / 2, a->N, a->stride_wn, 32, BN, CU_TENSOR_MAP_SWIZZLE_32B) ||
-        !make_map(&tm_as, sdt, a->ascales, a->M, a->K / 64, a->stride_asg * 2, BM, 1, CU_TENSOR_MAP_SWIZZLE_NONE) ||
-        !make_map(&tm_ws, sdt, a->wscales, a->N, a->K / 64, a->stride_wsg * 2, BN, 1, CU_TENSOR_MAP_SWIZZLE_NONE))
-        return NB_ERR_UNSUPPORTED;
+    const Scratch sc = scratch_layout(a);
+    if (!a->scratch || a->scratch_bytes < (int64_t)sc.total || (reinterpret_cast<uintptr_t>(a->scratch) & 255))
+        return NB_ERR_INVALID;
+    uint8_t* base = static_cast<uint8_t*>(a->scratch);
+    PrepackParams pp;
+    pp.act = static_cast<const uint8_t*>(a->act); pp.wgt = static_cast<const uint8_t*>(a->wgt);
+    pp.ascales = a->ascales; pp.wscales = a->wscales; pp.lora_act = static_cast<const float*>(a->lora_act);
+    pp.a8 = reinterpret_cast<int8_t*>(base + sc.a8); pp.w8 = reinterpret_cast<int8_t*>(base + sc.w8);
+    pp.asf = reinterpret_cast<float*>(base + sc.asf); pp.wsf = reinterpret_cast<float*>(base + sc.wsf);
+    pp.la16 = base + sc.la16;
+    pp.M = a->M; pp.N = a->N; pp.K = a->K; pp.R = a->R; pp.Np = sc.Np;
+    pp.stride_am = a->stride_am; pp.stride_wn = a->stride_wn; pp.stride_asg = a->stride_asg;
+    pp.stride_wsg = a->stride_wsg; pp.stride_lam = a->stride_lam;
+    const long long G = a->K / 64;
+    const long long units = (long long)(a->M + a->N) * (a->K / 32) + G * a->M + G * sc.Np +
+                            (a->R ? (long long)a->M * (a->R / 8) : 0);
+    prepack_kernel<T><<<(unsigned)((units + 255) / 256), 256, 0, s>>>(pp);
+    NB_CUDA_CHECK(cudaGetLastError());
+
+    CUtensorMap tm_a, tm_w, tm_as, tm_ws, tm_la, tm_lu;
+    const CUtensorMapDataType t16 = std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                          : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    bool ok = make_map(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, pp.a8, a->K, a->M, a->K, 128, BM, CU_TENSOR_MAP_SWIZZLE_128B) &&
+              make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, pp.w8, a->K, a->N, a->K, 128, BN, CU_TENSOR_MAP_SWIZZLE_128B) &&
+              make_map(&tm_as, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, pp.asf, (uint64_t)a->M * 2, G, (uint64_t)a->M * 8, 2 * BM, 2,
+                       CU_TENSOR_MAP_SWIZZLE_NONE) &&
+              make_map(&tm_ws, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, pp.wsf, sc.Np, G, (uint64_t)sc.Np * 4, BN, 2,
+                       CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (ok && a->R > 0)
+        ok = make_map(&tm_la, t16, pp.la16, a->R, a->M, (uint64_t)a->R * 2, 32, BM, CU_TENSOR_MAP_SWIZZLE_64B) &&
+             make_map(&tm_lu, t16, a->lora_up, a->R, a->N, (uint64_t)a->stride_lun * 2, 32, BN, CU_TENSOR_MAP_SWIZZLE_64B);
+    else if (ok) { tm_la = tm_a; tm_lu = tm_w; }
+    if (!ok) return NB_ERR_UNSUPPORTED;
     int dev = 0, sms = 0;
     NB_CUDA_CHECK(cudaGetDevice(&dev));
     NB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -628,17 +653,17 @@ static int launch_t(const nb_gemm_args* a, const TcParams& p, cudaStream_t s) {
     const int grid = total < sms ? total : sms;
     auto kern = gemm_tc_kernel<EPI, T, DEBUG_P>;
     NB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    kern<<<grid, NTHREADS, C::SMEM_BYTES, s>>>(tm_a, tm_w, tm_as, tm_ws, p);
+    kern<<<grid, NTHREADS, C::SMEM_BYTES, s>>>(tm_a, tm_w, tm_as, tm_ws, tm_la, tm_lu, p);
     NB_CUDA_CHECK(cudaGetLastError());
     return NB_OK;
 }
 
 }  // namespace tc
 
-#ifdef NB_TRACE
-extern "C" int nb_debug_set_trace(void* ptr) {
+#ifdef NB_PROF
+extern "C" int nb_debug_set_prof(void* ptr) {
     unsigned long long* v = static_cast<unsigned long long*>(ptr);
-    return cudaMemcpyToSymbol(tc::g_trace, &v, sizeof(v)) == cudaSuccess ? 0 : 3;
+    return cudaMemcpyToSymbol(tc::g_prof, &v, sizeof(v)) == cudaSuccess ? 0 : 3;
 }
 #endif
 
@@ -650,7 +675,6 @@ const char* tc_unsupported_reason(const nb_gemm_args* a, const void* epi, int ep
     if (epi_kind != NB_EPI_STORE && epi_kind != NB_EPI_QK_NORM_ROPE) return "epilogue";
     if (a->K % 64 || a->N % 8 || a->M < 1) return "K % 64, N % 8";
     if (!aligned16(a->act) || !aligned16(a->wgt) || a->stride_am % 16 || a->stride_wn % 16) return "act / wgt alignment";
-    if (!aligned16(a->ascales) || !aligned16(a->wscales) || a->stride_asg % 8 || a->stride_wsg % 8) return "scale alignment";
     if (a->out && (!aligned16(a->out) || a->stride_om % 8)) return "out alignment";
     if (!a->out) return "no 16-bit output";
     if (a->bias && (reinterpret_cast<uintptr_t>(a->bias) & 3)) return "bias alignment";
@@ -668,13 +692,15 @@ const char* tc_unsupported_reason(const nb_gemm_args* a, const void* epi, int ep
     return nullptr;
 }
 
+int64_t tc_scratch_bytes(const nb_gemm_args* a) { return (int64_t)tc::scratch_layout(a).total; }
+
 int launch_tc(const nb_gemm_args* a, const void* epi, int epi_kind, int32_t* p_out, cudaStream_t s) {
     tc::TcParams p = {};
-    p.out = a->out; p.bias = a->bias; p.lora_act = static_cast<const float*>(a->lora_act); p.lora_up = a->lora_up;
+    p.out = a->out; p.bias = a->bias;
     p.p_out = p_out;
     p.M = a->M; p.N = a->N; p.K = a->K; p.actual_m = a->actual_m; p.R = a->R;
     p.act_unsigned = a->act_unsigned;
-    p.stride_om = a->stride_om; p.stride_lam = a->stride_lam; p.stride_lun = a->stride_lun;
+    p.stride_om = a->stride_om;
     p.status = static_cast<int*>(a->status);
     if (epi_kind == NB_EPI_QK_NORM_ROPE) {
         const nb_qk_args* q = static_cast<const nb_qk_args*>(epi);

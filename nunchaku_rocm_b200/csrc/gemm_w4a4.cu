@@ -27,6 +27,7 @@ int launch_qk_rows(const float* src_f, void* out, long long stride_om, int M, in
 int launch_requant_rows(const float* lin, int M, int N, int mode, int dtype, const nb_requant_args* q, cudaStream_t s);
 const char* tc_unsupported_reason(const nb_gemm_args* a, const void* epi, int epi_kind);
 int launch_tc(const nb_gemm_args* a, const void* epi, int epi_kind, int32_t* p_out, cudaStream_t s);
+int64_t tc_scratch_bytes(const nb_gemm_args* a);
 
 static int validate(const nb_gemm_args* a, const void* epi, int epi_kind) {
     NB_REQUIRE(a && a->act && a->wgt && a->ascales && a->wscales);
@@ -52,10 +53,15 @@ static int validate(const nb_gemm_args* a, const void* epi, int epi_kind) {
     return NB_OK;
 }
 
-static bool needs_scratch(const nb_gemm_args* a, const void* epi, int epi_kind) {
-    if (epi_kind == NB_EPI_STORE) return false;
-    if (a->impl == NB_IMPL_GENERIC) return true;
-    return tc_unsupported_reason(a, epi, epi_kind) != nullptr;
+static bool uses_tc(const nb_gemm_args* a, const void* epi, int epi_kind) {
+    return a->impl != NB_IMPL_GENERIC && tc_unsupported_reason(a, epi, epi_kind) == nullptr;
+}
+
+// The tensor-core kernel keeps its pre-widened operands and fp32 scales in scratch; the generic kernel keeps the
+// fp32 tile there when a row-wise epilogue follows.
+static int64_t scratch_bytes(const nb_gemm_args* a, const void* epi, int epi_kind) {
+    if (uses_tc(a, epi, epi_kind)) return tc_scratch_bytes(a);
+    return epi_kind == NB_EPI_STORE ? 0 : (int64_t)a->M * a->N * 4;
 }
 
 static GenericParams to_generic(const nb_gemm_args* a) {
@@ -74,7 +80,8 @@ static GenericParams to_generic(const nb_gemm_args* a) {
 
 extern "C" int64_t nb_gemm_w4a4_scratch_bytes(const nb_gemm_args* a, const void* epi, int epi_kind) {
     if (!a || nb::validate(a, epi, epi_kind) != NB_OK) return 0;
-    return nb::needs_scratch(a, epi, epi_kind) ? (int64_t)a->M * a->N * 4 : 0;
+    if (a->M == 0) return 0;
+    return nb::scratch_bytes(a, epi, epi_kind);
 }
 
 extern "C" int nb_gemm_w4a4(const nb_gemm_args* a, const void* epi, int epi_kind, void* stream) {
@@ -102,6 +109,11 @@ extern "C" int nb_gemm_w4a4(const nb_gemm_args* a, const void* epi, int epi_kind
                               static_cast<const nb_qk_args*>(epi), s);
     return launch_requant_rows(p.acc_out, a->M, a->N, epi_kind == NB_EPI_GELU_QUANT ? 0 : 1, a->dtype,
                                static_cast<const nb_requant_args*>(epi), s);
+}
+
+extern "C" int64_t nb_gemm_w4a4_uses_tcgen05(const nb_gemm_args* a, const void* epi, int epi_kind) {
+    if (!a || nb::validate(a, epi, epi_kind) != NB_OK) return 0;
+    return nb::uses_tc(a, epi, epi_kind) ? 1 : 0;
 }
 
 extern "C" int nb_gemm_w4a4_group_sums(const nb_gemm_args* a, int32_t* p_out, void* stream) {

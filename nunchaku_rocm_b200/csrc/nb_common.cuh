@@ -136,6 +136,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// try_wait that lets the hardware park the thread for up to `hint_ns` before it reports "not yet"
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -143,16 +155,15 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 }
 // Bounded wait: gives up after ~2 s (or as soon as another thread of the CTA has given up), records
 // `code` in *abort_flag and returns false.  The caller must then unwind without touching the data.
-// Between polls the thread sleeps `backoff_ns`, so that warps waiting on a full pipeline do not take issue
-// slots and shared-memory bandwidth from the warps that are working.
+// Every poll is one operation on the shared-memory barrier unit, which all warps of the CTA share, so a
+// waiter parks in the hardware (`hint_ns`) instead of polling in a tight loop.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
-                                          unsigned backoff_ns = 32) {
+                                          unsigned hint_ns = 200) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = 0;
     for (uint32_t spin = 1;; ++spin) {
-        __nanosleep(backoff_ns);
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 255u) == 0) {
+        if (mbar_try_wait_hint(bar, parity, hint_ns)) return true;
+        if ((spin & 63u) == 0) {
             if (*abort_flag) return false;
             uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;
@@ -162,6 +173,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             }
         }
     }
+}
+// The same wait done by lane 0 for its warp (one poller per warp); every lane gets the verdict.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                               unsigned hint_ns = 200) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, code, hint_ns) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

@@ -312,7 +312,7 @@ def gemm_w4a4(
         a = _gemm_args(act, wgt, out2d, ascales, wscales, bias, la, lu, None, act_unsigned, False, False, 1.0, dtype, _impl)
         qout2d = qout.reshape(-1, qout.shape[-1])
         q = _requant_args(qout2d, oscales, smooth_factor, lora_down, lora_act_out, GELU_SHIFT, N, M, dtype)
-        fused_fast = L.lib().nb_gemm_w4a4_scratch_bytes(C.byref(a), C.byref(q), L.EPI_GELU_QUANT) == 0
+        fused_fast = L.lib().nb_gemm_w4a4_uses_tcgen05(C.byref(a), C.byref(q), L.EPI_GELU_QUANT) == 1
         if fused_fast or _impl == L.IMPL_GENERIC:
             _run(a, C.byref(q), L.EPI_GELU_QUANT, act)
             return out
@@ -386,6 +386,9 @@ def gemm_w4a4_group_sums(act, wgt, act_unsigned: bool = False, _impl: int = L.IM
     p = torch.empty(K // 64, M, N, dtype=torch.int32, device=dev)
     a = _gemm_args(act, wgt, out, ones_a, ones_w, None, None, None, None, act_unsigned, False, False, 1.0,
                    torch.bfloat16, _impl)
+    need = L.lib().nb_gemm_w4a4_scratch_bytes(C.byref(a), None, L.EPI_STORE)
+    scratch = torch.empty(max(need, 1), dtype=torch.uint8, device=dev)
+    a.scratch, a.scratch_bytes = L.ptr(scratch), need
     with torch.cuda.device(dev):
         L.check(L.lib().nb_gemm_w4a4_group_sums(C.byref(a), L.ptr(p), L.stream_of(act)), "gemm_w4a4_group_sums")
     return p

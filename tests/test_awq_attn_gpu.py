@@ -1,0 +1,118 @@
+"""
+GPU parity tests of the AWQ W4A16 operators and the attention operator against the CPU oracle, with the bars of
+the reference's own tests (tests/triton/test_gemm.py:98-159: exact dequantisation round trip, rtol/atol 3e-2 for the
+GEMV / GEMM; tests/triton/test_w4a4.py:241-254: rtol/atol 3e-2 for attention).
+"""
+
+import pytest
+import torch
+
+from oracle import awq_attn
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.bfloat16, torch.float16]
+
+
+def _awq_problem(n, k, m, dtype, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randint(0, 16, (n, k), dtype=torch.int32, generator=g)
+    s = (torch.rand(k // 64, n, generator=g) * 0.1 + 0.01).to(dtype)
+    z = (torch.randn(k // 64, n, generator=g) * 0.1).to(dtype)
+    x = torch.randn(m, k, generator=g).to(dtype)
+    return q, awq_attn.awq_pack(q), s, z, x
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,k", [(64, 128), (256, 3072), (72, 192)])
+def test_awq_dequantize_exact(cuda_dev, dtype, n, k):
+    from nunchaku_rocm_b200.ops.triton.awq import awq_dequantize
+
+    q, packed, s, z, _ = _awq_problem(n, k, 1, dtype, seed=n)
+    w = awq_dequantize(packed.to(cuda_dev), s.to(cuda_dev), z.to(cuda_dev), n, k, 64, dtype)
+    ref = awq_attn.awq_dequant(packed, s, z, n, k).to(dtype)
+    assert torch.equal(w.cpu(), ref)
+    # unit scale, zero offset: the codes come back exactly
+    ones, zeros = torch.ones_like(s), torch.zeros_like(z)
+    w = awq_dequantize(packed.to(cuda_dev), ones.to(cuda_dev), zeros.to(cuda_dev), n, k, 64, dtype)
+    assert torch.equal(w.cpu().to(torch.int32), q)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m", [1, 2, 3, 8, 11])
+@pytest.mark.parametrize("n,k", [(256, 512), (18432, 3072)])
+def test_awq_gemv(cuda_dev, dtype, m, n, k):
+    from nunchaku_rocm_b200.ops.gemv import awq_gemv_w4a16_cuda
+
+    _, packed, s, z, x = _awq_problem(n, k, m, dtype, seed=m + n)
+    out = awq_gemv_w4a16_cuda(x.to(cuda_dev), packed.to(cuda_dev), s.to(cuda_dev), z.to(cuda_dev), m, n, k, 64)
+    assert out.shape == (m, n) and out.dtype == dtype
+    ref = awq_attn.awq_gemv(x, packed, s, z, n, k)
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=3e-2, atol=3e-2)
+    # tighter: within two 16-bit rounding steps of the fp32 sum
+    eps = 2.0**-7 if dtype == torch.bfloat16 else 2.0**-10
+    assert ((out.float().cpu() - ref).abs() <= eps * ref.abs() + 2e-2).all()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_awq_gemm_and_linear(cuda_dev, dtype):
+    from nunchaku_rocm_b200.models.linear import AWQW4A16Linear
+    from nunchaku_rocm_b200.ops.dispatch import gemm_awq
+
+    n, k, m = 384, 256, 40
+    g = torch.Generator().manual_seed(5)
+    q = torch.randint(0, 16, (n, k), dtype=torch.int32, generator=g)
+    s128 = (torch.rand(k // 128, n, generator=g) * 0.1 + 0.01).to(dtype)
+    z128 = (torch.randn(k // 128, n, generator=g) * 0.1).to(dtype)
+    x = torch.randn(m, k, generator=g).to(dtype)
+    packed = awq_attn.awq_pack(q)
+    out = gemm_awq(x.to(cuda_dev), packed.to(cuda_dev), s128.to(cuda_dev), z128.to(cuda_dev))
+    ref = x.float() @ awq_attn.awq_dequant(packed, s128, z128, n, k, 128).T
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=3e-2, atol=3e-2)
+
+    lin = AWQW4A16Linear(k, n, bias=True, group_size=64, torch_dtype=dtype, device=cuda_dev)
+    _, packed, s, z, x = _awq_problem(n, k, 4, dtype, seed=9)
+    bias = torch.randn(n, generator=g).to(dtype)
+    lin.qweight.data.copy_(packed)
+    lin.wscales.data.copy_(s)
+    lin.wzeros.data.copy_(z)
+    lin.bias.data.copy_(bias)
+    y = lin(x.to(cuda_dev))
+    ref = awq_attn.awq_gemv(x, packed, s, z, n, k).to(dtype).float() + bias.float()
+    torch.testing.assert_close(y.float().cpu(), ref, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize(
+    "B,H,TQ,TKV,D", [(2, 8, 256, 256, 64), (1, 4, 128, 512, 128), (2, 2, 100, 77, 64), (1, 3, 333, 1000, 128)]
+)
+def test_attention(cuda_dev, dtype, B, H, TQ, TKV, D):
+    from nunchaku_rocm_b200.ops.triton.attention import attention_fp16
+
+    g = torch.Generator().manual_seed(TQ)
+    q = torch.randn(B, H, TQ, D, generator=g).to(dtype)
+    k = torch.randn(B, H, TKV, D, generator=g).to(dtype)
+    v = torch.randn(B, H, TKV, D, generator=g).to(dtype)
+    o = torch.empty(B, TQ, H * D, dtype=dtype, device=cuda_dev)
+    attention_fp16(q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev), o, D**-0.5)
+    torch.testing.assert_close(o.float().cpu(), awq_attn.attention_exact(q, k, v, D**-0.5), rtol=3e-2, atol=3e-2)
+    # against the oracle with the kernel's rounding points: one 16-bit rounding step
+    eps = 2.0**-7 if dtype == torch.bfloat16 else 2.0**-10
+    torch.testing.assert_close(o.float().cpu(), awq_attn.attention(q, k, v, D**-0.5), rtol=2 * eps, atol=2 * eps)
+
+
+def test_sdpa_wrapper_strided_views_and_fallback(cuda_dev):
+    # (B, S, 3 * H * D) fused projection viewed as q, k, v, the way the FLUX processor slices it
+    from nunchaku_rocm_b200.ops.dispatch import scaled_dot_product_attention
+
+    B, S, H, D = 2, 300, 4, 128
+    torch.manual_seed(0)
+    qkv = torch.randn(B, S, 3 * H * D, dtype=torch.bfloat16, device=cuda_dev)
+    q, k, v = (t.view(B, S, H, D).transpose(1, 2) for t in qkv.chunk(3, dim=-1))
+    out = scaled_dot_product_attention(q, k, v)
+    assert out.shape == (B, H, S, D)
+    ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float())
+    torch.testing.assert_close(out.float(), ref, rtol=3e-2, atol=3e-2)
+    # a mask goes to torch
+    mask = torch.ones(S, S, dtype=torch.bool, device=cuda_dev)
+    out2 = scaled_dot_product_attention(q, k, v, attn_mask=mask)
+    torch.testing.assert_close(out2.float(), ref, rtol=3e-2, atol=3e-2)
