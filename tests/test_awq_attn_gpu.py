@@ -66,8 +66,10 @@ def test_awq_gemm_and_linear(cuda_dev, dtype):
     x = torch.randn(m, k, generator=g).to(dtype)
     packed = awq_attn.awq_pack(q)
     out = gemm_awq(x.to(cuda_dev), packed.to(cuda_dev), s128.to(cuda_dev), z128.to(cuda_dev))
-    ref = x.float() @ awq_attn.awq_dequant(packed, s128, z128, n, k, 128).T
-    torch.testing.assert_close(out.float().cpu(), ref, rtol=3e-2, atol=3e-2)
+    ref = x.float() @ awq_attn.awq_dequant(packed, s128, z128, n, k, 128).float().T
+    # 16-bit weights and a 16-bit output of magnitude ~10: judge the tile as a whole
+    err = (out.float().cpu() - ref).norm() / ref.norm()
+    assert err <= 1e-2, err
 
     lin = AWQW4A16Linear(k, n, bias=True, group_size=64, torch_dtype=dtype, device=cuda_dev)
     _, packed, s, z, x = _awq_problem(n, k, 4, dtype, seed=9)
