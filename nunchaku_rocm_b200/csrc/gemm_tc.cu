@@ -6,14 +6,12 @@
 // then + T(lora_act) . lora_up^T (16-bit operands, fp32 accumulate), + bias, one rounding to T.
 //
 // Two launches per call:
-//  1. `prepack_kernel` (HBM-bound, a few microseconds): packed nibbles -> int8 rows holding 16 * value
-//     (n << 4 keeps the sign in the top bit; the factor 256 on a product is undone by the magic constant
-//     of the drain), with the same permutation of k inside every 8-element run for activations and
-//     weights, which a dot product does not see; scales -> fp32 in the order the drain reads them;
-//     lora_act -> T.  Measured on B200: widening inside the GEMM through shared memory costs a
-//     generic->async proxy fence of ~3000 cycles per K group and competes with the drain for issue slots and
-//     shared-memory bandwidth; with the operands pre-widened every byte the tensor core reads is written by
-//     TMA and the SM's CUDA cores only do the per-group scaling.
+//  1. `prepack_kernel` (HBM-bound, a few microseconds): packed nibbles -> int8 rows with the same permutation
+//     of k inside every 8-element run for activations and weights (a dot product does not see it); scales ->
+//     fp32 in the order the drain reads them; lora_act -> T.  Measured on B200: widening inside the GEMM
+//     through shared memory costs a generic->async proxy fence of ~3000 cycles per K group and competes with
+//     the drain for issue slots and shared-memory bandwidth; with the operands pre-widened every byte the
+//     tensor core reads is written by TMA and the SM's CUDA cores only do the per-group scaling.
 //  2. `gemm_tc_kernel`: one persistent CTA per SM (320 threads) walks a static contiguous range of
 //     128 x 128 output tiles.  A stage of the shared-memory ring holds two K groups (128 k):
 //       warp 0    TMA producer: A and W rows (128 x 128 B each, 128-byte swizzle) and the two groups' scale
@@ -24,9 +22,22 @@
 //                 fp32 slot of the same ring.
 //       warps 2-9 drain: a warp owns 32 rows x 64 columns.  tcgen05.ld.16x256b gives a thread the
 //                 accumulator-fragment layout (4 rows x 16 columns), so it needs 4 row scales and 16 column
-//                 scales per group; int -> float by the magic-number add, then two packed fp32x2 FMAs per
-//                 column pair.  After the last group: bias, optional per-head RMSNorm + RoPE, rounding, and a
-//                 coalesced store through a padded per-warp staging tile.
+//                 scales per group, and two packed fp32x2 FMAs per column pair (below).  The loads of the
+//                 next half group are in flight while the current half is scaled.  After the last group: bias,
+//                 optional per-head RMSNorm + RoPE, rounding, and a coalesced store through a padded per-warp
+//                 staging tile.
+//
+// int32 -> fp32 without a conversion instruction.  The drain's budget is two FMA issues per column pair, so the
+// accumulator is made to BE a float: operands are A' = 16 a (the nibble moved to the top of its byte) and
+// W' = w + 8 (the nibble with its sign bit flipped, 0..15), and for signed activations a third MMA of constant
+// operands (64 x 127 over k = 32) adds C = 260096, so that the accumulator
+//     u = 16 p + 128 Sa[m] + C,   Sa[m] = sum of the row's 64 activations in the group,
+// is never negative and below 2^23: its bit pattern read as fp32 is the denormal u * 2^-149.  One FMA with
+// per-row constants from the pre-pass, t = u_f * (as * 2^64) - (K_m * as * 2^-85), K_m = 128 Sa[m] + C, is
+// (as * p) * 2^-81 rounded once -- the constant is exact in fp32 because K_m is a multiple of 128 with at most
+// 12 significant bits and a 16-bit scale has at most 11 -- and the second FMA adds t * (ws * 2^81) to the running
+// sum.  Powers of two do not change a rounding (scales between 2^-40 and 2^60 stay clear of under- and overflow),
+// so the result is float(p) * as * ws accumulated in fp32, as in the reference.
 // Every wait on an mbarrier is bounded (~2 s); on expiry the CTA records a code in the status word,
 // unwinds without touching more data and frees its tensor memory.
 #include <cuda.h>
@@ -46,13 +57,13 @@ constexpr int NSLOT = 4;            // tensor-memory accumulator slots of BN col
 constexpr int DRAIN_WARPS = 8;      // warps 2..9
 constexpr int NTHREADS = 64 + DRAIN_WARPS * 32;
 constexpr int COLS = BN / 2;        // columns one drain warp owns
-// 1.5 * 2^15: one unit in the last place is 2^-8, so adding 256 * p to the bit pattern gives 49152 + p
-constexpr uint32_t MAGIC_BITS = 0x47400000u;
-constexpr float MAGIC_F = 49152.0f;
+constexpr int C_OFFSET = 64 * 127 * 32;  // what the constant MMA adds to every accumulator (signed activations)
+constexpr int AS_EXP = 64;               // row scales travel as as * 2^AS_EXP
+constexpr int WS_EXP = 149 - 4 - AS_EXP; // column scales as ws * 2^WS_EXP: 2^-149 (denormal) * 16 (A') undone
 
 struct Cfg {
     static constexpr int ST_A = BM * 128, ST_W = BN * 128;  // two K groups of int8 per row
-    static constexpr int ST_AS = 2 * BM * 8;                // per group and row: (as, -MAGIC * as)
+    static constexpr int ST_AS = 2 * BM * 8;                // per group and row: (as * 2^64, -K_m * as * 2^-85)
     static constexpr int ST_WS = 2 * BN * 4;                // per group and column: ws, in drain order
     static constexpr int ST_BYTES = ST_A + ST_W + ST_AS + ST_WS;
     static constexpr int STG_PITCH = COLS * 2 + 16;
@@ -61,7 +72,8 @@ struct Cfg {
     static constexpr int OFF_ST = 0;
     static constexpr int OFF_STG = OFF_ST + STAGES * ST_BYTES;
     static constexpr int OFF_XCH = OFF_STG + STG_BYTES;
-    static constexpr int OFF_BAR = OFF_XCH + XCH_BYTES;
+    static constexpr int OFF_CONST = OFF_XCH + XCH_BYTES;   // 4 KB of 64s and 4 KB of 127s: operands of the constant MMA
+    static constexpr int OFF_BAR = OFF_CONST + 8192;
     static constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;  // + slack to align the base to 1 KB
     static constexpr int TMEM_COLS = NSLOT * BN;             // 512
 };
@@ -82,6 +94,7 @@ struct TcParams {
     void* out;
     const void* bias;
     int32_t* p_out;  // debug: (K/64, M, N) group sums
+    const int32_t* km; // (K/64, M): K_m of the header comment, for the debug output
     int M, N, K, actual_m, R;
     int act_unsigned;
     long long stride_om;
@@ -159,6 +172,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         tmem_alloc(smem_u32(tmem_ptr_s), C::TMEM_COLS);
         tmem_relinquish();
     }
+    for (int i = threadIdx.x; i < 8192 / 16; i += NTHREADS) {
+        const uint32_t b = i < 256 ? 0x40404040u : 0x7F7F7F7Fu;
+        reinterpret_cast<uint4*>(smem + C::OFF_CONST)[i] = make_uint4(b, b, b, b);
+    }
+    fence_proxy_async_smem();  // the tensor core reads these bytes through the async proxy
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -228,6 +246,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const uint32_t idesc_i8 = umma_idesc(2u, p.act_unsigned ? 0u : 1u, 1u, BN);
             const uint32_t f16fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             const uint32_t idesc_lr = umma_idesc(1u, f16fmt, f16fmt, BN);
+            // constant operands: every byte equal, so any core-matrix placement inside the 4 KB reads the same
+            const uint64_t desc_ca = umma_desc_kmajor(s_base + C::OFF_CONST, 128, 256);
+            const uint64_t desc_cb = umma_desc_kmajor(s_base + C::OFF_CONST + 4096, 128, 256);
+            const bool offset_mma = !p.act_unsigned;  // unsigned activations never give a negative accumulator
             uint32_t it = 0, ait = 0;
             bool ok = true;
             NB_PF_DECL
@@ -245,10 +267,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         NB_PF(1);
                         tc_fence_after();
                         const uint32_t d = tmem_base + slot * BN;
+                        if (offset_mma) mma_i8(d, desc_ca, desc_cb, idesc_i8, 0u);
 #pragma unroll
                         for (int h = 0; h < 2; ++h)
                             mma_i8(d, umma_desc_sw128(a_addr + (2 * i + h) * 32), umma_desc_sw128(w_addr + (2 * i + h) * 32),
-                                   idesc_i8, h);
+                                   idesc_i8, (offset_mma || h) ? 1u : 0u);
                         tc_commit(bar(B_ACC_FULL + slot));
                         NB_PF(2);
                     }
@@ -299,85 +322,102 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
             for (int i = 0; i < 32; ++i) acc[i] = 0ull;
 
-            for (int j = 0; j < GS && ok; ++j, ++it) {
-                const int s = it % STAGES;
+            // Software pipeline over half groups (16 TMEM lanes = 32 registers each): while one half is scaled the
+            // loads of the next are in flight.  `v[0]` holds lane block 0, `v[1]` lane block 1 of a group.
+            {
+                const int slot = ait % NSLOT;
+                NB_PF(7);
+                if (!mbar_wait_warp(bar(B_ACC_FULL + slot), (ait / NSLOT) & 1, abort_s, E_DRAIN | 1, 100)) { ok = false; break; }
+                NB_PF(0);
+                tc_fence_after();
+                tmem_ld_16x256b_x8(lane_base + slot * BN, v[0]);
+            }
+            for (int g = 0; g < G; ++g, ++ait) {
+                const int slot = ait % NSLOT;
+                const int s = (it + (g >> 1)) % STAGES, i = g & 1;
                 const uint8_t* st = smem + C::OFF_ST + s * C::ST_BYTES;
-                const int ng = min(2, G - 2 * j);
-                for (int i = 0; i < ng; ++i, ++ait) {
-                    const int slot = ait % NSLOT;
-                    NB_PF(7);
-                    if (!mbar_wait_warp(bar(B_ACC_FULL + slot), (ait / NSLOT) & 1, abort_s, E_DRAIN | 1, 100)) { ok = false; break; }
-                    NB_PF(0);
-                    tc_fence_after();
-                    tmem_ld_16x256b_x8(lane_base + slot * BN, v[0]);
-                    tmem_ld_16x256b_x8(lane_base + (16u << 16) + slot * BN, v[1]);
-                    // scales of this group while the loads are in flight
-                    const float2* as_s = reinterpret_cast<const float2*>(st + C::ST_A + C::ST_W) + i * BM + q * 32 + gid;
-                    const ulonglong2* ws_s = reinterpret_cast<const ulonglong2*>(st + C::ST_A + C::ST_W + C::ST_AS + i * BN * 4 + half * COLS * 4) + tig;
-                    uint64_t as2[4], cm2[4];
+                // scales of this group
+                const float2* as_s = reinterpret_cast<const float2*>(st + C::ST_A + C::ST_W) + i * BM + q * 32 + gid;
+                const ulonglong2* ws_s = reinterpret_cast<const ulonglong2*>(st + C::ST_A + C::ST_W + C::ST_AS + i * BN * 4 + half * COLS * 4) + tig;
+                uint64_t as2[4], cm2[4];
 #pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        const float2 ac = as_s[r * 8];  // rows gid, gid + 8, gid + 16, gid + 24
-                        as2[r] = pack_f32x2(ac.x, ac.x);
-                        cm2[r] = pack_f32x2(ac.y, ac.y);
-                    }
-                    ulonglong2 w[4];
+                for (int r = 0; r < 4; ++r) {
+                    const float2 ac = as_s[r * 8];  // rows gid, gid + 8, gid + 16, gid + 24
+                    as2[r] = pack_f32x2(ac.x, ac.x);
+                    cm2[r] = pack_f32x2(ac.y, ac.y);
+                }
+                ulonglong2 w[4];
 #pragma unroll
-                    for (int jj = 0; jj < 4; ++jj) w[jj] = ws_s[jj * 4];
-                    NB_PF(1);
-                    tmem_wait_ld();
-                    NB_PF(2);
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + slot));
-                    NB_PF(3);
+                for (int jj = 0; jj < 4; ++jj) w[jj] = ws_s[jj * 4];
+                NB_PF(1);
+                tmem_wait_ld();  // v[0] has landed
+                NB_PF(2);
+                tmem_ld_16x256b_x8(lane_base + (16u << 16) + slot * BN, v[1]);
 #pragma unroll
-                    for (int lb = 0; lb < 2; ++lb) {
-                        uint32_t(&vv)[32] = v[lb];
-#pragma unroll
-                        for (int jx = 0; jx < 8; ++jx) {
-                            const uint64_t wj = (jx & 1) ? w[jx >> 1].y : w[jx >> 1].x;
-#pragma unroll
-                            for (int rs = 0; rs < 2; ++rs) {
-                                const int vi = 4 * jx + 2 * rs;
-                                const uint64_t x = pack_u32x2(vv[vi] + MAGIC_BITS, vv[vi + 1] + MAGIC_BITS);
-                                const uint64_t tt = fma_f32x2(x, as2[lb * 2 + rs], cm2[lb * 2 + rs]);
-                                uint64_t& a = acc[(lb * 8 + jx) * 2 + rs];
-                                a = fma_f32x2(tt, wj, a);
-                            }
+                for (int lb = 0; lb < 2; ++lb) {
+                    uint32_t(&vv)[32] = v[lb];
+                    if (lb == 1) {
+                        tmem_wait_ld();  // v[1] has landed: the slot is read out
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + slot));
+                        if (i == 1 || g == G - 1) {
+                            // This warp holds the stage's scales in registers (the empty asm makes the loads retire first).
+                            // Released BEFORE the wait below: the low-rank slot only completes after the producer has
+                            // reused ring stages, which it may not do while a drain warp still owes this arrival.
+                            asm volatile("" ::"l"(as2[2]), "l"(as2[3]), "l"(cm2[2]), "l"(cm2[3]), "l"(w[3].y) : "memory");
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(bar(B_SCDONE + s));
                         }
-                        if (DEBUG_P) {
+                        NB_PF(3);
+                        // next accumulator: the next group, or the low-rank slot after the last group
+                        if (g + 1 < G || LCH > 0) {
+                            const int ns = (ait + 1) % NSLOT;
+                            if (!mbar_wait_warp(bar(B_ACC_FULL + ns), ((ait + 1) / NSLOT) & 1, abort_s, E_DRAIN | 2, 100)) { ok = false; break; }
+                            tc_fence_after();
+                            tmem_ld_16x256b_x8(lane_base + ns * BN, v[0]);
+                        }
+                        NB_PF(0);
+                    }
 #pragma unroll
-                            for (int e = 0; e < 32; ++e) {
-                                const int m = m0 + q * 32 + lb * 16 + ((e >> 1) & 1) * 8 + gid;
-                                const int n = nc0 + (e >> 2) * 8 + 2 * tig + (e & 1);
-                                if (m < p.M && n < p.N) p.p_out[((long long)(2 * j + i) * p.M + m) * p.N + n] = ((int)vv[e]) >> 8;
-                            }
+                    for (int jx = 0; jx < 8; ++jx) {
+                        const uint64_t wj = (jx & 1) ? w[jx >> 1].y : w[jx >> 1].x;
+#pragma unroll
+                        for (int rs = 0; rs < 2; ++rs) {
+                            const int vi = 4 * jx + 2 * rs;
+                            const uint64_t tt = fma_f32x2(pack_u32x2(vv[vi], vv[vi + 1]), as2[lb * 2 + rs], cm2[lb * 2 + rs]);
+                            uint64_t& a = acc[(lb * 8 + jx) * 2 + rs];
+                            a = fma_f32x2(tt, wj, a);
                         }
                     }
+                    if (DEBUG_P) {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            const int m = m0 + q * 32 + lb * 16 + ((e >> 1) & 1) * 8 + gid;
+                            const int n = nc0 + (e >> 2) * 8 + 2 * tig + (e & 1);
+                            if (m < p.M && n < p.N)
+                                p.p_out[((long long)g * p.M + m) * p.N + n] = ((int)vv[e] - p.km[(long long)g * p.M + m]) >> 4;
+                        }
+                    }
+                    NB_PF(4);
                 }
                 if (!ok) break;
-                NB_PF(4);
-                // this warp has read the stage's scales
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(B_SCDONE + s));
                 NB_PF(5);
             }
             if (!ok) break;
+            it += GS;
             if (LCH > 0) {
                 const int slot = ait % NSLOT;
-                if (!mbar_wait_warp(bar(B_ACC_FULL + slot), (ait / NSLOT) & 1, abort_s, E_DRAIN | 3, 100)) { ok = false; break; }
-                tc_fence_after();
-                tmem_ld_16x256b_x8(lane_base + slot * BN, v[0]);
-                tmem_ld_16x256b_x8(lane_base + (16u << 16) + slot * BN, v[1]);
                 tmem_wait_ld();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + slot));
-                it += LCH;  // the low-rank stages carry nothing for the drain
-                ++ait;
+                tmem_ld_16x256b_x8(lane_base + (16u << 16) + slot * BN, v[1]);
 #pragma unroll
-                for (int lb = 0; lb < 2; ++lb)
+                for (int lb = 0; lb < 2; ++lb) {
+                    if (lb == 1) {
+                        tmem_wait_ld();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + slot));
+                    }
 #pragma unroll
                     for (int jx = 0; jx < 8; ++jx)
 #pragma unroll
@@ -385,6 +425,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             uint64_t& a = acc[(lb * 8 + jx) * 2 + rs];
                             a = add_f32x2(a, pack_u32x2(v[lb][4 * jx + 2 * rs], v[lb][4 * jx + 2 * rs + 1]));
                         }
+                }
+                it += LCH;  // the low-rank stages carry nothing for the drain
+                ++ait;
             }
 
             // ---------------- epilogue: bias, optional RMSNorm + RoPE, rounding, staged store ----------------
@@ -497,8 +540,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 struct PrepackParams {
     const uint8_t* act; const uint8_t* wgt;
     const void* ascales; const void* wscales; const float* lora_act;
-    int8_t* a8; int8_t* w8; float* asf; float* wsf; void* la16;
+    int8_t* a8; int8_t* w8; float* asf; float* wsf; void* la16; int32_t* km;
     int M, N, K, R, Np;  // Np: N rounded up to 128
+    int act_unsigned;
     long long stride_am, stride_wn, stride_asg, stride_wsg, stride_lam;
 };
 
@@ -517,10 +561,17 @@ __global__ void __launch_bounds__(256) prepack_kernel(const PrepackParams p) {
         const int c = (int)(u % upr);
         const uint8_t* src = (is_w ? p.wgt + row * p.stride_wn : p.act + row * p.stride_am) + c * 16;
         const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
-        // per packed word: even-k nibbles then odd-k nibbles, each moved to the top of its byte
+        // per packed word: even-k nibbles then odd-k nibbles; activations as 16 * a (nibble at the top of the byte),
+        // weights as w + 8 (sign bit flipped, 0..15)
         uint4 o0, o1;
-        o0.x = (v.x << 4) & 0xF0F0F0F0u; o0.y = v.x & 0xF0F0F0F0u; o0.z = (v.y << 4) & 0xF0F0F0F0u; o0.w = v.y & 0xF0F0F0F0u;
-        o1.x = (v.z << 4) & 0xF0F0F0F0u; o1.y = v.z & 0xF0F0F0F0u; o1.z = (v.w << 4) & 0xF0F0F0F0u; o1.w = v.w & 0xF0F0F0F0u;
+        if (is_w) {
+            const uint32_t f = 0x08080808u, mk = 0x0F0F0F0Fu;
+            o0.x = (v.x & mk) ^ f; o0.y = ((v.x >> 4) & mk) ^ f; o0.z = (v.y & mk) ^ f; o0.w = ((v.y >> 4) & mk) ^ f;
+            o1.x = (v.z & mk) ^ f; o1.y = ((v.z >> 4) & mk) ^ f; o1.z = (v.w & mk) ^ f; o1.w = ((v.w >> 4) & mk) ^ f;
+        } else {
+            o0.x = (v.x << 4) & 0xF0F0F0F0u; o0.y = v.x & 0xF0F0F0F0u; o0.z = (v.y << 4) & 0xF0F0F0F0u; o0.w = v.y & 0xF0F0F0F0u;
+            o1.x = (v.z << 4) & 0xF0F0F0F0u; o1.y = v.z & 0xF0F0F0F0u; o1.z = (v.w << 4) & 0xF0F0F0F0u; o1.w = v.w & 0xF0F0F0F0u;
+        }
         uint4* dst = reinterpret_cast<uint4*>((is_w ? p.w8 : p.a8) + row * p.K + c * 32);
         dst[0] = o0;
         dst[1] = o1;
@@ -530,7 +581,21 @@ __global__ void __launch_bounds__(256) prepack_kernel(const PrepackParams p) {
     if (u < as_units) {
         const int g = (int)(u / p.M), m = (int)(u % p.M);
         const float a = to_f32<T>(static_cast<const T*>(p.ascales)[(long long)g * p.stride_asg + m]);
-        reinterpret_cast<float2*>(p.asf)[u] = make_float2(a, -MAGIC_F * a);
+        // sum of the row's 64 activations in the group, from byte-wise nibble sums
+        const uint4* src = reinterpret_cast<const uint4*>(p.act + (long long)m * p.stride_am + g * 32);
+        const uint32_t flip = p.act_unsigned ? 0u : 0x88888888u;
+        uint32_t bs = 0;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint4 x = __ldg(src + h);
+            const uint32_t ww[4] = {x.x ^ flip, x.y ^ flip, x.z ^ flip, x.w ^ flip};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) bs += (ww[k] & 0x0F0F0F0Fu) + ((ww[k] >> 4) & 0x0F0F0F0Fu);  // <= 240 per byte
+        }
+        const int sa = (int)__dp4a(bs, 0x01010101u, 0u) - (p.act_unsigned ? 0 : 512);
+        const int km = 128 * sa + (p.act_unsigned ? 0 : C_OFFSET);
+        reinterpret_cast<float2*>(p.asf)[u] = make_float2(ldexpf(a, AS_EXP), -__fmul_rn((float)km, ldexpf(a, AS_EXP - 149)));
+        p.km[u] = km;
         return;
     }
     u -= as_units;
@@ -538,7 +603,7 @@ __global__ void __launch_bounds__(256) prepack_kernel(const PrepackParams p) {
         // column n of its 128-wide tile -> [tile][warp half][pair of 8-col blocks][tig][4]: one 128-bit load of a drain
         // thread is (cols c, c+1 of block j, cols c, c+1 of block j+1)
         const int g = (int)(u / p.Np), n = (int)(u % p.Np);
-        const float w = n < p.N ? to_f32<T>(static_cast<const T*>(p.wscales)[(long long)g * p.stride_wsg + n]) : 0.f;
+        const float w = n < p.N ? ldexpf(to_f32<T>(static_cast<const T*>(p.wscales)[(long long)g * p.stride_wsg + n]), WS_EXP) : 0.f;
         const int tile = n / BN, i = n % BN;
         const int hf = i / COLS, cc = i % COLS;
         const int blk = cc >> 3, tg = (cc >> 1) & 3, e = cc & 1;
@@ -593,7 +658,7 @@ static bool make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, u
 static inline size_t up256(size_t x) { return (x + 255) & ~size_t(255); }
 
 struct Scratch {
-    size_t a8, w8, asf, wsf, la16, total;
+    size_t a8, w8, asf, wsf, la16, km, total;
     int Np;
 };
 static Scratch scratch_layout(const nb_gemm_args* a) {
@@ -606,12 +671,13 @@ static Scratch scratch_layout(const nb_gemm_args* a) {
     s.asf = off; off += up256(G * a->M * 8);
     s.wsf = off; off += up256(G * s.Np * 4);
     s.la16 = off; off += up256((size_t)a->M * a->R * 2);
+    s.km = off; off += up256(G * a->M * 4);
     s.total = off;
     return s;
 }
 
 template <int EPI, typename T, bool DEBUG_P>
-static int launch_t(const nb_gemm_args* a, const TcParams& p, cudaStream_t s) {
+static int launch_t(const nb_gemm_args* a, TcParams p, cudaStream_t s) {
     using C = Cfg;
     const Scratch sc = scratch_layout(a);
     if (!a->scratch || a->scratch_bytes < (int64_t)sc.total || (reinterpret_cast<uintptr_t>(a->scratch) & 255))
@@ -623,12 +689,15 @@ static int launch_t(const nb_gemm_args* a, const TcParams& p, cudaStream_t s) {
     pp.a8 = reinterpret_cast<int8_t*>(base + sc.a8); pp.w8 = reinterpret_cast<int8_t*>(base + sc.w8);
     pp.asf = reinterpret_cast<float*>(base + sc.asf); pp.wsf = reinterpret_cast<float*>(base + sc.wsf);
     pp.la16 = base + sc.la16;
+    pp.km = reinterpret_cast<int32_t*>(base + sc.km);
+    pp.act_unsigned = a->act_unsigned;
     pp.M = a->M; pp.N = a->N; pp.K = a->K; pp.R = a->R; pp.Np = sc.Np;
     pp.stride_am = a->stride_am; pp.stride_wn = a->stride_wn; pp.stride_asg = a->stride_asg;
     pp.stride_wsg = a->stride_wsg; pp.stride_lam = a->stride_lam;
     const long long G = a->K / 64;
     const long long units = (long long)(a->M + a->N) * (a->K / 32) + G * a->M + G * sc.Np +
                             (a->R ? (long long)a->M * (a->R / 8) : 0);
+    p.km = pp.km;
     prepack_kernel<T><<<(unsigned)((units + 255) / 256), 256, 0, s>>>(pp);
     NB_CUDA_CHECK(cudaGetLastError());
 
