@@ -63,7 +63,7 @@ constexpr int WS_EXP = 149 - 4 - AS_EXP; // column scales as ws * 2^WS_EXP: 2^-1
 
 struct Cfg {
     static constexpr int ST_A = BM * 128, ST_W = BN * 128;  // two K groups of int8 per row
-    static constexpr int ST_AS = 2 * BM * 8;                // per group and row: (as * 2^64, -K_m * as * 2^-85)
+    static constexpr int ST_AS = 2 * BM * 16;               // per group and row: (s, s, c, c), s = as * 2^64, c = -K_m * as * 2^-85
     static constexpr int ST_WS = 2 * BN * 4;                // per group and column: ws, in drain order
     static constexpr int ST_BYTES = ST_A + ST_W + ST_AS + ST_WS;
     static constexpr int STG_PITCH = COLS * 2 + 16;
@@ -82,12 +82,12 @@ static_assert(Cfg::SMEM_BYTES <= 232448, "shared memory budget");
 
 enum {  // barrier indices
     B_FULL = 0,
-    B_EMPTY = B_FULL + STAGES,      // tcgen05.commit: the stage's MMAs have read their operands
-    B_SCDONE = B_EMPTY + STAGES,    // one arrival per drain warp: the stage's scales have been read (int8 stages only)
-    B_ACC_FULL = B_SCDONE + STAGES,
-    B_ACC_EMPTY = B_ACC_FULL + NSLOT,
+    B_DONE = B_FULL + STAGES,       // tcgen05.commit: the stage's MMAs have completed (operands read, accumulators written)
+    B_SCDONE = B_DONE + STAGES,     // one arrival per drain warp: the stage's scales have been read (int8 stages only)
+    B_ACC_EMPTY = B_SCDONE + STAGES,// one arrival per drain warp: the accumulator slot has been read out
     B_XCH = B_ACC_EMPTY + NSLOT,    // one per TMEM lane quarter: the two warps that share rows
-    B_COUNT = B_XCH + 4
+    B_LR = B_XCH + 4,               // tcgen05.commit: the tile's low-rank accumulator is complete
+    B_COUNT = B_LR + 1
 };
 
 struct TcParams {
@@ -162,9 +162,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     auto bar = [&](int i) { return s_bar + 8u * i; };
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < STAGES; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); mbar_init(bar(B_SCDONE + i), DRAIN_WARPS); }
-        for (int i = 0; i < NSLOT; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), DRAIN_WARPS); }
+        for (int i = 0; i < STAGES; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_DONE + i), 1); mbar_init(bar(B_SCDONE + i), DRAIN_WARPS); }
+        for (int i = 0; i < NSLOT; ++i) mbar_init(bar(B_ACC_EMPTY + i), DRAIN_WARPS);
         for (int i = 0; i < 4; ++i) mbar_init(bar(B_XCH + i), 2);
+        mbar_init(bar(B_LR), 1);
         *abort_s = 0;
         fence_barrier_init();
     }
@@ -205,7 +206,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 for (int j = 0; j < GS + LCH; ++j, ++it) {
                     const int s = it % STAGES;
                     NB_PF(7);
-                    if (!mbar_wait(bar(B_EMPTY + s), ((it / STAGES) & 1) ^ 1, abort_s, E_PROD | 1, 500)) { ok = false; break; }
+                    if (!mbar_wait(bar(B_DONE + s), ((it / STAGES) & 1) ^ 1, abort_s, E_PROD | 1, 500)) { ok = false; break; }
                     {
                         // the drain must also be done with the scales of the stage's last int8 fill
                         const uint32_t n = (sc_uses >> (8 * s)) & 0xFFu;
@@ -253,29 +254,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             uint32_t it = 0, ait = 0;
             bool ok = true;
             NB_PF_DECL
+            // One batch per ring stage: both K groups of the stage (up to six MMAs) and ONE commit.  The issuing thread
+            // pays a few hundred cycles per wait / commit, so the work between two of them has to be large.
             for (int t = t_begin; t < t_end && ok; ++t) {
                 for (int j = 0; j < GS && ok; ++j, ++it) {
                     const int s = it % STAGES;
+                    const int ng = min(2, G - 2 * j);
                     NB_PF(7);
                     if (!mbar_wait(bar(B_FULL + s), (it / STAGES) & 1, abort_s, E_MMA | 1, 100)) { ok = false; break; }
                     NB_PF(0);
-                    const uint32_t a_addr = s_base + C::OFF_ST + s * C::ST_BYTES, w_addr = a_addr + C::ST_A;
-                    const int ng = min(2, G - 2 * j);
-                    for (int i = 0; i < ng; ++i, ++ait) {
-                        const int slot = ait % NSLOT;
-                        if (!mbar_wait(bar(B_ACC_EMPTY + slot), ((ait / NSLOT) & 1) ^ 1, abort_s, E_MMA | 2, 100)) { ok = false; break; }
-                        NB_PF(1);
-                        tc_fence_after();
-                        const uint32_t d = tmem_base + slot * BN;
+                    for (int i = 0; i < ng; ++i)
+                        if (!mbar_wait(bar(B_ACC_EMPTY + (ait + i) % NSLOT), (((ait + i) / NSLOT) & 1) ^ 1, abort_s, E_MMA | 2, 100)) { ok = false; break; }
+                    if (!ok) break;
+                    NB_PF(1);
+                    tc_fence_after();
+                    const uint32_t a_addr = s_base + C::OFF_ST + s * C::ST_BYTES;
+                    const uint64_t da = umma_desc_sw128(a_addr), dw = umma_desc_sw128(a_addr + C::ST_A);
+                    // a 32-byte K step advances the descriptor's start address field by 2
+                    {
+                        const uint32_t d = tmem_base + (ait % NSLOT) * BN;
                         if (offset_mma) mma_i8(d, desc_ca, desc_cb, idesc_i8, 0u);
-#pragma unroll
-                        for (int h = 0; h < 2; ++h)
-                            mma_i8(d, umma_desc_sw128(a_addr + (2 * i + h) * 32), umma_desc_sw128(w_addr + (2 * i + h) * 32),
-                                   idesc_i8, (offset_mma || h) ? 1u : 0u);
-                        tc_commit(bar(B_ACC_FULL + slot));
-                        NB_PF(2);
+                        mma_i8(d, da, dw, idesc_i8, offset_mma ? 1u : 0u);
+                        mma_i8(d, da + 2, dw + 2, idesc_i8, 1u);
                     }
-                    tc_commit(bar(B_EMPTY + s));
+                    if (ng == 2) {
+                        const uint32_t d = tmem_base + ((ait + 1) % NSLOT) * BN;
+                        if (offset_mma) mma_i8(d, desc_ca, desc_cb, idesc_i8, 0u);
+                        mma_i8(d, da + 4, dw + 4, idesc_i8, offset_mma ? 1u : 0u);
+                        mma_i8(d, da + 6, dw + 6, idesc_i8, 1u);
+                    }
+                    tc_commit(bar(B_DONE + s));
+                    ait += ng;
+                    NB_PF(2);
                 }
                 if (ok && LCH > 0) {
                     const int slot = ait % NSLOT;
@@ -289,9 +299,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
                         for (int h = 0; h < 2; ++h)
                             mma_f16(d, umma_desc_sw64(a_addr + h * 32), umma_desc_sw64(w_addr + h * 32), idesc_lr, (c | h) ? 1u : 0u);
-                        tc_commit(bar(B_EMPTY + s));
+                        tc_commit(bar(B_DONE + s));
                     }
-                    if (ok) { tc_commit(bar(B_ACC_FULL + slot)); ++ait; }
+                    if (ok) { tc_commit(bar(B_LR)); ++ait; }
                     NB_PF(3);
                 }
             }
@@ -323,28 +333,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             for (int i = 0; i < 32; ++i) acc[i] = 0ull;
 
             // Software pipeline over half groups (16 TMEM lanes = 32 registers each): while one half is scaled the
-            // loads of the next are in flight.  `v[0]` holds lane block 0, `v[1]` lane block 1 of a group.
+            // loads of the next are in flight.  `v[0]` holds lane block 0, `v[1]` lane block 1 of a group.  The MMA warp
+            // completes a ring stage (two groups) at a time, so there is one wait per stage.
             {
-                const int slot = ait % NSLOT;
                 NB_PF(7);
-                if (!mbar_wait_warp(bar(B_ACC_FULL + slot), (ait / NSLOT) & 1, abort_s, E_DRAIN | 1, 100)) { ok = false; break; }
+                if (!mbar_wait_warp(bar(B_DONE + it % STAGES), (it / STAGES) & 1, abort_s, E_DRAIN | 1, 100)) { ok = false; break; }
                 NB_PF(0);
                 tc_fence_after();
-                tmem_ld_16x256b_x8(lane_base + slot * BN, v[0]);
+                tmem_ld_16x256b_x8(lane_base + (ait % NSLOT) * BN, v[0]);
             }
             for (int g = 0; g < G; ++g, ++ait) {
                 const int slot = ait % NSLOT;
-                const int s = (it + (g >> 1)) % STAGES, i = g & 1;
+                const uint32_t itg = it + (g >> 1);
+                const int s = itg % STAGES, i = g & 1;
                 const uint8_t* st = smem + C::OFF_ST + s * C::ST_BYTES;
                 // scales of this group
-                const float2* as_s = reinterpret_cast<const float2*>(st + C::ST_A + C::ST_W) + i * BM + q * 32 + gid;
+                const ulonglong2* as_s = reinterpret_cast<const ulonglong2*>(st + C::ST_A + C::ST_W) + i * BM + q * 32 + gid;
                 const ulonglong2* ws_s = reinterpret_cast<const ulonglong2*>(st + C::ST_A + C::ST_W + C::ST_AS + i * BN * 4 + half * COLS * 4) + tig;
                 uint64_t as2[4], cm2[4];
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
-                    const float2 ac = as_s[r * 8];  // rows gid, gid + 8, gid + 16, gid + 24
-                    as2[r] = pack_f32x2(ac.x, ac.x);
-                    cm2[r] = pack_f32x2(ac.y, ac.y);
+                    const ulonglong2 ac = as_s[r * 8];  // rows gid, gid + 8, gid + 16, gid + 24
+                    as2[r] = ac.x;
+                    cm2[r] = ac.y;
                 }
                 ulonglong2 w[4];
 #pragma unroll
@@ -361,21 +372,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + slot));
-                        if (i == 1 || g == G - 1) {
+                        const bool last_of_stage = i == 1 || g == G - 1;
+                        if (last_of_stage) {
                             // This warp holds the stage's scales in registers (the empty asm makes the loads retire first).
                             // Released BEFORE the wait below: the low-rank slot only completes after the producer has
                             // reused ring stages, which it may not do while a drain warp still owes this arrival.
                             asm volatile("" ::"l"(as2[2]), "l"(as2[3]), "l"(cm2[2]), "l"(cm2[3]), "l"(w[3].y) : "memory");
-                            __syncwarp();
                             if (lane == 0) mbar_arrive(bar(B_SCDONE + s));
                         }
                         NB_PF(3);
-                        // next accumulator: the next group, or the low-rank slot after the last group
-                        if (g + 1 < G || LCH > 0) {
-                            const int ns = (ait + 1) % NSLOT;
-                            if (!mbar_wait_warp(bar(B_ACC_FULL + ns), ((ait + 1) / NSLOT) & 1, abort_s, E_DRAIN | 2, 100)) { ok = false; break; }
+                        // next accumulator: the stage's second group, the next stage, or the low-rank slot after the last group
+                        if (!last_of_stage) {
+                            tmem_ld_16x256b_x8(lane_base + ((ait + 1) % NSLOT) * BN, v[0]);
+                        } else if (g + 1 < G || LCH > 0) {
+                            // (the low-rank slot has a barrier of its own: its ring stages are not watched here, and waiting for a
+                            // later use of a stage barrier while an earlier one is still pending would alias on the parity)
+                            const bool more = g + 1 < G;
+                            if (!mbar_wait_warp(more ? bar(B_DONE + (itg + 1) % STAGES) : bar(B_LR),
+                                                more ? ((itg + 1) / STAGES) & 1 : (uint32_t)(t - t_begin) & 1, abort_s, E_DRAIN | 2, 100)) { ok = false; break; }
+                            NB_PF(5);
                             tc_fence_after();
-                            tmem_ld_16x256b_x8(lane_base + ns * BN, v[0]);
+                            tmem_ld_16x256b_x8(lane_base + ((ait + 1) % NSLOT) * BN, v[0]);
                         }
                         NB_PF(0);
                     }
@@ -402,7 +419,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     NB_PF(4);
                 }
                 if (!ok) break;
-                NB_PF(5);
             }
             if (!ok) break;
             it += GS;
@@ -594,7 +610,8 @@ __global__ void __launch_bounds__(256) prepack_kernel(const PrepackParams p) {
         }
         const int sa = (int)__dp4a(bs, 0x01010101u, 0u) - (p.act_unsigned ? 0 : 512);
         const int km = 128 * sa + (p.act_unsigned ? 0 : C_OFFSET);
-        reinterpret_cast<float2*>(p.asf)[u] = make_float2(ldexpf(a, AS_EXP), -__fmul_rn((float)km, ldexpf(a, AS_EXP - 149)));
+        const float sc = ldexpf(a, AS_EXP), cc = -__fmul_rn((float)km, ldexpf(a, AS_EXP - 149));
+        reinterpret_cast<float4*>(p.asf)[u] = make_float4(sc, sc, cc, cc);
         p.km[u] = km;
         return;
     }
@@ -668,7 +685,7 @@ static Scratch scratch_layout(const nb_gemm_args* a) {
     size_t off = 0;
     s.a8 = off; off += up256((size_t)a->M * a->K);
     s.w8 = off; off += up256((size_t)a->N * a->K);
-    s.asf = off; off += up256(G * a->M * 8);
+    s.asf = off; off += up256(G * a->M * 16);
     s.wsf = off; off += up256(G * s.Np * 4);
     s.la16 = off; off += up256((size_t)a->M * a->R * 2);
     s.km = off; off += up256(G * a->M * 4);
@@ -706,7 +723,7 @@ static int launch_t(const nb_gemm_args* a, TcParams p, cudaStream_t s) {
                                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     bool ok = make_map(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, pp.a8, a->K, a->M, a->K, 128, BM, CU_TENSOR_MAP_SWIZZLE_128B) &&
               make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, pp.w8, a->K, a->N, a->K, 128, BN, CU_TENSOR_MAP_SWIZZLE_128B) &&
-              make_map(&tm_as, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, pp.asf, (uint64_t)a->M * 2, G, (uint64_t)a->M * 8, 2 * BM, 2,
+              make_map(&tm_as, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, pp.asf, (uint64_t)a->M * 2, G, (uint64_t)a->M * 16, 2 * BM, 2,
                        CU_TENSOR_MAP_SWIZZLE_NONE) &&
               make_map(&tm_ws, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, pp.wsf, sc.Np, G, (uint64_t)sc.Np * 4, BN, 2,
                        CU_TENSOR_MAP_SWIZZLE_NONE);

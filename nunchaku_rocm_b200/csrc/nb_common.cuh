@@ -177,6 +177,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // The same wait done by lane 0 for its warp (one poller per warp); every lane gets the verdict.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
                                                unsigned hint_ns = 200) {
+    // fast path without divergence: every lane tests (one broadcast read), the warp votes
+    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
     int ok = 1;
     if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, code, hint_ns) ? 1 : 0;
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
