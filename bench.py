@@ -357,8 +357,8 @@ def run_ours(args) -> None:
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch from the ncu capture summarised under
-# profiles/ (None until a capture exists)
-TRAFFIC_BYTES_PER_LAUNCH = None
+# profiles/gemm_tc_kernel_fused_qkv_4608x9216x3072.md
+TRAFFIC_BYTES_PER_LAUNCH = 91.15e6
 
 
 def main() -> None:
