@@ -121,6 +121,27 @@ int64_t nb_gemm_w4a4_scratch_bytes(const nb_gemm_args* args, const void* epi, in
 int64_t nb_gemm_w4a4_uses_tcgen05(const nb_gemm_args* args, const void* epi, int epi_kind);
 
 /*
+ * nb_gemm_w4a4 for callers that cannot provide scratch memory.  NO COUNTERPART IN THE REFERENCE: its operators
+ * allocate through torch whenever they need to.  Same arguments, kernels and results as nb_gemm_w4a4; `scratch` and
+ * `scratch_bytes` of the argument block are ignored and the scratch block lives in a fixed array of
+ * NB_NOALLOC_SCRATCH_BYTES inside the library's device module.  The call allocates and frees nothing, on the device
+ * or the host.  Meant for hosts that own all device memory themselves and expose no allocator to a plugin (a serving
+ * runtime that has carved up the whole HBM in advance, a foreign-language host that only holds raw input and output
+ * pointers), and for call sites where an allocation is not allowed or may fail late (inside a latency-critical
+ * region where a device allocation would synchronise the device, under memory pressure).
+ *   - Limit: a call whose nb_gemm_w4a4_scratch_bytes() exceeds NB_NOALLOC_SCRATCH_BYTES returns NB_ERR_TOO_LARGE and
+ *     launches nothing (for the tensor-core kernel the need is about (M + N) * K bytes plus the converted scales).
+ *   - First call on a device: the address of the array is looked up once (cudaGetSymbolAddress, which may load the
+ *     module).  Make that first call during set-up, outside any stream capture; later calls only launch kernels.
+ *   - The array is shared by every caller on the device: two calls that can overlap in time (different streams or
+ *     threads without ordering between them) race on it.  Order such calls on one stream or with events.
+ *   - Nothing in the array has to start at zero and nothing is cleared: each call's first kernel writes every byte its
+ *     later kernels read.
+ */
+#define NB_NOALLOC_SCRATCH_BYTES (16 << 20)
+int nb_gemm_w4a4_noalloc(const nb_gemm_args* args, const void* epi, int epi_kind, void* stream);
+
+/*
  * Debug: the exact int32 group sums p_g[m, n] = sum_{k in g} a[m,k] * w[n,k] as the tensor-core
  * kernel accumulates them, (K/64, M, N) int32.  The reference's integer contract
  * (nunchaku/ops/triton/gemm_w4a4.py:477-483) is checked against this.

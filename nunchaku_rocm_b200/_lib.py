@@ -22,6 +22,7 @@ NB_OK, NB_ERR_INVALID, NB_ERR_UNSUPPORTED, NB_ERR_LAUNCH, NB_ERR_DEVICE, NB_ERR_
 DTYPE_CODE = {torch.bfloat16: 0, torch.float16: 1}
 EPI_STORE, EPI_QK, EPI_GELU_QUANT, EPI_SWIGLU_QUANT = range(4)
 IMPL_AUTO, IMPL_TCGEN05, IMPL_GENERIC = range(3)
+NOALLOC_SCRATCH_BYTES = 16 << 20  # NB_NOALLOC_SCRATCH_BYTES
 
 
 class GemmArgs(C.Structure):
@@ -110,6 +111,7 @@ def lib() -> C.CDLL:
                 l.nb_gemm_w4a4_scratch_bytes.restype = C.c_int64
                 l.nb_gemm_w4a4.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_int, C.c_void_p]
                 l.nb_gemm_w4a4_scratch_bytes.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_int]
+                l.nb_gemm_w4a4_noalloc.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_int, C.c_void_p]
                 l.nb_gemm_w4a4_uses_tcgen05.restype = C.c_int64
                 l.nb_gemm_w4a4_uses_tcgen05.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_int]
                 l.nb_gemm_w4a4_group_sums.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_void_p]
