@@ -6,8 +6,7 @@
 // then + T(lora_act) . lora_up^T (16-bit operands, fp32 accumulate), + bias, one rounding to T.
 //
 // Two launches per call:
-//  1. `prepack_kernel` (HBM-bound, a few microseconds): packed nibbles -> int8 rows with the same permutation
-//     of k inside every 8-element run for activations and weights (a dot product does not see it); scales ->
+//  1. `prepack_kernel` (HBM-bound, a few microseconds): packed nibbles -> one e4m3 byte per value; scales ->
 //     fp32 in the order the drain reads them; lora_act -> T.  Measured on B200: widening inside the GEMM
 //     through shared memory costs a generic->async proxy fence of ~3000 cycles per K group and competes with
 //     the drain for issue slots and shared-memory bandwidth; with the operands pre-widened every byte the
@@ -27,17 +26,12 @@
 //                 optional per-head RMSNorm + RoPE, rounding, and a coalesced store through a padded per-warp
 //                 staging tile.
 //
-// int32 -> fp32 without a conversion instruction.  The drain's budget is two FMA issues per column pair, so the
-// accumulator is made to BE a float: operands are A' = 16 a (the nibble moved to the top of its byte) and
-// W' = w + 8 (the nibble with its sign bit flipped, 0..15), and for signed activations a third MMA of constant
-// operands (64 x 127 over k = 32) adds C = 260096, so that the accumulator
-//     u = 16 p + 128 Sa[m] + C,   Sa[m] = sum of the row's 64 activations in the group,
-// is never negative and below 2^23: its bit pattern read as fp32 is the denormal u * 2^-149.  One FMA with
-// per-row constants from the pre-pass, t = u_f * (as * 2^64) - (K_m * as * 2^-85), K_m = 128 Sa[m] + C, is
-// (as * p) * 2^-81 rounded once -- the constant is exact in fp32 because K_m is a multiple of 128 with at most
-// 12 significant bits and a 16-bit scale has at most 11 -- and the second FMA adds t * (ws * 2^81) to the running
-// sum.  Powers of two do not change a rounding (scales between 2^-40 and 2^60 stay clear of under- and overflow),
-// so the result is float(p) * as * ws accumulated in fp32, as in the reference.
+// Exact integers on the floating-point pipe.  Every int4 value (-8..7, or 0..15 for unsigned activations) is exactly
+// representable in e4m3, a product is at most 120 in magnitude and a 64-term sum at most 7680, so kind::f8f6f4 with
+// e4m3 operands and fp32 accumulation yields the group sum p_g as an exact integer-valued float (checked bit for bit
+// against the integer oracle, worst-case patterns included).  It runs at the rate of kind::i8 and the drain needs no
+// int -> float conversion: t = p * as (packed multiply), acc = fma(t, ws, acc) (packed FMA), two issues per column pair,
+// which is the reference's float(p) * as * ws accumulated in fp32.
 // Every wait on an mbarrier is bounded (~2 s); on expiry the CTA records a code in the status word,
 // unwinds without touching more data and frees its tensor memory.
 #include <cuda.h>
@@ -57,13 +51,9 @@ constexpr int NSLOT = 4;            // tensor-memory accumulator slots of BN col
 constexpr int DRAIN_WARPS = 8;      // warps 2..9
 constexpr int NTHREADS = 64 + DRAIN_WARPS * 32;
 constexpr int COLS = BN / 2;        // columns one drain warp owns
-constexpr int C_OFFSET = 64 * 127 * 32;  // what the constant MMA adds to every accumulator (signed activations)
-constexpr int AS_EXP = 64;               // row scales travel as as * 2^AS_EXP
-constexpr int WS_EXP = 149 - 4 - AS_EXP; // column scales as ws * 2^WS_EXP: 2^-149 (denormal) * 16 (A') undone
-
 struct Cfg {
     static constexpr int ST_A = BM * 128, ST_W = BN * 128;  // two K groups of int8 per row
-    static constexpr int ST_AS = 2 * BM * 16;               // per group and row: (s, s, c, c), s = as * 2^64, c = -K_m * as * 2^-85
+    static constexpr int ST_AS = 2 * BM * 8;                // per group and row: (as, as)
     static constexpr int ST_WS = 2 * BN * 4;                // per group and column: ws, in drain order
     static constexpr int ST_BYTES = ST_A + ST_W + ST_AS + ST_WS;
     static constexpr int STG_PITCH = COLS * 2 + 16;
@@ -72,8 +62,7 @@ struct Cfg {
     static constexpr int OFF_ST = 0;
     static constexpr int OFF_STG = OFF_ST + STAGES * ST_BYTES;
     static constexpr int OFF_XCH = OFF_STG + STG_BYTES;
-    static constexpr int OFF_CONST = OFF_XCH + XCH_BYTES;   // 4 KB of 64s and 4 KB of 127s: operands of the constant MMA
-    static constexpr int OFF_BAR = OFF_CONST + 8192;
+    static constexpr int OFF_BAR = OFF_XCH + XCH_BYTES;
     static constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;  // + slack to align the base to 1 KB
     static constexpr int TMEM_COLS = NSLOT * BN;             // 512
 };
@@ -94,7 +83,6 @@ struct TcParams {
     void* out;
     const void* bias;
     int32_t* p_out;  // debug: (K/64, M, N) group sums
-    const int32_t* km; // (K/64, M): K_m of the header comment, for the debug output
     int M, N, K, actual_m, R;
     int act_unsigned;
     long long stride_om;
@@ -173,11 +161,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         tmem_alloc(smem_u32(tmem_ptr_s), C::TMEM_COLS);
         tmem_relinquish();
     }
-    for (int i = threadIdx.x; i < 8192 / 16; i += NTHREADS) {
-        const uint32_t b = i < 256 ? 0x40404040u : 0x7F7F7F7Fu;
-        reinterpret_cast<uint4*>(smem + C::OFF_CONST)[i] = make_uint4(b, b, b, b);
-    }
-    fence_proxy_async_smem();  // the tensor core reads these bytes through the async proxy
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -244,17 +227,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     } else if (warp == 1) {
         // ================================ MMA issuer ================================
         if (lane == 0) {
-            const uint32_t idesc_i8 = umma_idesc(2u, p.act_unsigned ? 0u : 1u, 1u, BN);
+            const uint32_t idesc_f8 = umma_idesc(1u, 0u, 0u, BN);  // fp32 accumulators, e4m3 x e4m3
             const uint32_t f16fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             const uint32_t idesc_lr = umma_idesc(1u, f16fmt, f16fmt, BN);
-            // constant operands: every byte equal, so any core-matrix placement inside the 4 KB reads the same
-            const uint64_t desc_ca = umma_desc_kmajor(s_base + C::OFF_CONST, 128, 256);
-            const uint64_t desc_cb = umma_desc_kmajor(s_base + C::OFF_CONST + 4096, 128, 256);
-            const bool offset_mma = !p.act_unsigned;  // unsigned activations never give a negative accumulator
             uint32_t it = 0, ait = 0;
             bool ok = true;
             NB_PF_DECL
-            // One batch per ring stage: both K groups of the stage (up to six MMAs) and ONE commit.  The issuing thread
+            // One batch per ring stage: both K groups of the stage (four MMAs) and ONE commit.  The issuing thread
             // pays a few hundred cycles per wait / commit, so the work between two of them has to be large.
             for (int t = t_begin; t < t_end && ok; ++t) {
                 for (int j = 0; j < GS && ok; ++j, ++it) {
@@ -273,15 +252,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     // a 32-byte K step advances the descriptor's start address field by 2
                     {
                         const uint32_t d = tmem_base + (ait % NSLOT) * BN;
-                        if (offset_mma) mma_i8(d, desc_ca, desc_cb, idesc_i8, 0u);
-                        mma_i8(d, da, dw, idesc_i8, offset_mma ? 1u : 0u);
-                        mma_i8(d, da + 2, dw + 2, idesc_i8, 1u);
+                        mma_f8(d, da, dw, idesc_f8, 0u);
+                        mma_f8(d, da + 2, dw + 2, idesc_f8, 1u);
                     }
                     if (ng == 2) {
                         const uint32_t d = tmem_base + ((ait + 1) % NSLOT) * BN;
-                        if (offset_mma) mma_i8(d, desc_ca, desc_cb, idesc_i8, 0u);
-                        mma_i8(d, da + 4, dw + 4, idesc_i8, offset_mma ? 1u : 0u);
-                        mma_i8(d, da + 6, dw + 6, idesc_i8, 1u);
+                        mma_f8(d, da + 4, dw + 4, idesc_f8, 0u);
+                        mma_f8(d, da + 6, dw + 6, idesc_f8, 1u);
                     }
                     tc_commit(bar(B_DONE + s));
                     ait += ng;
@@ -348,15 +325,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 const int s = itg % STAGES, i = g & 1;
                 const uint8_t* st = smem + C::OFF_ST + s * C::ST_BYTES;
                 // scales of this group
-                const ulonglong2* as_s = reinterpret_cast<const ulonglong2*>(st + C::ST_A + C::ST_W) + i * BM + q * 32 + gid;
+                const uint64_t* as_s = reinterpret_cast<const uint64_t*>(st + C::ST_A + C::ST_W) + i * BM + q * 32 + gid;
                 const ulonglong2* ws_s = reinterpret_cast<const ulonglong2*>(st + C::ST_A + C::ST_W + C::ST_AS + i * BN * 4 + half * COLS * 4) + tig;
-                uint64_t as2[4], cm2[4];
+                uint64_t as2[4];
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const ulonglong2 ac = as_s[r * 8];  // rows gid, gid + 8, gid + 16, gid + 24
-                    as2[r] = ac.x;
-                    cm2[r] = ac.y;
-                }
+                for (int r = 0; r < 4; ++r) as2[r] = as_s[r * 8];  // rows gid, gid + 8, gid + 16, gid + 24
                 ulonglong2 w[4];
 #pragma unroll
                 for (int jj = 0; jj < 4; ++jj) w[jj] = ws_s[jj * 4];
@@ -377,7 +350,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             // This warp holds the stage's scales in registers (the empty asm makes the loads retire first).
                             // Released BEFORE the wait below: the low-rank slot only completes after the producer has
                             // reused ring stages, which it may not do while a drain warp still owes this arrival.
-                            asm volatile("" ::"l"(as2[2]), "l"(as2[3]), "l"(cm2[2]), "l"(cm2[3]), "l"(w[3].y) : "memory");
+                            asm volatile("" ::"l"(as2[2]), "l"(as2[3]), "l"(w[3].y) : "memory");
                             if (lane == 0) mbar_arrive(bar(B_SCDONE + s));
                         }
                         NB_PF(3);
@@ -402,7 +375,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
                         for (int rs = 0; rs < 2; ++rs) {
                             const int vi = 4 * jx + 2 * rs;
-                            const uint64_t tt = fma_f32x2(pack_u32x2(vv[vi], vv[vi + 1]), as2[lb * 2 + rs], cm2[lb * 2 + rs]);
+                            const uint64_t tt = mul_f32x2(pack_u32x2(vv[vi], vv[vi + 1]), as2[lb * 2 + rs]);
                             uint64_t& a = acc[(lb * 8 + jx) * 2 + rs];
                             a = fma_f32x2(tt, wj, a);
                         }
@@ -413,7 +386,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             const int m = m0 + q * 32 + lb * 16 + ((e >> 1) & 1) * 8 + gid;
                             const int n = nc0 + (e >> 2) * 8 + 2 * tig + (e & 1);
                             if (m < p.M && n < p.N)
-                                p.p_out[((long long)g * p.M + m) * p.N + n] = ((int)vv[e] - p.km[(long long)g * p.M + m]) >> 4;
+                                p.p_out[((long long)g * p.M + m) * p.N + n] = (int)__uint_as_float(vv[e]);
                         }
                     }
                     NB_PF(4);
@@ -556,11 +529,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 struct PrepackParams {
     const uint8_t* act; const uint8_t* wgt;
     const void* ascales; const void* wscales; const float* lora_act;
-    int8_t* a8; int8_t* w8; float* asf; float* wsf; void* la16; int32_t* km;
+    int8_t* a8; int8_t* w8; float* asf; float* wsf; void* la16;
     int M, N, K, R, Np;  // Np: N rounded up to 128
     int act_unsigned;
     long long stride_am, stride_wn, stride_asg, stride_wsg, stride_lam;
 };
+
+// Four nibbles (low 16 bits of `x`, element k in bits 4k..4k+3) -> four e4m3 bytes.  Signed nibbles are two's complement
+// -8..7, unsigned 0..15; every value is exact in e4m3.  Entries 0..7 and 8..15 of the table come from two byte permutes on
+// the low three bits; a third permute turns bit 3 of every nibble into a byte mask (selector 1 -> 0xFF, 0 -> 0x00).
+__device__ __forceinline__ uint32_t e4m3_of_nibbles(uint32_t x, bool uns) {
+    // e4m3: 0 1 2 3 4 5 6 7 -> 00 38 40 44 48 4A 4C 4E;  8..15 -> 50 51 52 53 54 55 56 57;  -8..-1 -> D0 CE CC CA C8 C4 C0 B8
+    const uint32_t lo0 = 0x44403800u, lo1 = 0x4E4C4A48u;
+    const uint32_t hi0 = uns ? 0x53525150u : 0xCACCCED0u, hi1 = uns ? 0x57565554u : 0xB8C0C4C8u;
+    const uint32_t sel = x & 0x7777u;
+    const uint32_t lo = __byte_perm(lo0, lo1, sel), hi = __byte_perm(hi0, hi1, sel);
+    const uint32_t m = __byte_perm(0x0000FF00u, 0u, (x & 0x8888u) >> 3);
+    return lo ^ ((lo ^ hi) & m);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256) prepack_kernel(const PrepackParams p) {
@@ -577,17 +563,16 @@ __global__ void __launch_bounds__(256) prepack_kernel(const PrepackParams p) {
         const int c = (int)(u % upr);
         const uint8_t* src = (is_w ? p.wgt + row * p.stride_wn : p.act + row * p.stride_am) + c * 16;
         const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
-        // per packed word: even-k nibbles then odd-k nibbles; activations as 16 * a (nibble at the top of the byte),
-        // weights as w + 8 (sign bit flipped, 0..15)
-        uint4 o0, o1;
-        if (is_w) {
-            const uint32_t f = 0x08080808u, mk = 0x0F0F0F0Fu;
-            o0.x = (v.x & mk) ^ f; o0.y = ((v.x >> 4) & mk) ^ f; o0.z = (v.y & mk) ^ f; o0.w = ((v.y >> 4) & mk) ^ f;
-            o1.x = (v.z & mk) ^ f; o1.y = ((v.z >> 4) & mk) ^ f; o1.z = (v.w & mk) ^ f; o1.w = ((v.w >> 4) & mk) ^ f;
-        } else {
-            o0.x = (v.x << 4) & 0xF0F0F0F0u; o0.y = v.x & 0xF0F0F0F0u; o0.z = (v.y << 4) & 0xF0F0F0F0u; o0.w = v.y & 0xF0F0F0F0u;
-            o1.x = (v.z << 4) & 0xF0F0F0F0u; o1.y = v.z & 0xF0F0F0F0u; o1.z = (v.w << 4) & 0xF0F0F0F0u; o1.w = v.w & 0xF0F0F0F0u;
+        // one e4m3 byte per nibble, in k order: a 16-entry table looked up with byte permutes
+        const bool uns = !is_w && p.act_unsigned;
+        const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            o[2 * k] = e4m3_of_nibbles(in[k] & 0xFFFFu, uns);
+            o[2 * k + 1] = e4m3_of_nibbles(in[k] >> 16, uns);
         }
+        const uint4 o0 = make_uint4(o[0], o[1], o[2], o[3]), o1 = make_uint4(o[4], o[5], o[6], o[7]);
         uint4* dst = reinterpret_cast<uint4*>((is_w ? p.w8 : p.a8) + row * p.K + c * 32);
         dst[0] = o0;
         dst[1] = o1;
@@ -597,22 +582,7 @@ __global__ void __launch_bounds__(256) prepack_kernel(const PrepackParams p) {
     if (u < as_units) {
         const int g = (int)(u / p.M), m = (int)(u % p.M);
         const float a = to_f32<T>(static_cast<const T*>(p.ascales)[(long long)g * p.stride_asg + m]);
-        // sum of the row's 64 activations in the group, from byte-wise nibble sums
-        const uint4* src = reinterpret_cast<const uint4*>(p.act + (long long)m * p.stride_am + g * 32);
-        const uint32_t flip = p.act_unsigned ? 0u : 0x88888888u;
-        uint32_t bs = 0;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const uint4 x = __ldg(src + h);
-            const uint32_t ww[4] = {x.x ^ flip, x.y ^ flip, x.z ^ flip, x.w ^ flip};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) bs += (ww[k] & 0x0F0F0F0Fu) + ((ww[k] >> 4) & 0x0F0F0F0Fu);  // <= 240 per byte
-        }
-        const int sa = (int)__dp4a(bs, 0x01010101u, 0u) - (p.act_unsigned ? 0 : 512);
-        const int km = 128 * sa + (p.act_unsigned ? 0 : C_OFFSET);
-        const float sc = ldexpf(a, AS_EXP), cc = -__fmul_rn((float)km, ldexpf(a, AS_EXP - 149));
-        reinterpret_cast<float4*>(p.asf)[u] = make_float4(sc, sc, cc, cc);
-        p.km[u] = km;
+        reinterpret_cast<float2*>(p.asf)[u] = make_float2(a, a);
         return;
     }
     u -= as_units;
@@ -620,7 +590,7 @@ __global__ void __launch_bounds__(256) prepack_kernel(const PrepackParams p) {
         // column n of its 128-wide tile -> [tile][warp half][pair of 8-col blocks][tig][4]: one 128-bit load of a drain
         // thread is (cols c, c+1 of block j, cols c, c+1 of block j+1)
         const int g = (int)(u / p.Np), n = (int)(u % p.Np);
-        const float w = n < p.N ? ldexpf(to_f32<T>(static_cast<const T*>(p.wscales)[(long long)g * p.stride_wsg + n]), WS_EXP) : 0.f;
+        const float w = n < p.N ? to_f32<T>(static_cast<const T*>(p.wscales)[(long long)g * p.stride_wsg + n]) : 0.f;
         const int tile = n / BN, i = n % BN;
         const int hf = i / COLS, cc = i % COLS;
         const int blk = cc >> 3, tg = (cc >> 1) & 3, e = cc & 1;
@@ -675,7 +645,7 @@ static bool make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, u
 static inline size_t up256(size_t x) { return (x + 255) & ~size_t(255); }
 
 struct Scratch {
-    size_t a8, w8, asf, wsf, la16, km, total;
+    size_t a8, w8, asf, wsf, la16, total;
     int Np;
 };
 static Scratch scratch_layout(const nb_gemm_args* a) {
@@ -685,16 +655,15 @@ static Scratch scratch_layout(const nb_gemm_args* a) {
     size_t off = 0;
     s.a8 = off; off += up256((size_t)a->M * a->K);
     s.w8 = off; off += up256((size_t)a->N * a->K);
-    s.asf = off; off += up256(G * a->M * 16);
+    s.asf = off; off += up256(G * a->M * 8);
     s.wsf = off; off += up256(G * s.Np * 4);
     s.la16 = off; off += up256((size_t)a->M * a->R * 2);
-    s.km = off; off += up256(G * a->M * 4);
     s.total = off;
     return s;
 }
 
 template <int EPI, typename T, bool DEBUG_P>
-static int launch_t(const nb_gemm_args* a, TcParams p, cudaStream_t s) {
+static int launch_t(const nb_gemm_args* a, const TcParams& p, cudaStream_t s) {
     using C = Cfg;
     const Scratch sc = scratch_layout(a);
     if (!a->scratch || a->scratch_bytes < (int64_t)sc.total || (reinterpret_cast<uintptr_t>(a->scratch) & 255))
@@ -706,7 +675,6 @@ static int launch_t(const nb_gemm_args* a, TcParams p, cudaStream_t s) {
     pp.a8 = reinterpret_cast<int8_t*>(base + sc.a8); pp.w8 = reinterpret_cast<int8_t*>(base + sc.w8);
     pp.asf = reinterpret_cast<float*>(base + sc.asf); pp.wsf = reinterpret_cast<float*>(base + sc.wsf);
     pp.la16 = base + sc.la16;
-    pp.km = reinterpret_cast<int32_t*>(base + sc.km);
     pp.act_unsigned = a->act_unsigned;
     pp.M = a->M; pp.N = a->N; pp.K = a->K; pp.R = a->R; pp.Np = sc.Np;
     pp.stride_am = a->stride_am; pp.stride_wn = a->stride_wn; pp.stride_asg = a->stride_asg;
@@ -714,7 +682,6 @@ static int launch_t(const nb_gemm_args* a, TcParams p, cudaStream_t s) {
     const long long G = a->K / 64;
     const long long units = (long long)(a->M + a->N) * (a->K / 32) + G * a->M + G * sc.Np +
                             (a->R ? (long long)a->M * (a->R / 8) : 0);
-    p.km = pp.km;
     prepack_kernel<T><<<(unsigned)((units + 255) / 256), 256, 0, s>>>(pp);
     NB_CUDA_CHECK(cudaGetLastError());
 
@@ -723,7 +690,7 @@ static int launch_t(const nb_gemm_args* a, TcParams p, cudaStream_t s) {
                                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     bool ok = make_map(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, pp.a8, a->K, a->M, a->K, 128, BM, CU_TENSOR_MAP_SWIZZLE_128B) &&
               make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, pp.w8, a->K, a->N, a->K, 128, BN, CU_TENSOR_MAP_SWIZZLE_128B) &&
-              make_map(&tm_as, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, pp.asf, (uint64_t)a->M * 2, G, (uint64_t)a->M * 16, 2 * BM, 2,
+              make_map(&tm_as, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, pp.asf, (uint64_t)a->M * 2, G, (uint64_t)a->M * 8, 2 * BM, 2,
                        CU_TENSOR_MAP_SWIZZLE_NONE) &&
               make_map(&tm_ws, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, pp.wsf, sc.Np, G, (uint64_t)sc.Np * 4, BN, 2,
                        CU_TENSOR_MAP_SWIZZLE_NONE);

@@ -97,6 +97,31 @@ def test_group_sums_bit_exact(cuda_dev, impl, act_unsigned, M, N, K):
 
 
 @pytest.mark.parametrize("impl", [GENERIC, TC])
+@pytest.mark.parametrize("act_unsigned", [False, True])
+def test_group_sums_extreme_codes_bit_exact(cuda_dev, impl, act_unsigned):
+    # The largest sums the format allows (|p| up to 64 * 15 * 8 = 7680) and every code pair at least once: the
+    # tensor-core path accumulates on a floating-point pipe and must still return the exact integers.
+    Kn = _ops()
+    M, N, K = 128, 128, 256
+    lo_a, hi_a = (0, 15) if act_unsigned else (-8, 7)
+    a = torch.empty(M, K, dtype=torch.int64)
+    w = torch.empty(N, K, dtype=torch.int64)
+    a[:32], w[:32] = hi_a, -8            # most negative sum
+    a[32:64], w[32:64] = lo_a if not act_unsigned else hi_a, 7
+    a[64:96] = (torch.arange(K)[None, :] + torch.arange(32)[:, None]) % 16 + lo_a   # every activation code
+    w[64:96] = (torch.arange(K)[None, :] // 16 + torch.arange(32)[:, None]) % 16 - 8  # against every weight code
+    g = torch.Generator().manual_seed(3)
+    a[96:] = torch.where(torch.rand(32, K, generator=g) < 0.5, lo_a, hi_a)
+    w[96:] = torch.where(torch.rand(32, K, generator=g) < 0.5, -8, 7)
+    act, wgt = w4a4.pack_nibbles(a), w4a4.pack_nibbles(w)
+    p = Kn.gemm_w4a4_group_sums(act.to(cuda_dev), wgt.to(cuda_dev), act_unsigned=act_unsigned, _impl=impl)
+    ref = w4a4.group_dots_int32(act, wgt, act_unsigned)
+    assert int(ref.abs().max()) == (7680 if act_unsigned else 4096)
+    assert torch.equal(p.cpu(), ref)
+    _status_clean(cuda_dev)
+
+
+@pytest.mark.parametrize("impl", [GENERIC, TC])
 def test_unit_scale_output_is_exact_integer_sum(cuda_dev, impl):
     # with unit scales the fp32 tile is sum_g p_g exactly (tests/triton/test_native_gemm.py:166-179)
     Kn = _ops()
