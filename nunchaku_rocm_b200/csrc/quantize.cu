@@ -5,14 +5,14 @@
 // then shift, reciprocal-multiply by smooth, per-group max, scale = max / qmax (stored rounded,
 // transposed (K/G, M)), codes from the unrounded scale with round-half-even, low nibble first.
 //
-// Work split: a CTA of 8 warps owns 32 rows.  Warp w owns the 16-row block (w & 1) and the 64-wide
-// K groups g = (w >> 1) mod 4.  A lane holds rows {gid, gid + 8} x columns {8 tig .. 8 tig + 7} and
-// {32 + 8 tig ..}, read with 128-bit loads; the per-group maximum is a 2-step warp shuffle over
-// the 4 lanes that share a row.  The same registers are the A fragments of the LoRA-down
-// mma.sync.m16n8k16 (a dot product does not care about a permutation of k applied to both
-// operands, so the B fragments are fetched with ldmatrix.trans from the matching rows of the
-// lora_down chunk, staged in shared memory by cp.async).  The four K-quarter partial sums are added
-// in a fixed order through shared memory, so the result is run-to-run identical.
+// Work split: a CTA owns 16 rows and splits K over its warps (4, 8 or 16 of them, chosen so that the grid fills the
+// machine): warp w takes the 64-wide K groups g = w, w + warps, ...  A lane holds rows {gid, gid + 8} x columns
+// {8 tig .. 8 tig + 7} and {32 + 8 tig ..}, read with 128-bit loads kept three iterations in flight; the per-group
+// maximum is a 2-step warp shuffle over the 4 lanes that share a row.  The same registers are the A fragments of the
+// LoRA-down mma.sync.m16n8k16 (a dot product does not care about a permutation of k applied to both operands, so the
+// B fragments are fetched with ldmatrix.trans from the matching rows of the lora_down chunk, staged in shared memory
+// by cp.async).  The warps' partial sums are added in a fixed order through shared memory, so the result is
+// run-to-run identical.
 #include <cuda_fp8.h>
 
 #include "nb_common.cuh"
@@ -20,9 +20,21 @@
 namespace nb {
 namespace {
 
-constexpr int QT_WARPS = 8;
-constexpr int QT_ROWS = 32;
-constexpr int QT_RCHUNK = 64;  // LoRA ranks per grid.y slice
+constexpr int QT_ROWS = 16;
+constexpr int QT_MAX_WARPS = 16;
+
+// Byte offset of the 16-byte unit c of k-row `krow` inside a staged lora_down chunk (64 k-rows x U units, U = ranks / 8
+// in {2, 4, 8}).  Rows are packed into 128-byte lines; the unit index inside a line is XOR-ed with bits of the k-row so
+// that the eight rows one ldmatrix 8x8 tile reads (k = 8 t + e + const, t < 4, e < 2) fall into eight different
+// 16-byte bank groups.
+__device__ __forceinline__ int ld_unit_offset(int krow, int c, int U) {
+    const int t = (krow >> 3) & 3, e = krow & 1;
+    int line, u, sw;
+    if (U == 8) { line = krow; u = c; sw = e | (t << 1); }
+    else if (U == 4) { line = krow >> 1; u = ((krow & 1) << 2) | c; sw = t; }
+    else { line = krow >> 2; u = ((krow & 3) << 1) | c; sw = (t & 1) | ((t >> 1) << 2); }
+    return line * 128 + ((u ^ sw) << 4);
+}
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -69,34 +81,40 @@ struct QParams {
     long long stride_im, stride_om, stride_sg, stride_ld, stride_lam;
 };
 
-// One 16-byte load of 8 T values -> fp32, zero when the row is out of range.
+// One 16-byte load of 8 T values, zero when the row is out of range, and its conversion to fp32.
+__device__ __forceinline__ uint4 load_raw(const void* p, bool ok) {
+    return ok ? __ldg(reinterpret_cast<const uint4*>(p)) : make_uint4(0, 0, 0, 0);
+}
 template <typename T>
-__device__ __forceinline__ void load8(const T* p, bool ok, float (&v)[8]) {
-    uint4 raw = ok ? __ldg(reinterpret_cast<const uint4*>(p)) : make_uint4(0, 0, 0, 0);
+__device__ __forceinline__ void widen8(const uint4& raw, float (&v)[8]) {
     float2 f;
     f = unpack2<T>(raw.x); v[0] = f.x; v[1] = f.y;
     f = unpack2<T>(raw.y); v[2] = f.x; v[3] = f.y;
     f = unpack2<T>(raw.z); v[4] = f.x; v[5] = f.y;
     f = unpack2<T>(raw.w); v[6] = f.x; v[7] = f.y;
 }
-
 template <typename T>
-__global__ void __launch_bounds__(QT_WARPS * 32) quantize_kernel(const QParams p) {
-    extern __shared__ __align__(16) uint8_t smem[];
+__device__ __forceinline__ void load8(const T* p, bool ok, float (&v)[8]) {
+    widen8<T>(load_raw(p, ok), v);
+}
+
+template <typename T, int RC>  // RC: LoRA ranks per grid.y slice (16, 32 or 64)
+__global__ void __launch_bounds__(QT_MAX_WARPS * 32) quantize_kernel(const QParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int KS = blockDim.x >> 5;  // K slices = warps
     const int gid = lane >> 2, tig = lane & 3;
-    const int rb = warp & 1, kq = warp >> 1;
-    const int m0 = blockIdx.x * QT_ROWS + rb * 16;
-    const int r0 = blockIdx.y * QT_RCHUNK;                  // first LoRA rank of this slice
-    const int rn = p.do_lora ? min(QT_RCHUNK, p.R - r0) : 0;  // ranks in this slice (multiple of 16)
+    const int kq = warp;
+    const int m0 = blockIdx.x * QT_ROWS;
+    const int r0 = blockIdx.y * RC;                    // first LoRA rank of this slice
+    const int rn = p.do_lora ? min(RC, p.R - r0) : 0;  // ranks in this slice: 16, 32, 48 (RC = 64 only) or 64
     const bool quantize = blockIdx.y == 0;
     const int G = p.K / 64;  // 64-wide column blocks; an NVFP4 block holds four 16-groups
 
-    // per-warp double buffer for the lora_down chunk: 64 k-rows x 128 bytes; the 16-byte unit u of row k
-    // lives at unit u ^ f(k), f(k) = (k & 1) | ((k >> 3) & 3) << 1, which spreads the eight rows one
-    // ldmatrix 8x8 tile reads (k = 8 t + e + const, t < 4, e < 2) over all eight bank groups
-    constexpr int ld_pitch = QT_RCHUNK * 2;
-    uint8_t* ld_buf = smem + warp * (2 * 64 * ld_pitch);
+    // per-warp double buffer for the lora_down chunk: 64 k-rows x RC ranks
+    constexpr int U = RC / 8;             // 16-byte units per k-row
+    constexpr int CHUNK = 64 * RC * 2;    // bytes
+    uint8_t* ld_buf = smem + warp * (2 * CHUNK);
     const T* x = static_cast<const T*>(p.input);
     const T* ldw = static_cast<const T*>(p.lora_down);
     const T* smooth = static_cast<const T*>(p.smooth);
@@ -104,36 +122,54 @@ __global__ void __launch_bounds__(QT_WARPS * 32) quantize_kernel(const QParams p
     const int row_a = m0 + gid, row_b = m0 + gid + 8;
     const bool ok_a = row_a < p.M, ok_b = row_b < p.M;
 
-    float acc[QT_RCHUNK / 8][4];
+    float acc[RC / 8][4];
 #pragma unroll
-    for (int i = 0; i < QT_RCHUNK / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    for (int i = 0; i < RC / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
     auto stage_ld = [&](int g, int buf) {
-        // 64 rows x rn*2 bytes, 16-byte units
-        const int units_per_row = rn / 8;
-        uint32_t dst0 = smem_u32(ld_buf + buf * 64 * ld_pitch);
-        for (int u = lane; u < 64 * units_per_row; u += 32) {
-            int kr = u / units_per_row, c = u % units_per_row;
-            const int f = (kr & 1) | (((kr >> 3) & 3) << 1);
-            cp_async16(dst0 + kr * ld_pitch + ((c ^ f) << 4), ldw + (long long)(g * 64 + kr) * p.stride_ld + r0 + c * 8);
+        // 64 k-rows x RC ranks in 16-byte units, 32 / U rows per pass of the warp (units beyond rn stay unwritten and
+        // are never multiplied); the loop unrolls, so the swizzled offsets fold to a few operations each
+        const uint32_t dst0 = smem_u32(ld_buf + buf * CHUNK);
+        const int c = lane % U, kr0 = lane / U;
+        const T* src = ldw + (long long)(g * 64 + kr0) * p.stride_ld + r0 + c * 8;
+        if (c * 8 < rn) {
+#pragma unroll
+            for (int j = 0; j < 2 * U; ++j)
+                cp_async16(dst0 + ld_unit_offset(kr0 + j * (32 / U), c, U), src + (long long)j * (32 / U) * p.stride_ld);
         }
     };
+    // The x block of a warp iteration is four 16-byte loads per lane.  Three iterations' loads are kept in flight (the
+    // kernel is HBM-bound and a warp's own iteration is far shorter than the memory latency).
+    auto issue_x = [&](int g, uint4(&r)[4]) {
+        const bool in = g < G;
+        const int c0 = (in ? g : 0) * 64 + 8 * tig;
+        r[0] = load_raw(x + (long long)row_a * p.stride_im + c0, ok_a && in);
+        r[1] = load_raw(x + (long long)row_a * p.stride_im + c0 + 32, ok_a && in);
+        r[2] = load_raw(x + (long long)row_b * p.stride_im + c0, ok_b && in);
+        r[3] = load_raw(x + (long long)row_b * p.stride_im + c0 + 32, ok_b && in);
+    };
+    uint4 xr0[4], xr1[4], xr2[4];
+    issue_x(kq, xr0);
+    issue_x(kq + KS, xr1);
 
     int it = 0;
     if (rn > 0 && kq < G) stage_ld(kq, 0);
     cp_async_commit();
 
-    for (int g = kq; g < G; g += 4, ++it) {
-        if (rn > 0 && g + 4 < G) stage_ld(g + 4, (it + 1) & 1);
+    for (int g = kq; g < G; g += KS, ++it) {
+        if (rn > 0 && g + KS < G) stage_ld(g + KS, (it + 1) & 1);
         cp_async_commit();
+        issue_x(g + 2 * KS, xr2);
 
-        // ---- load the 16 x 64 block: rows {gid, gid+8}, columns {8 tig.., 32 + 8 tig..}
+        // ---- the 16 x 64 block: rows {gid, gid+8}, columns {8 tig.., 32 + 8 tig..}
         float v[2][16];
         const int c0 = g * 64 + 8 * tig;
-        load8<T>(x + (long long)row_a * p.stride_im + c0, ok_a, *reinterpret_cast<float(*)[8]>(&v[0][0]));
-        load8<T>(x + (long long)row_a * p.stride_im + c0 + 32, ok_a, *reinterpret_cast<float(*)[8]>(&v[0][8]));
-        load8<T>(x + (long long)row_b * p.stride_im + c0, ok_b, *reinterpret_cast<float(*)[8]>(&v[1][0]));
-        load8<T>(x + (long long)row_b * p.stride_im + c0 + 32, ok_b, *reinterpret_cast<float(*)[8]>(&v[1][8]));
+        widen8<T>(xr0[0], *reinterpret_cast<float(*)[8]>(&v[0][0]));
+        widen8<T>(xr0[1], *reinterpret_cast<float(*)[8]>(&v[0][8]));
+        widen8<T>(xr0[2], *reinterpret_cast<float(*)[8]>(&v[1][0]));
+        widen8<T>(xr0[3], *reinterpret_cast<float(*)[8]>(&v[1][8]));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { xr0[i] = xr1[i]; xr1[i] = xr2[i]; }
         if (p.fuse_glu) {
             float gate[2][16];
             load8<T>(x + (long long)row_a * p.stride_im + p.K + c0, ok_a, *reinterpret_cast<float(*)[8]>(&gate[0][0]));
@@ -158,7 +194,7 @@ __global__ void __launch_bounds__(QT_WARPS * 32) quantize_kernel(const QParams p
         if (rn > 0) {
             cp_async_wait<1>();
             __syncwarp();
-            const uint32_t base = smem_u32(ld_buf + (it & 1) * 64 * ld_pitch);
+            const uint32_t base = smem_u32(ld_buf + (it & 1) * CHUNK);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 // A fragment i: k-slots (2 tig, 2 tig + 1) = elements 4i, 4i+1; slots (2 tig + 8, +9) = 4i+2, 4i+3
@@ -172,12 +208,11 @@ __global__ void __launch_bounds__(QT_WARPS * 32) quantize_kernel(const QParams p
                 // (slots 8-15, ranks +0), 16-23 matrix 2 (slots 0-7, ranks +8), 24-31 matrix 3 (slots 8-15, +8)
                 const int s = (lane & 7) + ((lane >> 3) & 1) * 8;
                 const int krow = (i < 2 ? 0 : 32) + 8 * ((s & 7) >> 1) + 4 * (i & 1) + 2 * (s >> 3) + (s & 1);
-                const int f = (krow & 1) | (((krow >> 3) & 3) << 1);
 #pragma unroll
-                for (int nt = 0; nt < QT_RCHUNK / 8; nt += 2) {
+                for (int nt = 0; nt < RC / 8; nt += 2) {
                     if (nt * 8 < rn) {
                         uint32_t b[4];
-                        ldmatrix_x4_trans(b, base + krow * ld_pitch + (((nt + (lane >> 4)) ^ f) << 4));
+                        ldmatrix_x4_trans(b, base + ld_unit_offset(krow, nt + (lane >> 4), U));
                         mma16816<T>(acc[nt], a, b[0], b[1]);
                         mma16816<T>(acc[nt + 1], a, b[2], b[3]);
                     }
@@ -201,7 +236,7 @@ __global__ void __launch_bounds__(QT_WARPS * 32) quantize_kernel(const QParams p
             load8<T>(smooth + c0 + 32, true, *reinterpret_cast<float(*)[8]>(&s[8]));
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                float inv = 1.0f / s[i];
+                const float inv = __frcp_rn(s[i]);  // the correctly rounded reciprocal, as 1.0f / s
                 v[0][i] *= inv;
                 v[1][i] *= inv;
             }
@@ -219,13 +254,16 @@ __global__ void __launch_bounds__(QT_WARPS * 32) quantize_kernel(const QParams p
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
                 mx = fmaxf(mx, 0.f);
                 const float scale = mx / (p.is_unsigned ? 15.0f : 7.0f);
-                const float inv = 1.0f / (scale == 0.f ? 1.0f : scale);
+                const float inv = __frcp_rn(scale == 0.f ? 1.0f : scale);
                 const float lo = p.is_unsigned ? 0.f : -8.f, hi = p.is_unsigned ? 15.f : 7.f;
                 uint32_t w[2] = {0, 0};
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    float q = fminf(fmaxf(rint_small(__fmul_rn(v[r][i], inv)), lo), hi);
-                    w[i >> 3] |= ((uint32_t)(int)q & 0xFu) << (4 * (i & 7));
+                    // clamp, then round half-even by the magic add: the low mantissa bits of 1.5 * 2^23 + q are the
+                    // two's-complement code (clamping to integer bounds commutes with the rounding)
+                    const float y = fminf(fmaxf(__fmul_rn(v[r][i], inv), lo), hi);
+                    const uint32_t u = __float_as_uint(__fadd_rn(y, 12582912.0f));
+                    asm("bfi.b32 %0, %1, %0, %2, 4;" : "+r"(w[i >> 3]) : "r"(u), "r"(4 * (i & 7)));
                 }
                 if (ok) {
                     *reinterpret_cast<uint32_t*>(orow + (c0 >> 1)) = w[0];
@@ -262,27 +300,25 @@ __global__ void __launch_bounds__(QT_WARPS * 32) quantize_kernel(const QParams p
     }
     cp_async_wait<0>();
 
-    // ---- fixed-order sum of the four K-quarter partials of each row block
+    // ---- fixed-order sum of the warps' partials
     if (rn > 0) {
-        __syncthreads();  // lora_down buffers are dead; reuse shared memory: [kq][rb][16 rows][QT_RCHUNK]
+        __syncthreads();  // lora_down buffers are dead; reuse shared memory: [warp][16 rows][RC]
         float* red = reinterpret_cast<float*>(smem);
-        float* mine = red + ((kq * 2 + rb) * 16) * QT_RCHUNK;
+        float* mine = red + (warp * 16) * RC;
 #pragma unroll
-        for (int nt = 0; nt < QT_RCHUNK / 8; ++nt) {
+        for (int nt = 0; nt < RC / 8; ++nt) {
             const int c = nt * 8 + 2 * tig;
-            mine[gid * QT_RCHUNK + c] = acc[nt][0];
-            mine[gid * QT_RCHUNK + c + 1] = acc[nt][1];
-            mine[(gid + 8) * QT_RCHUNK + c] = acc[nt][2];
-            mine[(gid + 8) * QT_RCHUNK + c + 1] = acc[nt][3];
+            mine[gid * RC + c] = acc[nt][0];
+            mine[gid * RC + c + 1] = acc[nt][1];
+            mine[(gid + 8) * RC + c] = acc[nt][2];
+            mine[(gid + 8) * RC + c + 1] = acc[nt][3];
         }
         __syncthreads();
-        for (int e = threadIdx.x; e < QT_ROWS * rn; e += QT_WARPS * 32) {
+        for (int e = threadIdx.x; e < QT_ROWS * rn; e += blockDim.x) {
             const int row = e / rn, c = e % rn;
-            const int rrb = row >> 4, rr = row & 15;
             float s = 0.f;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) s += red[((q * 2 + rrb) * 16 + rr) * QT_RCHUNK + c];
-            const int m = blockIdx.x * QT_ROWS + row;
+            for (int q = 0; q < KS; ++q) s += red[(q * 16 + row) * RC + c];
+            const int m = m0 + row;
             if (m < p.M) p.lora_act_out[(long long)m * p.stride_lam + r0 + c] = s;
         }
     }
@@ -317,19 +353,28 @@ extern "C" int nb_quantize_w4a4(const nb_quant_args* a, void* stream) {
     p.stride_im = a->stride_im; p.stride_om = a->stride_om; p.stride_sg = a->stride_sg;
     p.stride_ld = a->stride_ld; p.stride_lam = a->stride_lam;
 
-    dim3 grid((a->M + QT_ROWS - 1) / QT_ROWS, lora ? (a->R + QT_RCHUNK - 1) / QT_RCHUNK : 1);
-    const int ld_pitch = QT_RCHUNK * 2;
-    const size_t smem = (size_t)QT_WARPS * 2 * 64 * ld_pitch;  // 128 KB; also covers the 32 KB reduction buffer
+    // rank chunk per grid.y slice and K slices per CTA: enough warps to cover the memory latency of every SM
+    const int RC = !lora || a->R <= 16 ? 16 : (a->R <= 32 ? 32 : 64);
+    const int row_blocks = (a->M + QT_ROWS - 1) / QT_ROWS;
+    int dev = 0, sms = 0;
+    NB_CUDA_CHECK(cudaGetDevice(&dev));
+    NB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int ks = 4;
+    while (ks < QT_MAX_WARPS && (long long)row_blocks * ks < 14LL * sms && ks * 2 <= a->K / 64) ks *= 2;
+    dim3 grid(row_blocks, lora ? (a->R + RC - 1) / RC : 1);
+    const size_t smem = (size_t)ks * 2 * 64 * RC * 2;  // also covers the reduction buffer (ks x 16 x RC floats)
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (a->dtype == NB_DTYPE_BF16) {
-        NB_CUDA_CHECK(cudaFuncSetAttribute(quantize_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)smem));
-        quantize_kernel<__nv_bfloat16><<<grid, QT_WARPS * 32, smem, s>>>(p);
-    } else {
-        NB_CUDA_CHECK(
-            cudaFuncSetAttribute(quantize_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        quantize_kernel<__half><<<grid, QT_WARPS * 32, smem, s>>>(p);
-    }
+    auto launch = [&](auto kern) -> int {
+        NB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<grid, ks * 32, smem, s>>>(p);
+        return NB_OK;
+    };
+    int rc;
+    if (a->dtype == NB_DTYPE_BF16)
+        rc = RC == 16 ? launch(quantize_kernel<__nv_bfloat16, 16>) : RC == 32 ? launch(quantize_kernel<__nv_bfloat16, 32>) : launch(quantize_kernel<__nv_bfloat16, 64>);
+    else
+        rc = RC == 16 ? launch(quantize_kernel<__half, 16>) : RC == 32 ? launch(quantize_kernel<__half, 32>) : launch(quantize_kernel<__half, 64>);
+    if (rc != NB_OK) return rc;
     NB_CUDA_CHECK(cudaGetLastError());
     return NB_OK;
 }

@@ -1,0 +1,157 @@
+"""
+Per-kernel timings of the hot path on one GPU (a script, not a pytest file), after the reference's
+``tests/triton/bench_kernels.py`` (:36-44: warm-up, timed iterations, TFLOP/s = 2MNK/t for GEMMs, 4BHT^2D/t for
+attention, GB/s for the quantizer).  Differences: CUDA events on the launching stream instead of wall clock, inputs
+rotated over several buffer sets so that HBM-bound kernels do not run out of L2, and every line carries the roofline
+that bounds the kernel and the fraction of the measured peak (``MEASURED_PEAKS.json`` beside the repository root, else
+the stated fallback).
+
+    python tests/bench_kernels.py [--iters 50] [--warmup 10] [--only quantize,gemm,awq,attention]
+
+Prints one JSON object per kernel and shape.  Synthetic seeded inputs with the benchmark configurations' shapes.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from bench import make_cfg_inputs, measured_peaks  # noqa: E402
+
+
+def time_ms(fn, sets, iters, warmup):
+    """Median and best CUDA-event time of ``fn(set)`` over ``iters`` launches, rotating through ``sets``."""
+    for i in range(warmup):
+        fn(sets[i % len(sets)])
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for i, (a, b) in enumerate(evs):
+        a.record()
+        fn(sets[i % len(sets)])
+        b.record()
+    torch.cuda.synchronize()
+    t = [a.elapsed_time(b) for a, b in evs]
+    return statistics.median(t), min(t)
+
+
+def emit(kernel, shape, ms, best, work, unit, bound, peak, src, extra=None):
+    achieved = work / (ms * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
+    line = {
+        "kernel": kernel, "shape": shape, "ms_median": round(ms, 5), "ms_best": round(best, 5),
+        "bound": bound, "achieved": round(achieved, 2), "unit": unit, "peak": peak, "frac": round(achieved / peak, 4),
+        "peak_source": src,
+    }
+    if extra:
+        line.update(extra)
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--only", default="quantize,gemm,awq,attention")
+    args = ap.parse_args()
+    only = set(args.only.split(","))
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks, src = measured_peaks()
+    hbm = float(peaks["hbm_gbs"])
+    bf16 = float(peaks["bf16_tflops"])
+    i8 = 2.0 * bf16  # the 8-bit tensor pipe runs at twice the bf16 rate; the driver measures bf16 only
+
+    from nunchaku_rocm_b200.ops.quantize import svdq_quantize_w4a4_act_fuse_lora_cuda as quantize
+    from nunchaku_rocm_b200.ops.triton.gemm_w4a4 import gemm_w4a4
+    from nunchaku_rocm_b200.ops.triton.gemm_w4a4 import quantize_w4a4_act_fuse_lora as quantize_kernel_level
+    from nunchaku_rocm_b200.ops.triton.awq import awq_gemv_w4a16
+    from nunchaku_rocm_b200.ops.triton.attention import attention_fp16
+
+    M, R = 4608, 32
+    T = torch.bfloat16
+
+    # ---------------------------------------------------------------- activation quantizer (HBM)
+    if "quantize" in only:
+        for K in (3072, 12288):
+            n_sets = max(2, math.ceil(400e6 / (M * K * 2)))
+            sets = []
+            for i in range(n_sets):
+                p = make_cfg_inputs(M, K, 128, R, dev, seed=i)
+                mp = (M + 255) // 256 * 256
+                p["q"] = torch.empty(mp, K // 2, dtype=torch.uint8, device=dev)
+                p["s"] = torch.empty(K // 64, mp, dtype=T, device=dev)
+                p["l"] = torch.empty(mp, R, dtype=torch.float32, device=dev)
+                sets.append(p)
+            ms, best = time_ms(lambda p: quantize(p["x"], p["q"], p["s"], p["proj_down"], p["l"], p["smooth"]), sets,
+                               args.iters, args.warmup)
+            work = 2 * M * K + M * K // 2 + 2 * (K // 64) * M + 4 * M * R + 2 * K * R
+            emit("quantize_kernel", f"M={M} K={K} R={R} signed int4", ms, best, work, "GB/s", "hbm", hbm, src)
+            del sets
+
+    # ---------------------------------------------------------------- W4A4 GEMM (tensor pipe)
+    if "gemm" in only:
+        cases = [("plain", 3072, 3072, False), ("qk_norm_rope", 3072, 9216, False), ("fc2 unsigned acts", 12288, 3072, True)]
+        for name, K, N, uns in cases:
+            sets = []
+            for i in range(3):
+                p = make_cfg_inputs(M, K, N, R, dev, seed=10 + i)
+                if uns:
+                    xx = p["x"].float().abs().to(T)
+                    p["q"], p["s"], p["l"] = quantize_kernel_level(xx, lora_down=p["proj_down"], smooth=p["smooth"], unsigned=True)
+                else:
+                    p["q"], p["s"], p["l"] = quantize(p["x"], lora_down=p["proj_down"], smooth=p["smooth"])
+                p["out"] = torch.empty(M, N, dtype=T, device=dev)
+                sets.append(p)
+            kw = (lambda p: dict(norm_q=p["norm_q"], norm_k=p["norm_k"], rotary_emb=p["rotary_emb"])) if name == "qk_norm_rope" else (lambda p: {})
+            ms, best = time_ms(lambda p: gemm_w4a4(p["q"], p["qweight"], p["out"], p["s"], p["wscales"], p["bias"], p["l"],
+                                                   p["proj_up"], act_unsigned=uns, **kw(p)), sets, args.iters, args.warmup)
+            emit("prepack_kernel + gemm_tc_kernel", f"{name}: M={M} K={K} N={N} R={R}", ms, best, 2.0 * M * N * K, "TFLOP/s",
+                 "tensor", i8, src + " x2 (8-bit pipe)")
+            del sets
+
+    # ---------------------------------------------------------------- AWQ W4A16 GEMV (HBM)
+    if "awq" in only:
+        sys.path.insert(0, ROOT)
+        from oracle import awq_attn  # packing helper only (test infrastructure; this script is not product code)
+
+        n, k = 18432, 3072
+        g = torch.Generator().manual_seed(0)
+        sets = []
+        for i in range(8):  # 8 x 32 MB of weights > L2
+            q = torch.randint(0, 16, (n, k), dtype=torch.int32, generator=g)
+            sets.append(dict(
+                w=awq_attn.awq_pack(q).to(dev),
+                s=(torch.rand(k // 64, n, generator=g) * 0.1 + 0.01).to(T).to(dev),
+                z=(torch.randn(k // 64, n, generator=g) * 0.1).to(T).to(dev)))
+        for m in (1, 2, 4, 8):
+            x = torch.randn(m, k, generator=g).to(T).to(dev)
+            ms, best = time_ms(lambda p: awq_gemv_w4a16(x, p["w"], p["s"], p["z"], m, n, k, 64), sets, args.iters, args.warmup)
+            work = n * k // 2 + 2 * 2 * (k // 64) * n + 2 * m * k + 2 * m * n
+            emit("awq_gemv_kernel", f"m={m} n={n} k={k} g=64", ms, best, work, "GB/s", "hbm", hbm, src)
+        del sets
+
+    # ---------------------------------------------------------------- attention (tensor pipe, bf16)
+    if "attention" in only:
+        B, H, D = 1, 24, 128
+        for Tn in (4608,):
+            g = torch.Generator(device=dev).manual_seed(1)
+            sets = []
+            for i in range(2):
+                qkv = torch.randn(B, Tn, 3, H, D, generator=g, device=dev).to(T)
+                q, k, v = (qkv[:, :, j].permute(0, 2, 1, 3) for j in range(3))  # (B, H, T, D) strided views
+                sets.append(dict(q=q, k=k, v=v, o=torch.empty(B, Tn, H * D, dtype=T, device=dev)))
+            ms, best = time_ms(lambda p: attention_fp16(p["q"], p["k"], p["v"], p["o"], D ** -0.5), sets, args.iters, args.warmup)
+            emit("attention_kernel", f"B={B} H={H} T={Tn} D={D} bf16", ms, best, 4.0 * B * H * Tn * Tn * D, "TFLOP/s", "tensor",
+                 bf16, src)
+
+
+if __name__ == "__main__":
+    main()
