@@ -10,6 +10,8 @@
 // fp32 accumulation, one rounding to T.  A nibble becomes the fp32 value 128 + q by OR-ing it into the
 // mantissa of 128.0f (exact), so the inner loop is one shift, one logic op and one FMA per element and the
 // 128 is folded into the zero-point term: s*(sum (128+q) x) + (z - 128 s) * sum x.
+#include <type_traits>
+
 #include "nb_common.cuh"
 
 namespace nb {
@@ -113,6 +115,188 @@ __global__ void __launch_bounds__(256) awq_dequant_kernel(const uint16_t* __rest
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Batches of up to 8 rows on mma.sync.m16n8k16: the HBM stream of the weights is the only large cost.
+//
+// A warp owns 16 output channels (4 packed rows x 4) and a contiguous range of 64-wide scale groups.  The weights are
+// the A operand (16 channels x 16 k), the activations the B operand (16 k x 8 batch rows).  A dot product does not see
+// a permutation of k applied to both operands, so the k-slots of an MMA are chosen to fit the packing: the four lanes
+// of a quad read the 32 contiguous bytes that hold one channel's 64 k of a group (8 bytes each), and MMA i of the group
+// (i = 0..3) takes nibble i of every int16: slot 2 t + {0, 1} and 2 t + 8 + {0, 1} of lane t are
+// k = 64 c + 32 (t >> 1) + 8 i + 4 (t & 1) + {0, 1, 2, 3}.  A nibble pair becomes two 16-bit floats OFF + q by one
+// shift and one logic operation (OFF = 128 for bf16, 1024 for fp16; exact), and OFF is folded into the zero-point term:
+// out = sum_c s (sum (OFF + q) x) + (z - OFF s) sum x.  The per-group sums of x come from a fifth MMA per step whose A
+// operand is all ones; the activations (as T) are staged in shared memory once per CTA.
+// A CTA is 8 warps = (8 / KS) channel blocks x KS group ranges; the KS partial results are added in a fixed order.
+// The first weight loads are issued before the staging so that the two latencies overlap.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void mma16816_f32(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816_f32<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816_f32<__half>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int GV_UNROLL = 4;  // scale groups per batch; two batches of loads are in flight
+constexpr int GV_WARPS = 8;
+
+template <typename T, int KS>
+__global__ void __launch_bounds__(GV_WARPS * 32) awq_gemv_mma_kernel(const T* __restrict__ x, const uint16_t* __restrict__ kernel,
+                                                                     const T* __restrict__ scales, const T* __restrict__ zeros,
+                                                                     T* __restrict__ out, int m, int n, int k, long long stride_xm,
+                                                                     long long stride_kn, long long stride_sg, long long stride_om) {
+    constexpr int CB = GV_WARPS / KS;  // channel blocks (of 16) per CTA
+    constexpr int CH = 16 * CB;        // channels per CTA
+    constexpr int NT = GV_WARPS * 32;
+    constexpr bool BF = std::is_same<T, __nv_bfloat16>::value;
+    constexpr uint32_t MAGIC2 = BF ? 0x43004300u : 0x64006400u;  // OFF twice, as T
+    constexpr uint32_t ONE2 = BF ? 0x3F803F80u : 0x3C003C00u;    // 1.0 twice, as T
+    constexpr float OFF = BF ? 128.0f : 1024.0f;
+    const int G = k / 64, KP = k + 8;  // padded row of the staged activations (elements)
+    extern __shared__ __align__(16) uint8_t gv_smem[];
+    T* xs = reinterpret_cast<T*>(gv_smem);  // [8][KP]
+    const int ch0 = blockIdx.x * CH;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int cb = warp % CB, ks = warp / CB;
+    const int gpw = (G + KS - 1) / KS;  // groups per warp
+    const int c_begin = ks * gpw, c_end = min(G, c_begin + gpw);
+    // MMA rows gid and gid + 8 of this lane are the ADJACENT channels ch0 + 16 cb + 2 gid + {0, 1} (any assignment of
+    // rows to channels is allowed), so that one 32-bit load fetches both channels' scales; packed row ch / 4, block ch % 4
+    const int chA = ch0 + 16 * cb + 2 * gid, chB = chA + 1;
+    const bool okA = chA < n, okB = chB < n;
+    const uint16_t* rowA = kernel + (long long)(chA >> 2) * stride_kn + (chA & 3) * 16 + 4 * tig;
+    const uint16_t* rowB = kernel + (long long)(chB >> 2) * stride_kn + (chB & 3) * 16 + 4 * tig;
+    const T* xlane = xs + gid * KP + 32 * (tig >> 1) + 4 * (tig & 1);  // + 64 c + 8 i
+    const bool pair_ok = okB && ((reinterpret_cast<uintptr_t>(scales) | reinterpret_cast<uintptr_t>(zeros)) & 3) == 0 &&
+                         (stride_sg & 1) == 0;  // chA is even: the pair is 4-byte aligned when the rows are
+
+    // weights and scale / zero pairs of a batch of groups
+    struct Batch { uint2 wa[GV_UNROLL], wb[GV_UNROLL]; uint32_t s2[GV_UNROLL], z2[GV_UNROLL]; };
+    auto load_batch = [&](Batch& bt, int c0) {
+#pragma unroll
+        for (int u = 0; u < GV_UNROLL; ++u) {
+            const int c = c0 + u;
+            const bool in = c < c_end;
+            bt.wa[u] = in && okA ? __ldg(reinterpret_cast<const uint2*>(rowA + c * 64)) : make_uint2(0, 0);
+            bt.wb[u] = in && okB ? __ldg(reinterpret_cast<const uint2*>(rowB + c * 64)) : make_uint2(0, 0);
+            const unsigned short* sp = reinterpret_cast<const unsigned short*>(scales) + (long long)c * stride_sg + chA;
+            const unsigned short* zp = reinterpret_cast<const unsigned short*>(zeros) + (long long)c * stride_sg + chA;
+            if (in && pair_ok) {
+                bt.s2[u] = __ldg(reinterpret_cast<const uint32_t*>(sp));
+                bt.z2[u] = __ldg(reinterpret_cast<const uint32_t*>(zp));
+            } else {
+                bt.s2[u] = (in && okA ? (uint32_t)__ldg(sp) : 0u) | (in && okB ? (uint32_t)__ldg(sp + 1) << 16 : 0u);
+                bt.z2[u] = (in && okA ? (uint32_t)__ldg(zp) : 0u) | (in && okB ? (uint32_t)__ldg(zp + 1) << 16 : 0u);
+            }
+        }
+    };
+    Batch b0, b1;
+    load_batch(b0, c_begin);
+    load_batch(b1, c_begin + GV_UNROLL);
+
+    // ---- stage the activations as T (rows >= m are zero)
+    for (int i = threadIdx.x; i < 8 * (k / 8); i += NT) {
+        const int r = i / (k / 8), c8 = (i % (k / 8)) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < m) v = __ldg(reinterpret_cast<const uint4*>(x + (long long)r * stride_xm + c8));
+        *reinterpret_cast<uint4*>(xs + r * KP + c8) = v;
+    }
+    __syncthreads();
+
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    auto compute = [&](const Batch& bt, int c0) {
+#pragma unroll
+        for (int u = 0; u < GV_UNROLL; ++u) {
+            const int c = c0 + u;
+            if (c < c_end) {
+                float d[4] = {0.f, 0.f, 0.f, 0.f}, ones[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint32_t a1[4] = {ONE2, ONE2, ONE2, ONE2};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint32_t a[4];
+                    a[0] = ((bt.wa[u].x >> (4 * i)) & 0x000F000Fu) | MAGIC2;
+                    a[1] = ((bt.wb[u].x >> (4 * i)) & 0x000F000Fu) | MAGIC2;
+                    a[2] = ((bt.wa[u].y >> (4 * i)) & 0x000F000Fu) | MAGIC2;
+                    a[3] = ((bt.wb[u].y >> (4 * i)) & 0x000F000Fu) | MAGIC2;
+                    const uint2 b = *reinterpret_cast<const uint2*>(xlane + 64 * c + 8 * i);
+                    mma16816_f32<T>(d, a, b.x, b.y);
+                    mma16816_f32<T>(ones, a1, b.x, b.y);  // every row: the sum of the group's activations per batch row
+                }
+                // d[0..1]: channel A x batch rows 2 tig, 2 tig + 1; d[2..3]: channel B; ones[0..1]: the activation sums
+                const float2 sf = unpack2<T>(bt.s2[u]), zf = unpack2<T>(bt.z2[u]);
+                const float zA = zf.x - OFF * sf.x, zB = zf.y - OFF * sf.y;
+                acc[0] += sf.x * d[0] + zA * ones[0];
+                acc[1] += sf.x * d[1] + zA * ones[1];
+                acc[2] += sf.y * d[2] + zB * ones[0];
+                acc[3] += sf.y * d[3] + zB * ones[1];
+            }
+        }
+    };
+    // two batches in flight: while one is multiplied the next one's loads are outstanding
+    for (int c0 = c_begin; c0 < c_end; c0 += 2 * GV_UNROLL) {
+        compute(b0, c0);
+        load_batch(b0, c0 + 2 * GV_UNROLL);
+        compute(b1, c0 + GV_UNROLL);
+        load_batch(b1, c0 + 3 * GV_UNROLL);
+    }
+
+    // ---- fixed-order sum over the KS group ranges, then the store
+    __syncthreads();  // the staged activations are dead; reuse their memory: [warp][16][8]
+    float* red = reinterpret_cast<float*>(gv_smem);
+    {
+        float* mine = red + warp * 128;
+        // stored by channel inside the block: 2 gid and 2 gid + 1
+        mine[(2 * gid) * 8 + 2 * tig] = acc[0];
+        mine[(2 * gid) * 8 + 2 * tig + 1] = acc[1];
+        mine[(2 * gid + 1) * 8 + 2 * tig] = acc[2];
+        mine[(2 * gid + 1) * 8 + 2 * tig + 1] = acc[3];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < CH * 8; i += NT) {
+        const int r = i / CH, chl = i % CH;  // consecutive threads -> consecutive channels of one batch row
+        const int cbl = chl >> 4, row = chl & 15;
+        float v = 0.f;
+#pragma unroll
+        for (int q = 0; q < KS; ++q) v += red[(q * CB + cbl) * 128 + row * 8 + r];
+        if (r < m && ch0 + chl < n) out[(long long)r * stride_om + ch0 + chl] = from_f32<T>(v);
+    }
+}
+
+template <typename T, int KS>
+int launch_gemv_mma_t(const void* x, const void* kernel, const void* scales, const void* zeros, void* out, int m, int n,
+                      int k, long long sxm, long long skn, long long ssg, long long som, cudaStream_t s) {
+    constexpr int CH = 16 * (GV_WARPS / KS);
+    const int G = k / 64;
+    // the staged activations; the reduction buffer of 16 x 128 floats reuses the memory
+    size_t smem = (size_t)8 * (k + 8) * 2;
+    if (smem < (size_t)GV_WARPS * 128 * sizeof(float)) smem = (size_t)GV_WARPS * 128 * sizeof(float);
+    (void)G;
+    auto kern = awq_gemv_mma_kernel<T, KS>;
+    NB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<(n + CH - 1) / CH, GV_WARPS * 32, smem, s>>>(static_cast<const T*>(x), static_cast<const uint16_t*>(kernel),
+                                              static_cast<const T*>(scales), static_cast<const T*>(zeros),
+                                              static_cast<T*>(out), m, n, k, sxm, skn, ssg, som);
+    NB_CUDA_CHECK(cudaGetLastError());
+    return NB_OK;
+}
+
+// Shared memory of the tensor-core GEMV for the widest channel block, or 0 when the call does not fit its rules.
+inline size_t gemv_mma_smem(int k, int ks) {
+    (void)ks;
+    const size_t b = (size_t)8 * (k + 8) * 2;
+    return b < (size_t)GV_WARPS * 512 ? (size_t)GV_WARPS * 512 : b;
+}
+
 template <typename T, int MR>
 int launch_gemv_t(const void* x, const void* kernel, const void* scales, const void* zeros, void* out, int m, int n,
                   int k, long long sxm, long long skn, long long ssg, long long som, cudaStream_t s) {
@@ -130,11 +314,29 @@ template <typename T>
 int launch_gemv(const void* x, const void* kernel, const void* scales, const void* zeros, void* out, int m, int n,
                 int k, long long sxm, long long skn, long long ssg, long long som, cudaStream_t s) {
     // rows are processed in slabs of at most 8 so that the activations stay in shared memory
+    int dev = 0, sms = 0;
+    NB_CUDA_CHECK(cudaGetDevice(&dev));
+    NB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    // tensor-core kernel: 16-byte aligned activation rows; a CTA of 8 warps covers (8 / ks) blocks of 16 channels, with
+    // ks chosen so that there are about two CTAs per SM
+    int ks = 1;
+    while (ks < GV_WARPS && 2 * (((n + 15) / 16 + (GV_WARPS / ks) - 1) / (GV_WARPS / ks)) < 3 * sms && ks * 2 <= k / 64) ks *= 2;
+    const bool mma_ok = n % 4 == 0 && aligned16(x) && sxm % 8 == 0 && gemv_mma_smem(k, ks) <= 200 * 1024;
     for (int r0 = 0; r0 < m; r0 += 8) {
         const int mr = min(8, m - r0);
         const T* xr = static_cast<const T*>(x) + (long long)r0 * sxm;
         T* outr = static_cast<T*>(out) + (long long)r0 * som;
         int st;
+        if (mma_ok) {
+            switch (ks) {
+                case 1: st = launch_gemv_mma_t<T, 1>(xr, kernel, scales, zeros, outr, mr, n, k, sxm, skn, ssg, som, s); break;
+                case 2: st = launch_gemv_mma_t<T, 2>(xr, kernel, scales, zeros, outr, mr, n, k, sxm, skn, ssg, som, s); break;
+                case 4: st = launch_gemv_mma_t<T, 4>(xr, kernel, scales, zeros, outr, mr, n, k, sxm, skn, ssg, som, s); break;
+                default: st = launch_gemv_mma_t<T, 8>(xr, kernel, scales, zeros, outr, mr, n, k, sxm, skn, ssg, som, s); break;
+            }
+            if (st != NB_OK) return st;
+            continue;
+        }
         if (mr == 1) st = launch_gemv_t<T, 1>(xr, kernel, scales, zeros, outr, mr, n, k, sxm, skn, ssg, som, s);
         else if (mr == 2) st = launch_gemv_t<T, 2>(xr, kernel, scales, zeros, outr, mr, n, k, sxm, skn, ssg, som, s);
         else if (mr <= 4) st = launch_gemv_t<T, 4>(xr, kernel, scales, zeros, outr, mr, n, k, sxm, skn, ssg, som, s);

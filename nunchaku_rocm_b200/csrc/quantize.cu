@@ -255,15 +255,23 @@ __global__ void __launch_bounds__(QT_MAX_WARPS * 32) quantize_kernel(const QPara
                 mx = fmaxf(mx, 0.f);
                 const float scale = mx / (p.is_unsigned ? 15.0f : 7.0f);
                 const float inv = __frcp_rn(scale == 0.f ? 1.0f : scale);
-                const float lo = p.is_unsigned ? 0.f : -8.f, hi = p.is_unsigned ? 15.f : 7.f;
+                // |v| <= mx and inv = 1 / (mx / qmax) bound v * inv by qmax * (1 + 2^-22), which rounds to qmax: only the
+                // lower bound of the unsigned format (negative inputs) needs a clamp, and clamping to an integer bound
+                // commutes with the rounding
+                // round half-even by the magic add: the low mantissa bits of 1.5 * 2^23 + q are the two's-complement code
                 uint32_t w[2] = {0, 0};
+                if (p.is_unsigned) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    // clamp, then round half-even by the magic add: the low mantissa bits of 1.5 * 2^23 + q are the
-                    // two's-complement code (clamping to integer bounds commutes with the rounding)
-                    const float y = fminf(fmaxf(__fmul_rn(v[r][i], inv), lo), hi);
-                    const uint32_t u = __float_as_uint(__fadd_rn(y, 12582912.0f));
-                    asm("bfi.b32 %0, %1, %0, %2, 4;" : "+r"(w[i >> 3]) : "r"(u), "r"(4 * (i & 7)));
+                    for (int i = 0; i < 16; ++i) {
+                        const uint32_t u = __float_as_uint(__fadd_rn(fmaxf(__fmul_rn(v[r][i], inv), 0.f), 12582912.0f));
+                        asm("bfi.b32 %0, %1, %0, %2, 4;" : "+r"(w[i >> 3]) : "r"(u), "r"(4 * (i & 7)));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const uint32_t u = __float_as_uint(__fadd_rn(__fmul_rn(v[r][i], inv), 12582912.0f));
+                        asm("bfi.b32 %0, %1, %0, %2, 4;" : "+r"(w[i >> 3]) : "r"(u), "r"(4 * (i & 7)));
+                    }
                 }
                 if (ok) {
                     *reinterpret_cast<uint32_t*>(orow + (c0 >> 1)) = w[0];

@@ -1,7 +1,7 @@
 """
 Per-kernel timings of the hot path on one GPU (a script, not a pytest file), after the reference's
 ``tests/triton/bench_kernels.py`` (:36-44: warm-up, timed iterations, TFLOP/s = 2MNK/t for GEMMs, 4BHT^2D/t for
-attention, GB/s for the quantizer).  Differences: CUDA events on the launching stream instead of wall clock, inputs
+attention, GB/s for the quantizer).  Differences: CUDA events around a CUDA graph of the launches instead of wall clock, inputs
 rotated over several buffer sets so that HBM-bound kernels do not run out of L2, and every line carries the roofline
 that bounds the kernel and the fraction of the measured peak (``MEASURED_PEAKS.json`` beside the repository root, else
 the stated fallback).
@@ -29,17 +29,31 @@ from bench import make_cfg_inputs, measured_peaks  # noqa: E402
 
 
 def time_ms(fn, sets, iters, warmup):
-    """Median and best CUDA-event time of ``fn(set)`` over ``iters`` launches, rotating through ``sets``."""
+    """
+    Per-launch device time of ``fn(set)``, rotating through ``sets``.  The ``iters`` launches are captured into one CUDA
+    graph and the graph is timed with CUDA events (median and best of five replays, divided by ``iters``): a kernel of a
+    few microseconds would otherwise be timed together with the host's launch overhead.
+    """
     for i in range(warmup):
         fn(sets[i % len(sets)])
     torch.cuda.synchronize()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
-    for i, (a, b) in enumerate(evs):
-        a.record()
-        fn(sets[i % len(sets)])
-        b.record()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(iters):
+                fn(sets[i % len(sets)])
+    torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
-    t = [a.elapsed_time(b) for a, b in evs]
+    t = []
+    for _ in range(5):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        t.append(a.elapsed_time(b) / iters)
     return statistics.median(t), min(t)
 
 
