@@ -723,7 +723,7 @@ extern "C" int nb_debug_set_prof(void* ptr) {
 // Why the tcgen05 kernel cannot take this call, or nullptr (the role of `unsupported_reason`,
 // nunchaku/ops/triton/native/w4a4.py:164-231).
 const char* tc_unsupported_reason(const nb_gemm_args* a, const void* epi, int epi_kind) {
-    if (a->fp4) return "NVFP4";
+    if (a->fp4) return "NVFP4 (handled by the block-scaled kernel)";
     if (a->wcscales || a->alpha != 1.0f || a->fuse_silu) return "wcscales / alpha / SiLU";
     if (epi_kind != NB_EPI_STORE && epi_kind != NB_EPI_QK_NORM_ROPE) return "epilogue";
     if (a->K % 64 || a->N % 8 || a->M < 1) return "K % 64, N % 8";

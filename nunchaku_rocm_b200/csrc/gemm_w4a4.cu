@@ -28,6 +28,14 @@ int launch_requant_rows(const float* lin, int M, int N, int mode, int dtype, con
 const char* tc_unsupported_reason(const nb_gemm_args* a, const void* epi, int epi_kind);
 int launch_tc(const nb_gemm_args* a, const void* epi, int epi_kind, int32_t* p_out, cudaStream_t s);
 int64_t tc_scratch_bytes(const nb_gemm_args* a);
+const char* tc_fp4_unsupported_reason(const nb_gemm_args* a, const void* epi, int epi_kind);
+int launch_tc_fp4(const nb_gemm_args* a, cudaStream_t s);
+int64_t tc_fp4_scratch_bytes(const nb_gemm_args* a);
+
+// int4 calls go to the kind::f8f6f4 kernel, NVFP4 calls to the block-scaled kind::mxf4nvf4 kernel
+static const char* tc_reason(const nb_gemm_args* a, const void* epi, int epi_kind) {
+    return a->fp4 ? tc_fp4_unsupported_reason(a, epi, epi_kind) : tc_unsupported_reason(a, epi, epi_kind);
+}
 
 static int validate(const nb_gemm_args* a, const void* epi, int epi_kind) {
     NB_REQUIRE(a && a->act && a->wgt && a->ascales && a->wscales);
@@ -54,13 +62,13 @@ static int validate(const nb_gemm_args* a, const void* epi, int epi_kind) {
 }
 
 static bool uses_tc(const nb_gemm_args* a, const void* epi, int epi_kind) {
-    return a->impl != NB_IMPL_GENERIC && tc_unsupported_reason(a, epi, epi_kind) == nullptr;
+    return a->impl != NB_IMPL_GENERIC && tc_reason(a, epi, epi_kind) == nullptr;
 }
 
 // The tensor-core kernel keeps its pre-widened operands and fp32 scales in scratch; the generic kernel keeps the
 // fp32 tile there when a row-wise epilogue follows.
 static int64_t scratch_bytes(const nb_gemm_args* a, const void* epi, int epi_kind) {
-    if (uses_tc(a, epi, epi_kind)) return tc_scratch_bytes(a);
+    if (uses_tc(a, epi, epi_kind)) return a->fp4 ? tc_fp4_scratch_bytes(a) : tc_scratch_bytes(a);
     return epi_kind == NB_EPI_STORE ? 0 : (int64_t)a->M * a->N * 4;
 }
 
@@ -90,9 +98,9 @@ extern "C" int nb_gemm_w4a4(const nb_gemm_args* a, const void* epi, int epi_kind
     if (st != NB_OK) return st;
     if (a->M == 0) return NB_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const char* reason = tc_unsupported_reason(a, epi, epi_kind);
+    const char* reason = tc_reason(a, epi, epi_kind);
     if (a->impl == NB_IMPL_TCGEN05 && reason) return NB_ERR_UNSUPPORTED;
-    if (a->impl != NB_IMPL_GENERIC && !reason) return launch_tc(a, epi, epi_kind, nullptr, s);
+    if (a->impl != NB_IMPL_GENERIC && !reason) return a->fp4 ? launch_tc_fp4(a, s) : launch_tc(a, epi, epi_kind, nullptr, s);
 
     GenericParams p = to_generic(a);
     if (epi_kind == NB_EPI_STORE) {

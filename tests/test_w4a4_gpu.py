@@ -371,7 +371,7 @@ def test_swiglu_quant(cuda_dev, dtype):
 
 
 # ------------------------------------------------------------------------------------------------
-# NVFP4 (generic kernel until the block-scaled tensor-core kernel takes it)
+# NVFP4: the generic kernel and the block-scaled tensor-core kernel (kind::mxf4nvf4)
 # ------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_gemm_fp4_wcscales_alpha(cuda_dev, dtype):
@@ -387,6 +387,49 @@ def test_gemm_fp4_wcscales_alpha(cuda_dev, dtype):
     out = Kn.gemm_w4a4(*_cuda(cuda_dev, act, wgt), None, *_cuda(cuda_dev, asc, wsc), wcscales=wcs.to(cuda_dev),
                        alpha=0.75, fp4=True, out_dtype=dtype)
     _close(out, ref, "fp4")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("impl", [GENERIC, 0])  # 0 = automatic: the block-scaled tensor-core kernel when the shape allows
+@pytest.mark.parametrize("M,N,K,R", [(128, 128, 256, 0), (200, 264, 512, 32), (384, 640, 1024, 16), (130, 136, 768, 48)])
+def test_gemm_fp4_shapes_lora_bias(cuda_dev, dtype, impl, M, N, K, R):
+    Kn = _ops()
+    g = torch.Generator().manual_seed(M + N + K + R)
+    act = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, generator=g)
+    wgt = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g)
+    asc = (torch.rand(K // 16, M, generator=g) * 0.05 + 0.01).to(torch.float8_e4m3fn)
+    wsc = (torch.rand(K // 16, N, generator=g) * 0.05 + 0.01).to(torch.float8_e4m3fn)
+    wcs = (torch.rand(N, generator=g) * 0.5 + 0.5).to(dtype)
+    bias = torch.randn(N, generator=g).to(dtype)
+    la = torch.randn(M, R, generator=g) * 0.5 if R else None
+    lu = (torch.randn(N, R, generator=g) * 0.1).to(dtype) if R else None
+    ref = w4a4.gemm_w4a4(act, wgt, asc, wsc, bias=bias, lora_act=la, lora_up=lu, fp4=True, alpha=1.25, wcscales=wcs)
+    dv = lambda t: None if t is None else t.to(cuda_dev)
+    out = Kn.gemm_w4a4(dv(act), dv(wgt), None, dv(asc), dv(wsc), dv(bias), dv(la), dv(lu), wcscales=dv(wcs), alpha=1.25,
+                       fp4=True, out_dtype=dtype, _impl=impl)
+    assert out.shape == (M, N)
+    _close(out, ref, f"fp4 {M}x{N}x{K} R={R} impl={impl}")
+    again = Kn.gemm_w4a4(dv(act), dv(wgt), None, dv(asc), dv(wsc), dv(bias), dv(la), dv(lu), wcscales=dv(wcs), alpha=1.25,
+                         fp4=True, out_dtype=dtype, _impl=impl)
+    assert torch.equal(out, again)
+    _status_clean(cuda_dev)
+
+
+def test_gemm_fp4_tensor_core_kernel_is_selected(cuda_dev):
+    # the shapes above with K % 256 == 0 must run on the block-scaled kernel, not silently on the generic one
+    import ctypes as C
+
+    from nunchaku_rocm_b200 import _lib as L
+    from nunchaku_rocm_b200.ops.triton.gemm_w4a4 import _gemm_args
+
+    M, N, K = 256, 256, 512
+    act = torch.zeros(M, K // 2, dtype=torch.uint8, device=cuda_dev)
+    wgt = torch.zeros(N, K // 2, dtype=torch.uint8, device=cuda_dev)
+    asc = torch.zeros(K // 16, M, dtype=torch.float8_e4m3fn, device=cuda_dev)
+    wsc = torch.zeros(K // 16, N, dtype=torch.float8_e4m3fn, device=cuda_dev)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=cuda_dev)
+    a = _gemm_args(act, wgt, out, asc, wsc, None, None, None, None, False, False, True, 1.0, torch.bfloat16, L.IMPL_AUTO)
+    assert L.lib().nb_gemm_w4a4_uses_tcgen05(C.byref(a), None, L.EPI_STORE) == 1
 
 
 # ------------------------------------------------------------------------------------------------
