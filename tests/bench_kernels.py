@@ -6,7 +6,7 @@ rotated over several buffer sets so that HBM-bound kernels do not run out of L2,
 that bounds the kernel and the fraction of the measured peak (``MEASURED_PEAKS.json`` beside the repository root, else
 the stated fallback).
 
-    python tests/bench_kernels.py [--iters 50] [--warmup 10] [--only quantize,gemm,awq,attention]
+    python tests/bench_kernels.py [--iters 50] [--warmup 10] [--only quantize,gemm,fp4,awq,attention]
 
 Prints one JSON object per kernel and shape.  Synthetic seeded inputs with the benchmark configurations' shapes.
 """
@@ -73,7 +73,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--only", default="quantize,gemm,awq,attention")
+    ap.add_argument("--only", default="quantize,gemm,fp4,awq,attention")
     args = ap.parse_args()
     only = set(args.only.split(","))
     dev = torch.device("cuda", 0)
@@ -129,6 +129,30 @@ def main():
                                                    p["proj_up"], act_unsigned=uns, **kw(p)), sets, args.iters, args.warmup)
             emit("prepack_kernel + gemm_tc_kernel", f"{name}: M={M} K={K} N={N} R={R}", ms, best, 2.0 * M * N * K, "TFLOP/s",
                  "tensor", i8, src + " x2 (8-bit pipe)")
+            del sets
+
+    # ---------------------------------------------------------------- NVFP4 GEMM (block-scaled tensor pipe)
+    if "fp4" in only:
+        fp4_peak = 4.0 * bf16  # e2m1 operands run at four times the bf16 rate; the driver measures bf16 only
+        for name, Mq, K, N in [("qwen qkv", 7168, 3072, 9216), ("qwen mlp fc1", 7168, 3072, 12288), ("qwen mlp fc2", 7168, 12288, 3072)]:
+            sets = []
+            for i in range(3):
+                g = torch.Generator(device=dev).manual_seed(20 + i)
+                p = dict(
+                    act=torch.randint(0, 256, (Mq, K // 2), dtype=torch.uint8, generator=g, device=dev),
+                    wgt=torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g, device=dev),
+                    asc=(torch.rand(K // 16, Mq, generator=g, device=dev) * 0.05 + 0.01).to(torch.float8_e4m3fn),
+                    wsc=(torch.rand(K // 16, N, generator=g, device=dev) * 0.05 + 0.01).to(torch.float8_e4m3fn),
+                    wcs=(torch.rand(N, generator=g, device=dev) * 0.5 + 0.5).to(T),
+                    bias=torch.randn(N, generator=g, device=dev).to(T),
+                    la=torch.randn(Mq, R, generator=g, device=dev),
+                    lu=(torch.randn(N, R, generator=g, device=dev) * 0.02).to(T),
+                    out=torch.empty(Mq, N, dtype=T, device=dev))
+                sets.append(p)
+            ms, best = time_ms(lambda p: gemm_w4a4(p["act"], p["wgt"], p["out"], p["asc"], p["wsc"], p["bias"], p["la"], p["lu"],
+                                                   wcscales=p["wcs"], alpha=0.9, fp4=True), sets, args.iters, args.warmup)
+            emit("prepack_fp4_kernel + gemm_fp4_kernel", f"{name}: M={Mq} K={K} N={N} R={R}", ms, best, 2.0 * Mq * N * K, "TFLOP/s",
+                 "tensor", fp4_peak, src + " x4 (4-bit pipe)")
             del sets
 
     # ---------------------------------------------------------------- AWQ W4A16 GEMV (HBM)
