@@ -287,25 +287,51 @@ def run_ours(args) -> None:
     ops = 2.0 * M_TOK * N_OUT * K_IN
 
     # ---- end to end through the operator API, host buffers in and out --------------------------------
-    hx = [s["x"].cpu().pin_memory() for s in sets[:2]]
-    hout = [torch.empty(M_TOK, N_OUT, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
-    dx = torch.empty_like(sets[0]["x"])
+    # Every step copies its input from pinned host memory and its result back to pinned host memory.  The three phases
+    # run on three streams (upload, compute, download) chained by events, so the copies of neighbouring steps overlap
+    # the kernels as a serving loop would arrange it; all of it is inside the timed region.
+    NB = 3  # steps in flight
+    hx = [sets[i % N_SETS]["x"].cpu().pin_memory() for i in range(NB)]
+    hout = [torch.empty(M_TOK, N_OUT, dtype=torch.bfloat16).pin_memory() for _ in range(NB)]
+    dx = [torch.empty_like(sets[0]["x"]) for _ in range(NB)]
+    dout = [torch.empty(M_TOK, N_OUT, dtype=torch.bfloat16, device=dev) for _ in range(NB)]
+    main = torch.cuda.current_stream()
+    s_up, s_down = torch.cuda.Stream(), torch.cuda.Stream()
+    ev_up = [torch.cuda.Event() for _ in range(NB)]      # upload of slot b finished
+    ev_done = [torch.cuda.Event() for _ in range(NB)]    # kernels of slot b finished
+    ev_free = [torch.cuda.Event() for _ in range(NB)]    # download of slot b finished: its buffers are free again
 
     def e2e_step(i):
+        b = i % NB
         p = sets[i % N_SETS]
-        dx.copy_(hx[i % 2], non_blocking=True)
-        quantize(dx, p["q"], p["s"], p["proj_down"], p["l"], p["smooth"])
-        gemm_w4a4(p["q"], p["qweight"], p["out"], p["s"], p["wscales"], p["bias"], p["l"], p["proj_up"],
+        with torch.cuda.stream(s_up):
+            s_up.wait_event(ev_done[b])   # the kernels that read dx[b] three steps ago
+            dx[b].copy_(hx[b], non_blocking=True)
+            ev_up[b].record(s_up)
+        main.wait_event(ev_up[b])
+        main.wait_event(ev_free[b])       # the download that read dout[b] three steps ago
+        quantize(dx[b], p["q"], p["s"], p["proj_down"], p["l"], p["smooth"])
+        gemm_w4a4(p["q"], p["qweight"], dout[b], p["s"], p["wscales"], p["bias"], p["l"], p["proj_up"],
                   norm_q=p["norm_q"], norm_k=p["norm_k"], rotary_emb=p["rotary_emb"])
-        hout[i % 2].copy_(p["out"], non_blocking=True)
+        ev_done[b].record(main)
+        with torch.cuda.stream(s_down):
+            s_down.wait_event(ev_done[b])
+            hout[b].copy_(dout[b], non_blocking=True)
+            ev_free[b].record(s_down)
+
+    def e2e_drain():
+        main.wait_stream(s_up)
+        main.wait_stream(s_down)
 
     e2e_steps = max(3, min(args.steps, 50))
-    for i in range(3):
+    for i in range(NB):
         e2e_step(i)
+    e2e_drain()
     barrier()
     e0.record()
     for i in range(e2e_steps):
         e2e_step(i)
+    e2e_drain()
     e1.record()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1), dev) / e2e_steps
@@ -341,6 +367,7 @@ def run_ours(args) -> None:
                 "unit": "TOPS",
                 "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": hx[0].numel() * hx[0].element_size(),
+                "pipelining": "3 steps in flight on upload / compute / download streams",
                 "d2h_bytes_per_step": hout[0].numel() * hout[0].element_size(),
             },
             # quantizer + operand pre-pass + GEMM per step

@@ -6,7 +6,7 @@ rotated over several buffer sets so that HBM-bound kernels do not run out of L2,
 that bounds the kernel and the fraction of the measured peak (``MEASURED_PEAKS.json`` beside the repository root, else
 the stated fallback).
 
-    python tests/bench_kernels.py [--iters 50] [--warmup 10] [--only quantize,gemm,fp4,awq,attention]
+    python tests/bench_kernels.py [--iters 50] [--warmup 10] [--only quantize,gemm,mlp,fp4,awq,attention]
 
 Prints one JSON object per kernel and shape.  Synthetic seeded inputs with the benchmark configurations' shapes.
 """
@@ -73,7 +73,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--only", default="quantize,gemm,fp4,awq,attention")
+    ap.add_argument("--only", default="quantize,gemm,mlp,fp4,awq,attention")
     args = ap.parse_args()
     only = set(args.only.split(","))
     dev = torch.device("cuda", 0)
@@ -130,6 +130,31 @@ def main():
             emit("prepack_kernel + gemm_tc_kernel", f"{name}: M={M} K={K} N={N} R={R}", ms, best, 2.0 * M * N * K, "TFLOP/s",
                  "tensor", i8, src + " x2 (8-bit pipe)")
             del sets
+
+    # ---------------------------------------------------------------- transformer MLP pair through the layer API
+    if "mlp" in only:
+        from nunchaku_rocm_b200.models.linear import SVDQW4A4Linear
+        from nunchaku_rocm_b200.ops.fused import fused_gelu_mlp
+
+        def rand_layer(cin, cout, unsigned, seed):
+            g = torch.Generator(device=dev).manual_seed(seed)
+            lin = SVDQW4A4Linear(cin, cout, rank=R, bias=True, precision="int4", act_unsigned=unsigned, torch_dtype=T, device=dev)
+            with torch.no_grad():
+                lin.qweight.copy_(torch.randint(-128, 128, lin.qweight.shape, dtype=torch.int8, generator=g, device=dev))
+                lin.wscales.copy_((torch.rand(lin.wscales.shape, generator=g, device=dev) * 0.015 + 0.005).to(T))
+                lin.bias.copy_((torch.randn(cout, generator=g, device=dev) * 0.1).to(T))
+                lin.smooth_factor.copy_((torch.rand(cin, generator=g, device=dev) + 0.5).to(T))
+                lin.proj_down.copy_((torch.randn(cin, R, generator=g, device=dev) * 0.02).to(T))
+                lin.proj_up.copy_((torch.randn(cout, R, generator=g, device=dev) * 0.02).to(T))
+            return lin
+
+        fc1, fc2 = rand_layer(3072, 12288, False, 1), rand_layer(12288, 3072, True, 2)
+        for Mm in (256, 1024, 4608, 8192):
+            g = torch.Generator(device=dev).manual_seed(Mm)
+            sets = [dict(x=torch.randn(1, Mm, 3072, generator=g, device=dev).to(T)) for _ in range(3)]
+            ms, best = time_ms(lambda p: fused_gelu_mlp(p["x"], fc1, fc2), sets, max(10, args.iters // 2), args.warmup)
+            emit("fused_gelu_mlp (quantize, fc1 GEMM, GELU + requant, fc2 GEMM)", f"M={Mm} 3072->12288->3072 R={R}", ms, best,
+                 2.0 * Mm * 12288 * 3072 * 2, "TFLOP/s", "tensor", i8, src + " x2 (8-bit pipe)")
 
     # ---------------------------------------------------------------- NVFP4 GEMM (block-scaled tensor pipe)
     if "fp4" in only:
