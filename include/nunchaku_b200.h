@@ -198,8 +198,14 @@ typedef struct nb_attn_args {
     int64_t stride_kb, stride_kh, stride_kn;
     int64_t stride_vb, stride_vh, stride_vn;
     int64_t stride_ob, stride_om;
+    void* scratch;         /* device scratch of nb_attention_scratch_bytes() bytes, 256-byte aligned; may be null when that is 0 */
+    int64_t scratch_bytes;
+    void* status;          /* device int32 a kernel sets non-zero if a bounded wait expires; may be null */
+    int32_t impl;          /* NB_IMPL_AUTO: tcgen05 kernel for D = 128, else the mma.sync kernel; NB_IMPL_GENERIC: mma.sync */
 } nb_attn_args;
 int nb_attention(const nb_attn_args* args, void* stream);
+/* Scratch the call needs: the tcgen05 kernel keeps the pre-scaled Q and the transposed V there; 0 for the mma.sync kernel. */
+int64_t nb_attention_scratch_bytes(const nb_attn_args* args);
 
 /* Diagnostics (the reference's `status()` / error plumbing, nunchaku/ops/triton/native/hip.py:110-116). */
 const char* nb_strerror(int status);

@@ -83,6 +83,7 @@ class AttnArgs(C.Structure):
                 "stride_ob", "stride_om",
             )
         ]
+        + [("scratch", C.c_void_p), ("scratch_bytes", C.c_int64), ("status", C.c_void_p), ("impl", C.c_int32)]
     )
 
 
@@ -116,6 +117,9 @@ def lib() -> C.CDLL:
                 l.nb_gemm_w4a4_uses_tcgen05.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_int]
                 l.nb_gemm_w4a4_group_sums.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_void_p]
                 l.nb_quantize_w4a4.argtypes = [C.POINTER(QuantArgs), C.c_void_p]
+                l.nb_attention.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
+                l.nb_attention_scratch_bytes.argtypes = [C.POINTER(AttnArgs)]
+                l.nb_attention_scratch_bytes.restype = C.c_int64
                 l.nb_qk_norm_rope.argtypes = [
                     C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_int32, C.POINTER(QKArgs), C.c_void_p,
                 ]

@@ -7,8 +7,8 @@
 // A CTA of 8 warps owns 128 query rows of one (batch, head); each warp owns 16 rows and keeps its Q
 // fragments, the 16 x 64 score tile and the 16 x D output accumulator in registers.  K and V tiles of 64
 // keys are double-buffered in shared memory with cp.async, in 16-byte units XOR-swizzled by the row so that
-// ldmatrix reads are conflict-free.  The matrix products run on mma.sync.m16n8k16 (the tcgen05 version of
-// this kernel is the next step for this operator).
+// ldmatrix reads are conflict-free.  The matrix products run on mma.sync.m16n8k16.  This kernel takes the calls the
+// tcgen05 kernel does not (head dimension 64, unaligned outputs, callers without scratch).
 #include "nb_common.cuh"
 
 namespace nb {
@@ -228,9 +228,35 @@ int launch_attn(const nb_attn_args* a, cudaStream_t s) {
 }  // namespace
 }  // namespace nb
 
+namespace nb {
+const char* attn_tc_unsupported_reason(const nb_attn_args* a);
+int64_t attn_tc_scratch_bytes(const nb_attn_args* a);
+int launch_attention_tc(const nb_attn_args* a, cudaStream_t s);
+
+static bool attn_common_ok(const nb_attn_args* a) {
+    if (!a || !a->q || !a->k || !a->v || !a->o) return false;
+    if (a->dtype != NB_DTYPE_BF16 && a->dtype != NB_DTYPE_FP16) return false;
+    const long long strides[] = {a->stride_qb, a->stride_qh, a->stride_qm, a->stride_kb, a->stride_kh, a->stride_kn,
+                                 a->stride_vb, a->stride_vh, a->stride_vn};
+    for (long long st : strides)
+        if (st % 8) return false;
+    return aligned16(a->q) && aligned16(a->k) && aligned16(a->v);
+}
+static bool attn_uses_tc(const nb_attn_args* a) {
+    return a->impl != NB_IMPL_GENERIC && attn_common_ok(a) && attn_tc_unsupported_reason(a) == nullptr;
+}
+}  // namespace nb
+
+extern "C" int64_t nb_attention_scratch_bytes(const nb_attn_args* a) {
+    if (!a || a->B <= 0 || a->H <= 0) return 0;
+    return nb::attn_uses_tc(a) ? nb::attn_tc_scratch_bytes(a) : 0;
+}
+
 extern "C" int nb_attention(const nb_attn_args* a, void* stream) {
     using namespace nb;
     NB_REQUIRE(a && a->q && a->k && a->v && a->o);
+    if (a->impl == NB_IMPL_TCGEN05 && !attn_uses_tc(a)) return NB_ERR_UNSUPPORTED;
+    if (a->B > 0 && a->H > 0 && attn_uses_tc(a)) return launch_attention_tc(a, static_cast<cudaStream_t>(stream));
     NB_REQUIRE(a->B > 0 && a->H > 0 && a->Tq >= 0 && a->Tkv >= 0);
     NB_REQUIRE(a->dtype == NB_DTYPE_BF16 || a->dtype == NB_DTYPE_FP16);
     if (a->D != 64 && a->D != 128) return NB_ERR_UNSUPPORTED;

@@ -1,0 +1,513 @@
+// Unmasked flash attention on the 5th-generation tensor cores (tcgen05.mma kind::f16, accumulators and the
+// probability tile in tensor memory), head dimension 128.
+//
+// Rounding points follow the reference kernel (nunchaku/ops/triton/attention.py:61-117): q * scale * log2(e) is rounded
+// to the input dtype, scores and the running max / sum are fp32 in base 2, the probabilities are rounded to the input
+// dtype before P @ V, the accumulator is fp32, one division by the row sum at the end.  One liberty that does not change
+// the result beyond fp32 rounding: the running maximum a row subtracts is only raised when the true maximum has grown by
+// more than 8 (probabilities stay below 2^8), which makes the rescaling of the output accumulator a rare event.
+//
+// Two launches:
+//  1. `attn_prepack_kernel`: Q' = T(q * scale * log2 e) as (B H, Tq rounded up to 128, 128), and V transposed to
+//     (B H, 128, Tkv rounded up to 8) so that both MMAs read K-major operands; pad rows / columns are zero.
+//  2. `attention_tc_kernel`: a CTA owns 128 query rows of one (batch, head) and walks the keys in tiles of 128.
+//       warp 0    TMA producer: Q' once; K tiles straight from the caller's strided tensor (4-D tensor map) and
+//                 V^T tiles through two-stage rings (128-byte swizzle, no multicast).
+//       warp 1    MMA issuer: S_j = Q' K_j^T (8 MMAs, N = 128) into one of two score slots, then O += P_{j-1} V_{j-1}
+//                 with P read from tensor memory as the A operand; S_j is issued before P_{j-1} is waited for, so the
+//                 tensor pipe works on the next scores while the CUDA cores do the softmax of the current tile.
+//       warps 2-5 softmax, one row per thread (tcgen05.ld 32x32b): row max, exp2, row sum, P -> tensor memory
+//                 (tcgen05.st), the occasional rescale of O in tensor memory, and the final O / l store.
+//     Tensor memory: S0 | S1 | O | P0 | P1 = 128 + 128 + 128 + 64 + 64 columns.
+// Every mbarrier wait is bounded; on expiry the CTA records a code in the status word and unwinds.
+#include <cuda.h>
+
+#include <algorithm>
+#include <type_traits>
+
+#include "nb_common.cuh"
+
+namespace nb {
+namespace atc {
+
+constexpr int BM = 128, BN = 128, HD = 128;
+constexpr int NTHREADS = 192;
+constexpr int TILE = 128 * 128 * 2;  // bytes of a 128 x 128 16-bit tile (two 64-wide halves of 16 KB)
+constexpr int OFF_Q = 0, OFF_K = TILE, OFF_V = 3 * TILE, OFF_BAR = 5 * TILE;
+constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+constexpr uint32_t TM_S = 0, TM_O = 256, TM_P = 384;
+
+enum { B_Q = 0, B_KF = 1, B_KE = 3, B_VF = 5, B_VE = 7, B_SF = 9, B_SE = 11, B_PF = 13, B_PV = 15, B_COUNT = 17 };
+enum { E_PROD = 0x210, E_MMA = 0x230, E_SM = 0x240 };
+
+struct Params {
+    void* o;
+    int Tq, Tkv, H;
+    long long stride_ob, stride_om;
+    int tq_pad;  // rows of Q' per (batch, head)
+    int* status;
+};
+
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// A operand from tensor memory (row = lane, two 16-bit values per column), B from shared memory
+__device__ __forceinline__ void mma_f16_ts(uint32_t d, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
+        "%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
+        "%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NTHREADS, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_v, const int4 kperm, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t s_base = smem_u32(smem);
+    const uint32_t s_bar = s_base + OFF_BAR;
+    uint32_t* tmem_ptr_s = reinterpret_cast<uint32_t*>(smem + OFF_BAR + 8 * B_COUNT);
+    volatile int* abort_s = reinterpret_cast<volatile int*>(smem + OFF_BAR + 8 * B_COUNT + 8);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    auto bar = [&](int i) { return s_bar + 8u * i; };
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar(B_Q), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(B_KF + i), 1); mbar_init(bar(B_KE + i), 1);
+            mbar_init(bar(B_VF + i), 1); mbar_init(bar(B_VE + i), 1);
+            mbar_init(bar(B_SF + i), 1); mbar_init(bar(B_SE + i), 4);
+            mbar_init(bar(B_PF + i), 4); mbar_init(bar(B_PV + i), 1);
+        }
+        *abort_s = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_ptr_s), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_s;
+
+    const int m0 = blockIdx.x * BM, head = blockIdx.y, batch = blockIdx.z;
+    const int bh = batch * p.H + head;
+    const int NT = (p.Tkv + BN - 1) / BN;
+
+    if (warp == 0) {
+        // ================================ producer ================================
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+            mbar_expect_tx(bar(B_Q), TILE);
+            tma_load_2d(s_base + OFF_Q, &tm_q, bar(B_Q), 0, bh * p.tq_pad + m0);
+            tma_load_2d(s_base + OFF_Q + TILE / 2, &tm_q, bar(B_Q), 64, bh * p.tq_pad + m0);
+            bool ok = true;
+            for (int j = 0; j < NT && ok; ++j) {
+                const int s = j & 1;
+                const uint32_t par = ((j >> 1) & 1) ^ 1;
+                if (!mbar_wait(bar(B_KE + s), par, abort_s, E_PROD | 1, 500)) { ok = false; break; }
+                mbar_expect_tx(bar(B_KF + s), TILE);
+                {
+                    // coordinates (d, key, head, batch) in the order the tensor map sorted the outer dimensions by stride
+                    int c[4];
+                    c[0] = 0;
+                    c[kperm.x] = j * BN; c[kperm.y] = head; c[kperm.z] = batch;
+                    tma_load_4d(s_base + OFF_K + s * TILE, &tm_k, bar(B_KF + s), 0, c[1], c[2], c[3]);
+                    tma_load_4d(s_base + OFF_K + s * TILE + TILE / 2, &tm_k, bar(B_KF + s), 64, c[1], c[2], c[3]);
+                }
+                if (!mbar_wait(bar(B_VE + s), par, abort_s, E_PROD | 2, 500)) { ok = false; break; }
+                mbar_expect_tx(bar(B_VF + s), TILE);
+                tma_load_2d(s_base + OFF_V + s * TILE, &tm_v, bar(B_VF + s), j * BN, bh * HD);
+                tma_load_2d(s_base + OFF_V + s * TILE + TILE / 2, &tm_v, bar(B_VF + s), j * BN + 64, bh * HD);
+            }
+            if (!ok) {
+                // let copies already in flight land before the CTA goes away (bounded)
+                uint64_t t0 = globaltimer_ns();
+                while (globaltimer_ns() - t0 < 100000000ull) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ================================ MMA issuer ================================
+        if (lane == 0) {
+            const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+            const uint32_t idesc = umma_idesc(1u, fmt, fmt, 128);
+            bool ok = mbar_wait(bar(B_Q), 0, abort_s, E_MMA | 1, 100);
+            auto pv = [&](int i) -> bool {
+                const int b = i & 1;
+                const uint32_t par = (i >> 1) & 1;
+                if (!mbar_wait(bar(B_PF + b), par, abort_s, E_MMA | 4, 100)) return false;
+                if (!mbar_wait(bar(B_VF + b), par, abort_s, E_MMA | 5, 100)) return false;
+                tc_fence_after();
+                const uint32_t v_addr = s_base + OFF_V + b * TILE;
+#pragma unroll
+                for (int kh = 0; kh < 2; ++kh)
+#pragma unroll
+                    for (int st = 0; st < 4; ++st)
+                        mma_f16_ts(tmem_base + TM_O, tmem_base + TM_P + b * 64 + (kh * 4 + st) * 8,
+                                   desc_sw128(v_addr + kh * (TILE / 2) + st * 32), idesc, (i > 0 || kh || st) ? 1u : 0u);
+                tc_commit(bar(B_PV + b));
+                tc_commit(bar(B_VE + b));
+                return true;
+            };
+            for (int j = 0; j < NT && ok; ++j) {
+                const int b = j & 1;
+                const uint32_t par = (j >> 1) & 1;
+                if (!mbar_wait(bar(B_KF + b), par, abort_s, E_MMA | 2, 100)) { ok = false; break; }
+                if (!mbar_wait(bar(B_SE + b), par ^ 1, abort_s, E_MMA | 3, 100)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t q_addr = s_base + OFF_Q, k_addr = s_base + OFF_K + b * TILE;
+#pragma unroll
+                for (int dh = 0; dh < 2; ++dh)
+#pragma unroll
+                    for (int st = 0; st < 4; ++st)
+                        mma_f16(tmem_base + TM_S + b * 128, desc_sw128(q_addr + dh * (TILE / 2) + st * 32),
+                                desc_sw128(k_addr + dh * (TILE / 2) + st * 32), idesc, (dh || st) ? 1u : 0u);
+                tc_commit(bar(B_SF + b));
+                tc_commit(bar(B_KE + b));
+                if (j >= 1) ok = pv(j - 1);
+            }
+            if (ok && NT > 0) pv(NT - 1);
+        }
+    } else {
+        // ================================ softmax ================================
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < NT && ok; ++j) {
+            const int b = j & 1;
+            const uint32_t par = (j >> 1) & 1;
+            if (!mbar_wait_warp(bar(B_SF + b), par, abort_s, E_SM | 1, 100)) { ok = false; break; }
+            tc_fence_after();
+            float s[128];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(lane_addr + TM_S + b * 128 + c * 32, *reinterpret_cast<float(*)[32]>(&s[c * 32]));
+            tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_SE + b));  // the score slot may be overwritten by tile j + 2
+            if (j == NT - 1 && (p.Tkv & (BN - 1))) {
+                const int valid = p.Tkv - j * BN;
+#pragma unroll
+                for (int i = 0; i < 128; ++i)
+                    if (i >= valid) s[i] = -INFINITY;
+            }
+            float mx = s[0];
+#pragma unroll
+            for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+            // raise the subtracted maximum only when it lags by more than 8 (or at the first tile)
+            const bool need = mx > m_used + 8.0f;
+            if (__any_sync(0xffffffffu, need)) {
+                const float m_new = fmaxf(m_used, mx);
+                if (j > 0) {
+                    // O must hold every product issued so far before it is rescaled
+                    if (!mbar_wait_warp(bar(B_PV + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_s, E_SM | 2, 100)) { ok = false; break; }
+                    tc_fence_after();
+                    const float alpha = ex2(m_used - m_new);
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        float o[32];
+                        uint32_t w[32];
+                        tmem_ld32(lane_addr + TM_O + c * 32, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(o[i] * alpha);
+                        tmem_st32(lane_addr + TM_O + c * 32, w);
+                    }
+                    tmem_wait_st();
+                    l *= alpha;
+                }
+                m_used = m_new;
+            }
+            // probabilities: fp32 for the row sum, rounded to T for the product
+            uint32_t pk[64];
+            float sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+                const float p0 = ex2(s[2 * i] - m_used), p1 = ex2(s[2 * i + 1] - m_used);
+                sum += p0 + p1;
+                pk[i] = pack2<T>(p0, p1);
+            }
+            l += sum;
+            // the P slot is free once the product that read it two tiles ago has completed
+            if (j >= 2 && !mbar_wait_warp(bar(B_PV + b), ((j - 2) >> 1) & 1, abort_s, E_SM | 3, 100)) { ok = false; break; }
+            tc_fence_after();
+            tmem_st32(lane_addr + TM_P + b * 64, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
+            tmem_st32(lane_addr + TM_P + b * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_PF + b));
+        }
+        if (ok && NT > 0 && mbar_wait_warp(bar(B_PV + ((NT - 1) & 1)), ((NT - 1) >> 1) & 1, abort_s, E_SM | 4, 100)) {
+            tc_fence_after();
+            const int m = m0 + row;
+            const float inv = 1.0f / (l == 0.f ? 1.0f : l);
+            T* og = static_cast<T*>(p.o) + (long long)batch * p.stride_ob + (long long)m * p.stride_om + (long long)head * HD;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                float o[32];
+                tmem_ld32(lane_addr + TM_O + c * 32, o);
+                tmem_wait_ld();
+                if (m < p.Tq) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        uint4 w;
+                        w.x = pack2<T>(o[8 * u] * inv, o[8 * u + 1] * inv);
+                        w.y = pack2<T>(o[8 * u + 2] * inv, o[8 * u + 3] * inv);
+                        w.z = pack2<T>(o[8 * u + 4] * inv, o[8 * u + 5] * inv);
+                        w.w = pack2<T>(o[8 * u + 6] * inv, o[8 * u + 7] * inv);
+                        *reinterpret_cast<uint4*>(og + c * 32 + u * 8) = w;
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_s && p.status) atomicCAS(p.status, 0, *abort_s);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// pre-pass: Q' = T(q * scale * log2 e) with zero pad rows; V^T with zero pad columns
+// ------------------------------------------------------------------------------------------------
+struct PrepackParams {
+    const void* q; const void* v; void* qs; void* vt;
+    int B, H, Tq, Tkv, tq_pad, tkv_pad;
+    float qscale;
+    long long stride_qb, stride_qh, stride_qm, stride_vb, stride_vh, stride_vn;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) attn_prepack_q_kernel(const PrepackParams p) {
+    const long long tid = (long long)blockIdx.x * 256 + threadIdx.x;  // one 16-byte unit of Q'
+    const long long total = (long long)p.B * p.H * p.tq_pad * (HD / 8);
+    if (tid >= total) return;
+    const int u = (int)(tid % (HD / 8));
+    const long long r = tid / (HD / 8);
+    const int m = (int)(r % p.tq_pad);
+    const int bh = (int)(r / p.tq_pad);
+    uint4 o = make_uint4(0, 0, 0, 0);
+    if (m < p.Tq) {
+        const T* src = static_cast<const T*>(p.q) + (long long)(bh / p.H) * p.stride_qb + (long long)(bh % p.H) * p.stride_qh +
+                       (long long)m * p.stride_qm + u * 8;
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        uint32_t z[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = unpack2<T>(w[i]);
+            z[i] = pack2<T>(f.x * p.qscale, f.y * p.qscale);
+        }
+        o = make_uint4(z[0], z[1], z[2], z[3]);
+    }
+    reinterpret_cast<uint4*>(p.qs)[tid] = o;
+}
+
+// one block transposes 64 keys x 64 d of one (batch, head)
+template <typename T>
+__global__ void __launch_bounds__(256) attn_prepack_vt_kernel(const PrepackParams p) {
+    __shared__ uint16_t tile[64][64 + 2];
+    const int k0 = blockIdx.x * 64, d0 = blockIdx.y * 64, bh = blockIdx.z;
+    const uint16_t* v = reinterpret_cast<const uint16_t*>(p.v) + (long long)(bh / p.H) * p.stride_vb + (long long)(bh % p.H) * p.stride_vh;
+    for (int i = threadIdx.x; i < 64 * 8; i += 256) {
+        const int kr = i >> 3, u = i & 7;
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (k0 + kr < p.Tkv) raw = __ldg(reinterpret_cast<const uint4*>(v + (long long)(k0 + kr) * p.stride_vn + d0 + u * 8));
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            tile[kr][u * 8 + 2 * e] = (uint16_t)(w[e] & 0xFFFFu);
+            tile[kr][u * 8 + 2 * e + 1] = (uint16_t)(w[e] >> 16);
+        }
+    }
+    __syncthreads();
+    uint16_t* vt = reinterpret_cast<uint16_t*>(p.vt) + ((long long)bh * HD + d0) * p.tkv_pad;
+    for (int i = threadIdx.x; i < 64 * 8; i += 256) {
+        const int dr = i >> 3, u = i & 7;
+        if (k0 + u * 8 < p.tkv_pad) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) w[e] = (uint32_t)tile[u * 8 + 2 * e][dr] | ((uint32_t)tile[u * 8 + 2 * e + 1][dr] << 16);
+            *reinterpret_cast<uint4*>(vt + (long long)dr * p.tkv_pad + k0 + u * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+static bool make_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, const void* base, const cuuint64_t* dims,
+                     const cuuint64_t* strides_bytes, const cuuint32_t* box) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    return fn(m, dt, rank, const_cast<void*>(base), dims, strides_bytes, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static inline size_t up256(size_t x) { return (x + 255) & ~size_t(255); }
+struct Scratch { size_t qs, vt, total; int tq_pad, tkv_pad; };
+static Scratch scratch_layout(const nb_attn_args* a) {
+    Scratch s;
+    s.tq_pad = (a->Tq + BM - 1) / BM * BM;
+    s.tkv_pad = (a->Tkv + 7) / 8 * 8;
+    const size_t bh = (size_t)a->B * a->H;
+    s.qs = 0;
+    s.vt = up256(bh * s.tq_pad * HD * 2);
+    s.total = s.vt + up256(bh * HD * s.tkv_pad * 2);
+    return s;
+}
+
+template <typename T>
+static int launch_t(const nb_attn_args* a, cudaStream_t s) {
+    const Scratch sc = scratch_layout(a);
+    if (!a->scratch || a->scratch_bytes < (int64_t)sc.total || (reinterpret_cast<uintptr_t>(a->scratch) & 255))
+        return NB_ERR_INVALID;
+    uint8_t* base = static_cast<uint8_t*>(a->scratch);
+    PrepackParams pp;
+    pp.q = a->q; pp.v = a->v; pp.qs = base + sc.qs; pp.vt = base + sc.vt;
+    pp.B = a->B; pp.H = a->H; pp.Tq = a->Tq; pp.Tkv = a->Tkv; pp.tq_pad = sc.tq_pad; pp.tkv_pad = sc.tkv_pad;
+    pp.qscale = a->scale * 1.4426950408889634f;
+    pp.stride_qb = a->stride_qb; pp.stride_qh = a->stride_qh; pp.stride_qm = a->stride_qm;
+    pp.stride_vb = a->stride_vb; pp.stride_vh = a->stride_vh; pp.stride_vn = a->stride_vn;
+    const long long bh = (long long)a->B * a->H;
+    const long long q_units = bh * sc.tq_pad * (HD / 8);
+    attn_prepack_q_kernel<T><<<(unsigned)((q_units + 255) / 256), 256, 0, s>>>(pp);
+    NB_CUDA_CHECK(cudaGetLastError());
+    attn_prepack_vt_kernel<T><<<dim3((a->Tkv + 63) / 64, HD / 64, (unsigned)bh), 256, 0, s>>>(pp);
+    NB_CUDA_CHECK(cudaGetLastError());
+
+    const CUtensorMapDataType t16 = std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                          : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap tm_q, tm_k, tm_v;
+    bool ok;
+    {
+        cuuint64_t dims[2] = {HD, (cuuint64_t)bh * sc.tq_pad};
+        cuuint64_t str[1] = {HD * 2};
+        cuuint32_t box[2] = {64, BM};
+        ok = make_map(&tm_q, t16, 2, pp.qs, dims, str, box);
+    }
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)sc.tkv_pad, (cuuint64_t)bh * HD};
+        cuuint64_t str[1] = {(cuuint64_t)sc.tkv_pad * 2};
+        cuuint32_t box[2] = {64, HD};
+        ok = ok && make_map(&tm_v, t16, 2, pp.vt, dims, str, box);
+    }
+    int4 kperm;
+    {
+        // K from the caller's strided (B, H, T, D) view: the outer dimensions sorted by stride, as the encoder wants them
+        struct Dim { cuuint64_t size, stride; int role; } d[3] = {{(cuuint64_t)a->Tkv, (cuuint64_t)a->stride_kn * 2, 0},
+                                                                   {(cuuint64_t)a->H, (cuuint64_t)a->stride_kh * 2, 1},
+                                                                   {(cuuint64_t)a->B, (cuuint64_t)a->stride_kb * 2, 2}};
+        std::stable_sort(d, d + 3, [](const Dim& x, const Dim& y) { return x.stride < y.stride; });
+        cuuint64_t dims[4] = {HD, d[0].size, d[1].size, d[2].size};
+        cuuint64_t str[3] = {d[0].stride, d[1].stride, d[2].stride};
+        cuuint32_t box[4] = {64, 1, 1, 1};
+        int pos[3];
+        for (int i = 0; i < 3; ++i) {
+            pos[d[i].role] = i + 1;
+            if (d[i].role == 0) box[i + 1] = BN;
+        }
+        kperm = make_int4(pos[0], pos[1], pos[2], 0);
+        // a dimension of size 1 may carry any stride; give it a valid one
+        for (int i = 0; i < 3; ++i)
+            if (str[i] == 0 || str[i] % 16) str[i] = 16;
+        ok = ok && make_map(&tm_k, t16, 4, a->k, dims, str, box);
+    }
+    if (!ok) return NB_ERR_UNSUPPORTED;
+
+    Params p = {};
+    p.o = a->o; p.Tq = a->Tq; p.Tkv = a->Tkv; p.H = a->H;
+    p.stride_ob = a->stride_ob; p.stride_om = a->stride_om;
+    p.tq_pad = sc.tq_pad;
+    p.status = static_cast<int*>(a->status);
+    auto kern = attention_tc_kernel<T>;
+    NB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    kern<<<dim3(sc.tq_pad / BM, a->H, a->B), NTHREADS, SMEM_BYTES, s>>>(tm_q, tm_k, tm_v, kperm, p);
+    NB_CUDA_CHECK(cudaGetLastError());
+    return NB_OK;
+}
+
+}  // namespace atc
+
+// Why the tcgen05 kernel cannot take this attention call, or nullptr.
+const char* attn_tc_unsupported_reason(const nb_attn_args* a) {
+    if (a->D != 128) return "head dimension";
+    if (a->Tq < 1 || a->Tkv < 1) return "empty";
+    if (!aligned16(a->o) || a->stride_om % 8 || a->stride_ob % 8) return "output alignment";
+    if (a->B > 65535 || a->H > 65535) return "grid";
+    return nullptr;
+}
+int64_t attn_tc_scratch_bytes(const nb_attn_args* a) { return (int64_t)atc::scratch_layout(a).total; }
+int launch_attention_tc(const nb_attn_args* a, cudaStream_t s) {
+    return a->dtype == NB_DTYPE_BF16 ? atc::launch_t<__nv_bfloat16>(a, s) : atc::launch_t<__half>(a, s);
+}
+
+}  // namespace nb

@@ -84,19 +84,32 @@ def test_awq_gemm_and_linear(cuda_dev, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("impl", [0, 2])  # 0: automatic (tcgen05 kernel for D = 128), 2: the mma.sync kernel
 @pytest.mark.parametrize(
-    "B,H,TQ,TKV,D", [(2, 8, 256, 256, 64), (1, 4, 128, 512, 128), (2, 2, 100, 77, 64), (1, 3, 333, 1000, 128)]
+    "B,H,TQ,TKV,D",
+    [(2, 8, 256, 256, 64), (1, 4, 128, 512, 128), (2, 2, 100, 77, 64), (1, 3, 333, 1000, 128), (2, 3, 640, 1, 128),
+     (1, 2, 130, 129, 128)],
 )
-def test_attention(cuda_dev, dtype, B, H, TQ, TKV, D):
+def test_attention(cuda_dev, dtype, impl, B, H, TQ, TKV, D):
+    from nunchaku_rocm_b200 import _lib
     from nunchaku_rocm_b200.ops.triton.attention import attention_fp16
 
+    if impl == 2 and D == 64:
+        pytest.skip("D = 64 always runs on the mma.sync kernel; covered by impl 0")
     g = torch.Generator().manual_seed(TQ)
     q = torch.randn(B, H, TQ, D, generator=g).to(dtype)
     k = torch.randn(B, H, TKV, D, generator=g).to(dtype)
     v = torch.randn(B, H, TKV, D, generator=g).to(dtype)
+    # larger scores in some rows, so that the running maximum grows a lot along the keys
+    q[:, :, ::7] *= 6.0
     o = torch.empty(B, TQ, H * D, dtype=dtype, device=cuda_dev)
-    attention_fp16(q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev), o, D**-0.5)
-    torch.testing.assert_close(o.float().cpu(), awq_attn.attention_exact(q, k, v, D**-0.5), rtol=3e-2, atol=3e-2)
+    attention_fp16(q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev), o, D**-0.5, _impl=impl)
+    torch.cuda.synchronize(cuda_dev)
+    assert _lib.device_status(cuda_dev) == 0
+    # against exact fp32 attention: the reference's bar (rtol 3e-2); the rows with scores scaled by 6 make the bf16 rounding
+    # of q * scale * log2(e) visible, hence the wider absolute bar for bf16
+    tol = 3e-2 if dtype == torch.float16 else 6e-2
+    torch.testing.assert_close(o.float().cpu(), awq_attn.attention_exact(q, k, v, D**-0.5), rtol=3e-2, atol=tol)
     # against the oracle with the kernel's rounding points: one 16-bit rounding step
     eps = 2.0**-7 if dtype == torch.bfloat16 else 2.0**-10
     torch.testing.assert_close(o.float().cpu(), awq_attn.attention(q, k, v, D**-0.5), rtol=2 * eps, atol=2 * eps)
