@@ -207,6 +207,15 @@ int nb_attention(const nb_attn_args* args, void* stream);
 /* Scratch the call needs: the tcgen05 kernel keeps the pre-scaled Q and the transposed V there; 0 for the mma.sync kernel. */
 int64_t nb_attention_scratch_bytes(const nb_attn_args* args);
 
+/*
+ * Self-test on the current device, the role of the reference's native self-test (nunchaku/ops/triton/native/w4a4.py:537-651):
+ * a small seeded W4A4 problem with bias and a rank-16 branch runs on the tensor-core kernel and on the generic kernel;
+ * the exact integer group sums must be equal and the 16-bit outputs must agree to two rounding steps.  Allocates and
+ * frees its own few hundred KB of device memory and synchronises the device.  Returns NB_OK, or NB_ERR_DEVICE on a
+ * mismatch.
+ */
+int nb_selftest(void);
+
 /* Diagnostics (the reference's `status()` / error plumbing, nunchaku/ops/triton/native/hip.py:110-116). */
 const char* nb_strerror(int status);
 int nb_last_cuda_error(void);          /* cudaError_t of the last NB_ERR_LAUNCH, cleared by reading */

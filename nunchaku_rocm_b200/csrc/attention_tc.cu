@@ -238,9 +238,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 for (int i = 0; i < 128; ++i)
                     if (i >= valid) s[i] = -INFINITY;
             }
-            float mx = s[0];
+            // one thread per row means no other warp hides this thread's latencies: keep the reductions shallow
+            float m8[8];
 #pragma unroll
-            for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+            for (int i = 0; i < 8; ++i) m8[i] = s[i];
+#pragma unroll
+            for (int i = 8; i < 128; ++i) m8[i & 7] = fmaxf(m8[i & 7], s[i]);
+            const float mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
             // raise the subtracted maximum only when it lags by more than 8 (or at the first tile)
             const bool need = mx > m_used + 8.0f;
             if (__any_sync(0xffffffffu, need)) {
@@ -267,14 +271,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             }
             // probabilities: fp32 for the row sum, rounded to T for the product
             uint32_t pk[64];
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < 64; ++i) {
                 const float p0 = ex2(s[2 * i] - m_used), p1 = ex2(s[2 * i + 1] - m_used);
-                sum += p0 + p1;
+                sum4[i & 3] += p0 + p1;
                 pk[i] = pack2<T>(p0, p1);
             }
-            l += sum;
+            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             // the P slot is free once the product that read it two tiles ago has completed
             if (j >= 2 && !mbar_wait_warp(bar(B_PV + b), ((j - 2) >> 1) & 1, abort_s, E_SM | 3, 100)) { ok = false; break; }
             tc_fence_after();

@@ -415,6 +415,14 @@ def test_gemm_fp4_shapes_lora_bias(cuda_dev, dtype, impl, M, N, K, R):
     _status_clean(cuda_dev)
 
 
+def test_library_selftest(cuda_dev):
+    # the C-level self-test (tensor-core kernel against the generic one) that a host without Python can call
+    from nunchaku_rocm_b200 import _lib
+
+    with torch.cuda.device(cuda_dev):
+        assert _lib.lib().nb_selftest() == 0
+
+
 def test_gemm_fp4_tensor_core_kernel_is_selected(cuda_dev):
     # the shapes above with K % 256 == 0 must run on the block-scaled kernel, not silently on the generic one
     import ctypes as C
