@@ -13,11 +13,13 @@
 //  2. `attention_tc_kernel`: a CTA owns 128 query rows of one (batch, head) and walks the keys in tiles of 128.
 //       warp 0    TMA producer: Q' once; K tiles straight from the caller's strided tensor (4-D tensor map) and
 //                 V^T tiles through two-stage rings (128-byte swizzle, no multicast).
-//       warp 1    MMA issuer: S_j = Q' K_j^T (8 MMAs, N = 128) into one of two score slots, then O += P_{j-1} V_{j-1}
-//                 with P read from tensor memory as the A operand; S_j is issued before P_{j-1} is waited for, so the
-//                 tensor pipe works on the next scores while the CUDA cores do the softmax of the current tile.
-//       warps 2-5 softmax, one row per thread (tcgen05.ld 32x32b): row max, exp2, row sum, P -> tensor memory
-//                 (tcgen05.st), the occasional rescale of O in tensor memory, and the final O / l store.
+//       warp 1    MMA issuer for the scores: S_j = Q' K_j^T (8 MMAs, N = 128) into one of two score slots, so the tensor
+//                 pipe works on the next scores while the CUDA cores do the softmax of the current tile.
+//       warp 10   MMA issuer for O += P_j V_j, with P read from tensor memory as the A operand.
+//       warps 2-9 softmax: two warps per 32-row lane quarter, each with one row per thread and half of the 128 columns
+//                 (tcgen05.ld 32x32b): partial row max exchanged with the partner through shared memory, exp2, partial
+//                 row sum, P -> tensor memory (tcgen05.st), the occasional rescale of O in tensor memory, and the
+//                 final O / l store.  Two warps per scheduler hide each other's latencies.
 //     Tensor memory: S0 | S1 | O | P0 | P1 = 128 + 128 + 128 + 64 + 64 columns.
 // Every mbarrier wait is bounded; on expiry the CTA records a code in the status word and unwinds.
 #include <cuda.h>
@@ -31,13 +33,15 @@ namespace nb {
 namespace atc {
 
 constexpr int BM = 128, BN = 128, HD = 128;
-constexpr int NTHREADS = 192;
+constexpr int SM_WARPS = 8;
+constexpr int NTHREADS = 64 + SM_WARPS * 32 + 32;  // producer, score issuer, softmax warps, P V issuer
 constexpr int TILE = 128 * 128 * 2;  // bytes of a 128 x 128 16-bit tile (two 64-wide halves of 16 KB)
-constexpr int OFF_Q = 0, OFF_K = TILE, OFF_V = 3 * TILE, OFF_BAR = 5 * TILE;
+constexpr int OFF_Q = 0, OFF_K = TILE, OFF_V = 3 * TILE, OFF_XCH = 5 * TILE;  // exchange: [2 tiles][2 halves][128] max, [2][128] sum
+constexpr int OFF_BAR = OFF_XCH + 6 * 128 * 4;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
 constexpr uint32_t TM_S = 0, TM_O = 256, TM_P = 384;
 
-enum { B_Q = 0, B_KF = 1, B_KE = 3, B_VF = 5, B_VE = 7, B_SF = 9, B_SE = 11, B_PF = 13, B_PV = 15, B_COUNT = 17 };
+enum { B_Q = 0, B_KF = 1, B_KE = 3, B_VF = 5, B_VE = 7, B_SF = 9, B_SE = 11, B_PF = 13, B_PV = 15, B_XM = 17, B_COUNT = 21 };
 enum { E_PROD = 0x210, E_MMA = 0x230, E_SM = 0x240 };
 
 struct Params {
@@ -120,9 +124,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar(B_KF + i), 1); mbar_init(bar(B_KE + i), 1);
             mbar_init(bar(B_VF + i), 1); mbar_init(bar(B_VE + i), 1);
-            mbar_init(bar(B_SF + i), 1); mbar_init(bar(B_SE + i), 4);
-            mbar_init(bar(B_PF + i), 4); mbar_init(bar(B_PV + i), 1);
+            mbar_init(bar(B_SF + i), 1); mbar_init(bar(B_SE + i), SM_WARPS);
+            mbar_init(bar(B_PF + i), SM_WARPS); mbar_init(bar(B_PV + i), 1);
         }
+        for (int i = 0; i < 4; ++i) mbar_init(bar(B_XM + i), 2);  // the two warps that share a lane quarter
         *abort_s = 0;
         fence_barrier_init();
     }
@@ -149,8 +154,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             bool ok = true;
             for (int j = 0; j < NT && ok; ++j) {
                 const int s = j & 1;
-                const uint32_t par = ((j >> 1) & 1) ^ 1;
-                if (!mbar_wait(bar(B_KE + s), par, abort_s, E_PROD | 1, 500)) { ok = false; break; }
+                const uint32_t par = ((j >> 1) & 1) ^ 1;  // parity of the stage's previous use, tile j - 2
+                // stage s is free once the MMAs of its previous use have completed: the scores' / the product's own barrier
+                if (j >= 2 && !mbar_wait(bar(B_SF + s), par, abort_s, E_PROD | 1, 500)) { ok = false; break; }
                 mbar_expect_tx(bar(B_KF + s), TILE);
                 {
                     // coordinates (d, key, head, batch) in the order the tensor map sorted the outer dimensions by stride
@@ -160,7 +166,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     tma_load_4d(s_base + OFF_K + s * TILE, &tm_k, bar(B_KF + s), 0, c[1], c[2], c[3]);
                     tma_load_4d(s_base + OFF_K + s * TILE + TILE / 2, &tm_k, bar(B_KF + s), 64, c[1], c[2], c[3]);
                 }
-                if (!mbar_wait(bar(B_VE + s), par, abort_s, E_PROD | 2, 500)) { ok = false; break; }
+                if (j >= 2 && !mbar_wait(bar(B_PV + s), par, abort_s, E_PROD | 2, 500)) { ok = false; break; }
                 mbar_expect_tx(bar(B_VF + s), TILE);
                 tma_load_2d(s_base + OFF_V + s * TILE, &tm_v, bar(B_VF + s), j * BN, bh * HD);
                 tma_load_2d(s_base + OFF_V + s * TILE + TILE / 2, &tm_v, bar(B_VF + s), j * BN + 64, bh * HD);
@@ -172,108 +178,129 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             }
         }
     } else if (warp == 1) {
-        // ================================ MMA issuer ================================
+        // ================================ MMA issuer: scores ================================
+        // The issuing thread pays ~100 cycles per tcgen05.mma and more per commit and wait, and a 128 x 128 x 16 MMA is only
+        // 64 cycles of tensor work, so the two products have an issuing warp each and every descriptor is one add away
+        // from a precomputed base.  A commit doubles as the "stage consumed" signal for the producer.
         if (lane == 0) {
             const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             const uint32_t idesc = umma_idesc(1u, fmt, fmt, 128);
             bool ok = mbar_wait(bar(B_Q), 0, abort_s, E_MMA | 1, 100);
-            auto pv = [&](int i) -> bool {
-                const int b = i & 1;
-                const uint32_t par = (i >> 1) & 1;
-                if (!mbar_wait(bar(B_PF + b), par, abort_s, E_MMA | 4, 100)) return false;
-                if (!mbar_wait(bar(B_VF + b), par, abort_s, E_MMA | 5, 100)) return false;
-                tc_fence_after();
-                const uint32_t v_addr = s_base + OFF_V + b * TILE;
-#pragma unroll
-                for (int kh = 0; kh < 2; ++kh)
-#pragma unroll
-                    for (int st = 0; st < 4; ++st)
-                        mma_f16_ts(tmem_base + TM_O, tmem_base + TM_P + b * 64 + (kh * 4 + st) * 8,
-                                   desc_sw128(v_addr + kh * (TILE / 2) + st * 32), idesc, (i > 0 || kh || st) ? 1u : 0u);
-                tc_commit(bar(B_PV + b));
-                tc_commit(bar(B_VE + b));
-                return true;
-            };
+            const uint64_t dq = desc_sw128(s_base + OFF_Q), dk0 = desc_sw128(s_base + OFF_K);
             for (int j = 0; j < NT && ok; ++j) {
                 const int b = j & 1;
                 const uint32_t par = (j >> 1) & 1;
                 if (!mbar_wait(bar(B_KF + b), par, abort_s, E_MMA | 2, 100)) { ok = false; break; }
                 if (!mbar_wait(bar(B_SE + b), par ^ 1, abort_s, E_MMA | 3, 100)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t q_addr = s_base + OFF_Q, k_addr = s_base + OFF_K + b * TILE;
+                const uint64_t dk = dk0 + (uint64_t)(b * (TILE >> 4));
+                const uint32_t d = tmem_base + TM_S + b * 128;
+                // the descriptor's start-address field counts 16-byte units: +2 per 32-byte K step, +1024 per 64-wide half
 #pragma unroll
                 for (int dh = 0; dh < 2; ++dh)
 #pragma unroll
                     for (int st = 0; st < 4; ++st)
-                        mma_f16(tmem_base + TM_S + b * 128, desc_sw128(q_addr + dh * (TILE / 2) + st * 32),
-                                desc_sw128(k_addr + dh * (TILE / 2) + st * 32), idesc, (dh || st) ? 1u : 0u);
+                        mma_f16(d, dq + dh * 1024 + st * 2, dk + dh * 1024 + st * 2, idesc, (dh || st) ? 1u : 0u);
                 tc_commit(bar(B_SF + b));
-                tc_commit(bar(B_KE + b));
-                if (j >= 1) ok = pv(j - 1);
             }
-            if (ok && NT > 0) pv(NT - 1);
+        }
+    } else if (warp == 2 + SM_WARPS) {
+        // ================================ MMA issuer: P V ================================
+        if (lane == 0) {
+            const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+            const uint32_t idesc = umma_idesc(1u, fmt, fmt, 128);
+            const uint64_t dv0 = desc_sw128(s_base + OFF_V);
+            bool ok = true;
+            for (int i = 0; i < NT && ok; ++i) {
+                const int b = i & 1;
+                const uint32_t par = (i >> 1) & 1;
+                if (!mbar_wait(bar(B_PF + b), par, abort_s, E_MMA | 4, 100)) { ok = false; break; }
+                if (!mbar_wait(bar(B_VF + b), par, abort_s, E_MMA | 5, 100)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t dv = dv0 + (uint64_t)(b * (TILE >> 4));
+                const uint32_t pa = tmem_base + TM_P + b * 64;
+#pragma unroll
+                for (int kh = 0; kh < 2; ++kh)
+#pragma unroll
+                    for (int st = 0; st < 4; ++st)
+                        mma_f16_ts(tmem_base + TM_O, pa + (kh * 4 + st) * 8, dv + kh * 1024 + st * 2, idesc,
+                                   (i > 0 || kh || st) ? 1u : 0u);
+                tc_commit(bar(B_PV + b));
+            }
         }
     } else {
         // ================================ softmax ================================
-        const int q = warp & 3;
+        const int q = warp & 3;            // lane quarter this warp may read
+        const int hf = (warp - 2) >> 2;    // column half of the score / output tile
         const int row = q * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        float* xmax = reinterpret_cast<float*>(smem + OFF_XCH);            // [tile parity][half][128]
+        float* xsum = reinterpret_cast<float*>(smem + OFF_XCH) + 4 * 128;  // [half][128]
         float m_used = -INFINITY, l = 0.f;
+        uint32_t xph = 0;
         bool ok = true;
         for (int j = 0; j < NT && ok; ++j) {
             const int b = j & 1;
             const uint32_t par = (j >> 1) & 1;
             if (!mbar_wait_warp(bar(B_SF + b), par, abort_s, E_SM | 1, 100)) { ok = false; break; }
             tc_fence_after();
-            float s[128];
+            float s[64];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(lane_addr + TM_S + b * 128 + c * 32, *reinterpret_cast<float(*)[32]>(&s[c * 32]));
+            for (int c = 0; c < 2; ++c)
+                tmem_ld32(lane_addr + TM_S + b * 128 + hf * 64 + c * 32, *reinterpret_cast<float(*)[32]>(&s[c * 32]));
             tmem_wait_ld();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_SE + b));  // the score slot may be overwritten by tile j + 2
             if (j == NT - 1 && (p.Tkv & (BN - 1))) {
-                const int valid = p.Tkv - j * BN;
+                const int valid = p.Tkv - j * BN - hf * 64;
 #pragma unroll
-                for (int i = 0; i < 128; ++i)
+                for (int i = 0; i < 64; ++i)
                     if (i >= valid) s[i] = -INFINITY;
             }
-            // one thread per row means no other warp hides this thread's latencies: keep the reductions shallow
             float m8[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) m8[i] = s[i];
 #pragma unroll
-            for (int i = 8; i < 128; ++i) m8[i & 7] = fmaxf(m8[i & 7], s[i]);
-            const float mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
-            // raise the subtracted maximum only when it lags by more than 8 (or at the first tile)
+            for (int i = 8; i < 64; ++i) m8[i & 7] = fmaxf(m8[i & 7], s[i]);
+            float mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+            // the row maximum over both column halves: exchange with the partner warp (buffers alternate with the tile)
+            xmax[(b * 2 + hf) * 128 + row] = mx;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_XM + q));
+            if (!mbar_wait_warp(bar(B_XM + q), xph & 1, abort_s, E_SM | 5, 100)) { ok = false; break; }
+            ++xph;
+            mx = fmaxf(mx, xmax[(b * 2 + (hf ^ 1)) * 128 + row]);
+            // raise the subtracted maximum only when it lags by more than 8 (or at the first tile); both warps of a row
+            // see the same numbers and take the same decision
             const bool need = mx > m_used + 8.0f;
             if (__any_sync(0xffffffffu, need)) {
                 const float m_new = fmaxf(m_used, mx);
                 if (j > 0) {
-                    // O must hold every product issued so far before it is rescaled
+                    // O must hold every product issued so far before it is rescaled; this warp scales its column half
                     if (!mbar_wait_warp(bar(B_PV + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_s, E_SM | 2, 100)) { ok = false; break; }
                     tc_fence_after();
                     const float alpha = ex2(m_used - m_new);
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < 2; ++c) {
                         float o[32];
                         uint32_t w[32];
-                        tmem_ld32(lane_addr + TM_O + c * 32, o);
+                        tmem_ld32(lane_addr + TM_O + hf * 64 + c * 32, o);
                         tmem_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(o[i] * alpha);
-                        tmem_st32(lane_addr + TM_O + c * 32, w);
+                        tmem_st32(lane_addr + TM_O + hf * 64 + c * 32, w);
                     }
                     tmem_wait_st();
                     l *= alpha;
                 }
                 m_used = m_new;
             }
-            // probabilities: fp32 for the row sum, rounded to T for the product
-            uint32_t pk[64];
+            // probabilities: fp32 for the (partial) row sum, rounded to T for the product
+            uint32_t pk[32];
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
+            for (int i = 0; i < 32; ++i) {
                 const float p0 = ex2(s[2 * i] - m_used), p1 = ex2(s[2 * i + 1] - m_used);
                 sum4[i & 3] += p0 + p1;
                 pk[i] = pack2<T>(p0, p1);
@@ -282,22 +309,29 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             // the P slot is free once the product that read it two tiles ago has completed
             if (j >= 2 && !mbar_wait_warp(bar(B_PV + b), ((j - 2) >> 1) & 1, abort_s, E_SM | 3, 100)) { ok = false; break; }
             tc_fence_after();
-            tmem_st32(lane_addr + TM_P + b * 64, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
-            tmem_st32(lane_addr + TM_P + b * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
+            tmem_st32(lane_addr + TM_P + b * 64 + hf * 32, pk);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_PF + b));
         }
+        if (ok && NT > 0) {
+            // total row sum = the two halves' partial sums
+            xsum[hf * 128 + row] = l;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_XM + q));
+            ok = mbar_wait_warp(bar(B_XM + q), xph & 1, abort_s, E_SM | 6, 100);
+            if (ok) l += xsum[(hf ^ 1) * 128 + row];
+        }
         if (ok && NT > 0 && mbar_wait_warp(bar(B_PV + ((NT - 1) & 1)), ((NT - 1) >> 1) & 1, abort_s, E_SM | 4, 100)) {
             tc_fence_after();
             const int m = m0 + row;
             const float inv = 1.0f / (l == 0.f ? 1.0f : l);
-            T* og = static_cast<T*>(p.o) + (long long)batch * p.stride_ob + (long long)m * p.stride_om + (long long)head * HD;
+            T* og = static_cast<T*>(p.o) + (long long)batch * p.stride_ob + (long long)m * p.stride_om + (long long)head * HD + hf * 64;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 float o[32];
-                tmem_ld32(lane_addr + TM_O + c * 32, o);
+                tmem_ld32(lane_addr + TM_O + hf * 64 + c * 32, o);
                 tmem_wait_ld();
                 if (m < p.Tq) {
 #pragma unroll
