@@ -242,21 +242,28 @@ static bool attn_common_ok(const nb_attn_args* a) {
         if (st % 8) return false;
     return aligned16(a->q) && aligned16(a->k) && aligned16(a->v);
 }
-static bool attn_uses_tc(const nb_attn_args* a) {
+// the call fits the tcgen05 kernel's rules (scratch apart)
+static bool attn_fits_tc(const nb_attn_args* a) {
     return a->impl != NB_IMPL_GENERIC && attn_common_ok(a) && attn_tc_unsupported_reason(a) == nullptr;
+}
+static bool attn_scratch_ok(const nb_attn_args* a) {
+    return a->scratch && a->scratch_bytes >= attn_tc_scratch_bytes(a) && (reinterpret_cast<uintptr_t>(a->scratch) & 255) == 0;
 }
 }  // namespace nb
 
 extern "C" int64_t nb_attention_scratch_bytes(const nb_attn_args* a) {
     if (!a || a->B <= 0 || a->H <= 0) return 0;
-    return nb::attn_uses_tc(a) ? nb::attn_tc_scratch_bytes(a) : 0;
+    return nb::attn_fits_tc(a) ? nb::attn_tc_scratch_bytes(a) : 0;
 }
 
 extern "C" int nb_attention(const nb_attn_args* a, void* stream) {
     using namespace nb;
     NB_REQUIRE(a && a->q && a->k && a->v && a->o);
-    if (a->impl == NB_IMPL_TCGEN05 && !attn_uses_tc(a)) return NB_ERR_UNSUPPORTED;
-    if (a->B > 0 && a->H > 0 && attn_uses_tc(a)) return launch_attention_tc(a, static_cast<cudaStream_t>(stream));
+    // tcgen05 kernel when the call fits it and brings its scratch; a caller that passes none (NB_IMPL_AUTO) gets the
+    // mma.sync kernel, which needs no scratch
+    if (a->B > 0 && a->H > 0 && attn_fits_tc(a) && attn_scratch_ok(a))
+        return launch_attention_tc(a, static_cast<cudaStream_t>(stream));
+    if (a->impl == NB_IMPL_TCGEN05) return attn_fits_tc(a) ? NB_ERR_INVALID : NB_ERR_UNSUPPORTED;
     NB_REQUIRE(a->B > 0 && a->H > 0 && a->Tq >= 0 && a->Tkv >= 0);
     NB_REQUIRE(a->dtype == NB_DTYPE_BF16 || a->dtype == NB_DTYPE_FP16);
     if (a->D != 64 && a->D != 128) return NB_ERR_UNSUPPORTED;

@@ -15,13 +15,13 @@
 //     128 x 128 output tiles.  A stage of the shared-memory ring holds two K groups (128 k):
 //       warp 0    TMA producer: A and W rows (128 x 128 B each, 128-byte swizzle) and the two groups' scale
 //                 rows (no multicast, no cluster); low-rank chunks of 32 ranks travel through the same ring.
-//       warp 1    MMA issuer: per group two 128 x 128 x 32 kind::i8 MMAs into one of FOUR tensor-memory slots,
-//                 so the tensor pipe runs up to three groups ahead of the drain; tcgen05.commit publishes the
-//                 slot and, per stage, releases the operands.  The low-rank product is kind::f16 into an
-//                 fp32 slot of the same ring.
+//       warp 1    MMA issuer: per ring stage (two groups) four 128 x 128 x 32 kind::f8f6f4 MMAs into two of FOUR
+//                 tensor-memory slots and ONE tcgen05.commit, which publishes both slots and releases the operands:
+//                 the issuing thread pays a few hundred cycles per wait and commit, so the work between two of them has
+//                 to be large.  The low-rank product is kind::f16 into an fp32 slot of the same ring.
 //       warps 2-9 drain: a warp owns 32 rows x 64 columns.  tcgen05.ld.16x256b gives a thread the
 //                 accumulator-fragment layout (4 rows x 16 columns), so it needs 4 row scales and 16 column
-//                 scales per group, and two packed fp32x2 FMAs per column pair (below).  The loads of the
+//                 scales per group, and a packed fp32x2 multiply and FMA per column pair (below).  The loads of the
 //                 next half group are in flight while the current half is scaled.  After the last group: bias,
 //                 optional per-head RMSNorm + RoPE, rounding, and a coalesced store through a padded per-warp
 //                 staging tile.

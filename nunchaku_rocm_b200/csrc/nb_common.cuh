@@ -224,14 +224,6 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// D[tmem] (+)= A[smem desc] * B[smem desc]; one thread issues for the CTA
-__device__ __forceinline__ void mma_i8(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
-        : "memory");
-}
 // kind::f8f6f4: 8-bit (or narrower) floating-point operands, fp32 accumulators, K = 32 per instruction
 __device__ __forceinline__ void mma_f8(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
     asm volatile(
@@ -248,15 +240,6 @@ __device__ __forceinline__ void mma_f16(uint32_t d, uint64_t adesc, uint64_t bde
         : "memory");
 }
 
-// 32 lanes x 16 consecutive 32-bit columns: thread i of the warp reads TMEM lane (lane field of taddr) + i
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr)
-        : "memory");
-}
 
 // 16 lanes x 64 columns in the accumulator-fragment layout: with gid = lane / 4, tig = lane % 4, register
 // 4 j + 2 r + e is TMEM lane (lane field) + 8 r + gid, column 8 j + 2 tig + e
@@ -319,8 +302,5 @@ __device__ __forceinline__ uint64_t umma_desc_kmajor(uint32_t smem_addr, uint32_
 __device__ __host__ constexpr uint32_t umma_idesc(uint32_t c_fmt, uint32_t a_fmt, uint32_t b_fmt, uint32_t n) {
     return (c_fmt << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
-
-__device__ __forceinline__ void setmaxnreg_inc_176() { asm volatile("setmaxnreg.inc.sync.aligned.u32 176;"); }
-__device__ __forceinline__ void setmaxnreg_dec_80() { asm volatile("setmaxnreg.dec.sync.aligned.u32 80;"); }
 
 }  // namespace nb
