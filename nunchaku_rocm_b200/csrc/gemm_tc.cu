@@ -48,17 +48,25 @@ constexpr int BM = 128;
 constexpr int BN = 128;
 constexpr int STAGES = 4;
 constexpr int NSLOT = 4;            // tensor-memory accumulator slots of BN columns
-constexpr int DRAIN_WARPS = 8;      // warps 2..9
+#ifndef NB_TC_DRAIN_WARPS
+#define NB_TC_DRAIN_WARPS 8
+#endif
+constexpr int DRAIN_WARPS = NB_TC_DRAIN_WARPS;  // warps 2..: four TMEM lane quarters x NCQ column slices
+constexpr int NCQ = DRAIN_WARPS / 4;
 constexpr int NTHREADS = 64 + DRAIN_WARPS * 32;
-constexpr int COLS = BN / 2;        // columns one drain warp owns
+constexpr int COLS = BN / NCQ;      // columns one drain warp owns
+constexpr int NJ = COLS / 8;        // 8-column blocks per warp
+constexpr int NV = 4 * NJ;          // registers of one 16-lane block of a warp's slice
+static_assert(DRAIN_WARPS == 8 || DRAIN_WARPS == 16, "drain warps");
 struct Cfg {
     static constexpr int ST_A = BM * 128, ST_W = BN * 128;  // two K groups of int8 per row
-    static constexpr int ST_AS = 2 * BM * 8;                // per group and row: (as, as)
-    static constexpr int ST_WS = 2 * BN * 4;                // per group and column: ws, in drain order
+    static constexpr int ST_AS = 2 * BM * 4;                // per group and row: as, rows permuted per 32-row block
+    static constexpr int ST_WS = 1024;                      // per group and column: ws as T, in drain order (512 B used)
+    static constexpr int ST_WS_TX = 2 * BN * 2;
     static constexpr int ST_BYTES = ST_A + ST_W + ST_AS + ST_WS;
     static constexpr int STG_PITCH = COLS * 2 + 16;
     static constexpr int STG_BYTES = DRAIN_WARPS * 32 * STG_PITCH;
-    static constexpr int XCH_BYTES = DRAIN_WARPS * 32 * 4;  // per-row partial sums exchanged between column halves
+    static constexpr int XCH_BYTES = 2 * DRAIN_WARPS * 32 * 4;  // per-row partial sums exchanged between column slices, two buffers
     static constexpr int OFF_ST = 0;
     static constexpr int OFF_STG = OFF_ST + STAGES * ST_BYTES;
     static constexpr int OFF_XCH = OFF_STG + STG_BYTES;
@@ -152,7 +160,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_DONE + i), 1); mbar_init(bar(B_SCDONE + i), DRAIN_WARPS); }
         for (int i = 0; i < NSLOT; ++i) mbar_init(bar(B_ACC_EMPTY + i), DRAIN_WARPS);
-        for (int i = 0; i < 4; ++i) mbar_init(bar(B_XCH + i), 2);
+        for (int i = 0; i < 4; ++i) mbar_init(bar(B_XCH + i), NCQ);
         mbar_init(bar(B_LR), 1);
         *abort_s = 0;
         fence_barrier_init();
@@ -199,10 +207,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     NB_PF(0);
                     const uint32_t dst = s_base + C::OFF_ST + s * C::ST_BYTES;
                     if (j < GS) {
-                        mbar_expect_tx(bar(B_FULL + s), C::ST_BYTES);
+                        mbar_expect_tx(bar(B_FULL + s), C::ST_A + C::ST_W + C::ST_AS + C::ST_WS_TX);
                         tma_load_2d(dst, &tm_a, bar(B_FULL + s), j * 128, m0);
                         tma_load_2d(dst + C::ST_A, &tm_w, bar(B_FULL + s), j * 128, n0);
-                        tma_load_2d(dst + C::ST_A + C::ST_W, &tm_as, bar(B_FULL + s), m0 * 2, j * 2);
+                        tma_load_2d(dst + C::ST_A + C::ST_W, &tm_as, bar(B_FULL + s), m0, j * 2);
                         tma_load_2d(dst + C::ST_A + C::ST_W + C::ST_AS, &tm_ws, bar(B_FULL + s), n0, j * 2);
                     } else {
                         // 32 ranks of T(lora_act) rows m0.. and lora_up rows n0..: 128 x 64 B each, 64-byte swizzle
@@ -242,9 +250,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     NB_PF(7);
                     if (!mbar_wait(bar(B_FULL + s), (it / STAGES) & 1, abort_s, E_MMA | 1, 100)) { ok = false; break; }
                     NB_PF(0);
-                    for (int i = 0; i < ng; ++i)
-                        if (!mbar_wait(bar(B_ACC_EMPTY + (ait + i) % NSLOT), (((ait + i) / NSLOT) & 1) ^ 1, abort_s, E_MMA | 2, 100)) { ok = false; break; }
-                    if (!ok) break;
+                    // the first group's slot is released half a stage before the second's: its MMAs go out before the
+                    // issuer waits for the second slot
+                    if (!mbar_wait(bar(B_ACC_EMPTY + ait % NSLOT), ((ait / NSLOT) & 1) ^ 1, abort_s, E_MMA | 2, 100)) { ok = false; break; }
                     NB_PF(1);
                     tc_fence_after();
                     const uint32_t a_addr = s_base + C::OFF_ST + s * C::ST_BYTES;
@@ -256,6 +264,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         mma_f8(d, da + 2, dw + 2, idesc_f8, 1u);
                     }
                     if (ng == 2) {
+                        NB_PF(2);
+                        if (!mbar_wait(bar(B_ACC_EMPTY + (ait + 1) % NSLOT), (((ait + 1) / NSLOT) & 1) ^ 1, abort_s, E_MMA | 2, 100)) { ok = false; break; }
+                        NB_PF(1);
+                        tc_fence_after();
                         const uint32_t d = tmem_base + ((ait + 1) % NSLOT) * BN;
                         mma_f8(d, da + 4, dw + 4, idesc_f8, 0u);
                         mma_f8(d, da + 6, dw + 6, idesc_f8, 1u);
@@ -291,7 +303,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         // 4 j + 2 rs + e.
         const int dw = warp - 2;
         const int q = warp & 3;     // TMEM lane quarter this warp may read (warp id mod 4)
-        const int half = dw >> 2;   // column half of the tile
+        const int half = dw >> 2;   // column slice of the tile
         const int pw = half * 4 + q;             // index used for staging / exchange buffers
         const int gid = lane >> 2, tig = lane & 3;
         uint8_t* stg = smem + C::OFF_STG + pw * 32 * C::STG_PITCH;
@@ -299,16 +311,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16) + half * COLS;
         uint32_t it = 0, ait = 0, xph = 0;
         bool ok = true;
-        uint64_t acc[32];  // [lane block lb][j][row select] pairs of fp32
-        uint32_t v[2][32];
+        uint64_t acc[NV];  // [lane block lb][j][row select] pairs of fp32
+        uint32_t v[2][NV];
         NB_PF_DECL
 
         for (int t = t_begin; t < t_end && ok; ++t) {
             const int m0 = (t / NT) * BM, n0 = (t % NT) * BN;
             const int nc0 = n0 + half * COLS;  // first global column of this warp
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] = 0ull;
-
+            for (int i = 0; i < NV; ++i) acc[i] = 0ull;
             // Software pipeline over half groups (16 TMEM lanes = 32 registers each): while one half is scaled the
             // loads of the next are in flight.  `v[0]` holds lane block 0, `v[1]` lane block 1 of a group.  The MMA warp
             // completes a ring stage (two groups) at a time, so there is one wait per stage.
@@ -317,29 +328,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 if (!mbar_wait_warp(bar(B_DONE + it % STAGES), (it / STAGES) & 1, abort_s, E_DRAIN | 1, 100)) { ok = false; break; }
                 NB_PF(0);
                 tc_fence_after();
-                tmem_ld_16x256b_x8(lane_base + (ait % NSLOT) * BN, v[0]);
+                tmem_ld_16x256b(lane_base + (ait % NSLOT) * BN, v[0]);
             }
+            // The scales of a group are requested one group ahead (raw: 4 row scales as fp32, 2 NJ column scales as T) and
+            // widened at the top of their group, so their shared-memory latency is off the critical path.
+            uint4 as_n, ws_n[NJ / 4];
+            auto load_scales = [&](uint32_t stage, int i) {
+                const uint8_t* st = smem + C::OFF_ST + stage * C::ST_BYTES + C::ST_A + C::ST_W;
+                as_n = *reinterpret_cast<const uint4*>(st + (i * BM + q * 32 + gid * 4) * 4);  // rows gid, +8, +16, +24
+                const uint4* ws_s = reinterpret_cast<const uint4*>(st + C::ST_AS + (i * BN + half * COLS + tig * NJ * 2) * 2);
+#pragma unroll
+                for (int jj = 0; jj < NJ / 4; ++jj) ws_n[jj] = ws_s[jj];
+            };
+            load_scales(it % STAGES, 0);
             for (int g = 0; g < G; ++g, ++ait) {
                 const int slot = ait % NSLOT;
                 const uint32_t itg = it + (g >> 1);
                 const int s = itg % STAGES, i = g & 1;
-                const uint8_t* st = smem + C::OFF_ST + s * C::ST_BYTES;
                 // scales of this group
-                const uint64_t* as_s = reinterpret_cast<const uint64_t*>(st + C::ST_A + C::ST_W) + i * BM + q * 32 + gid;
-                const ulonglong2* ws_s = reinterpret_cast<const ulonglong2*>(st + C::ST_A + C::ST_W + C::ST_AS + i * BN * 4 + half * COLS * 4) + tig;
-                uint64_t as2[4];
+                const uint4 as4 = as_n;
+                uint64_t as2[4] = {pack_u32x2(as4.x, as4.x), pack_u32x2(as4.y, as4.y), pack_u32x2(as4.z, as4.z), pack_u32x2(as4.w, as4.w)};
+                uint32_t w16[NJ];
 #pragma unroll
-                for (int r = 0; r < 4; ++r) as2[r] = as_s[r * 8];  // rows gid, gid + 8, gid + 16, gid + 24
-                ulonglong2 w[4];
+                for (int jj = 0; jj < NJ / 4; ++jj) { const uint4 t4 = ws_n[jj]; w16[4 * jj] = t4.x; w16[4 * jj + 1] = t4.y; w16[4 * jj + 2] = t4.z; w16[4 * jj + 3] = t4.w; }
+                ulonglong2 w[NJ / 2];
 #pragma unroll
-                for (int jj = 0; jj < 4; ++jj) w[jj] = ws_s[jj * 4];
+                for (int jj = 0; jj < NJ / 2; ++jj) {
+                    const float2 f0 = unpack2<T>(w16[2 * jj]), f1 = unpack2<T>(w16[2 * jj + 1]);
+                    w[jj] = make_ulonglong2(pack_f32x2(f0.x, f0.y), pack_f32x2(f1.x, f1.y));
+                }
                 NB_PF(1);
                 tmem_wait_ld();  // v[0] has landed
                 NB_PF(2);
-                tmem_ld_16x256b_x8(lane_base + (16u << 16) + slot * BN, v[1]);
+                tmem_ld_16x256b(lane_base + (16u << 16) + slot * BN, v[1]);
 #pragma unroll
                 for (int lb = 0; lb < 2; ++lb) {
-                    uint32_t(&vv)[32] = v[lb];
+                    uint32_t(&vv)[NV] = v[lb];
                     if (lb == 1) {
                         tmem_wait_ld();  // v[1] has landed: the slot is read out
                         tc_fence_before();
@@ -350,13 +374,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             // This warp holds the stage's scales in registers (the empty asm makes the loads retire first).
                             // Released BEFORE the wait below: the low-rank slot only completes after the producer has
                             // reused ring stages, which it may not do while a drain warp still owes this arrival.
-                            asm volatile("" ::"l"(as2[2]), "l"(as2[3]), "l"(w[3].y) : "memory");
+                            asm volatile("" ::"l"(as2[2]), "l"(as2[3]), "l"(w[NJ / 2 - 1].y) : "memory");
                             if (lane == 0) mbar_arrive(bar(B_SCDONE + s));
                         }
                         NB_PF(3);
                         // next accumulator: the stage's second group, the next stage, or the low-rank slot after the last group
                         if (!last_of_stage) {
-                            tmem_ld_16x256b_x8(lane_base + ((ait + 1) % NSLOT) * BN, v[0]);
+                            tmem_ld_16x256b(lane_base + ((ait + 1) % NSLOT) * BN, v[0]);
                         } else if (g + 1 < G || LCH > 0) {
                             // (the low-rank slot has a barrier of its own: its ring stages are not watched here, and waiting for a
                             // later use of a stage barrier while an earlier one is still pending would alias on the parity)
@@ -365,24 +389,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                                                 more ? ((itg + 1) / STAGES) & 1 : (uint32_t)(t - t_begin) & 1, abort_s, E_DRAIN | 2, 100)) { ok = false; break; }
                             NB_PF(5);
                             tc_fence_after();
-                            tmem_ld_16x256b_x8(lane_base + ((ait + 1) % NSLOT) * BN, v[0]);
+                            tmem_ld_16x256b(lane_base + ((ait + 1) % NSLOT) * BN, v[0]);
                         }
+                        if (g + 1 < G) load_scales((it + ((g + 1) >> 1)) % STAGES, (g + 1) & 1);  // (its stage has been waited for)
                         NB_PF(0);
                     }
 #pragma unroll
-                    for (int jx = 0; jx < 8; ++jx) {
+                    for (int jx = 0; jx < NJ; ++jx) {
                         const uint64_t wj = (jx & 1) ? w[jx >> 1].y : w[jx >> 1].x;
 #pragma unroll
                         for (int rs = 0; rs < 2; ++rs) {
                             const int vi = 4 * jx + 2 * rs;
                             const uint64_t tt = mul_f32x2(pack_u32x2(vv[vi], vv[vi + 1]), as2[lb * 2 + rs]);
-                            uint64_t& a = acc[(lb * 8 + jx) * 2 + rs];
+                            uint64_t& a = acc[(lb * NJ + jx) * 2 + rs];
                             a = fma_f32x2(tt, wj, a);
                         }
                     }
                     if (DEBUG_P) {
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) {
+                        for (int e = 0; e < NV; ++e) {
                             const int m = m0 + q * 32 + lb * 16 + ((e >> 1) & 1) * 8 + gid;
                             const int n = nc0 + (e >> 2) * 8 + 2 * tig + (e & 1);
                             if (m < p.M && n < p.N)
@@ -395,10 +420,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
             if (!ok) break;
             it += GS;
+            // bias and (Q / K tiles) RMSNorm weights of this warp's columns, requested before the low-rank slot is added
+            const int qk_part = EPI == NB_EPI_QK_NORM_ROPE ? n0 / (p.N / 3) : 2;
+            uint32_t bias_w[NJ], norm_w[NJ];
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {
+                const int col = nc0 + 8 * j + 2 * tig;
+                bias_w[j] = (p.bias && col < p.N) ? __ldg(reinterpret_cast<const uint32_t*>(static_cast<const T*>(p.bias) + col)) : 0u;
+                norm_w[j] = 0u;
+                if (EPI == NB_EPI_QK_NORM_ROPE && qk_part < 2)
+                    norm_w[j] = __ldg(reinterpret_cast<const uint32_t*>(static_cast<const T*>(qk_part == 0 ? p.norm_q : p.norm_k) + half * COLS + 8 * j + 2 * tig));
+            }
             if (LCH > 0) {
                 const int slot = ait % NSLOT;
                 tmem_wait_ld();
-                tmem_ld_16x256b_x8(lane_base + (16u << 16) + slot * BN, v[1]);
+                tmem_ld_16x256b(lane_base + (16u << 16) + slot * BN, v[1]);
 #pragma unroll
                 for (int lb = 0; lb < 2; ++lb) {
                     if (lb == 1) {
@@ -408,10 +444,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + slot));
                     }
 #pragma unroll
-                    for (int jx = 0; jx < 8; ++jx)
+                    for (int jx = 0; jx < NJ; ++jx)
 #pragma unroll
                         for (int rs = 0; rs < 2; ++rs) {
-                            uint64_t& a = acc[(lb * 8 + jx) * 2 + rs];
+                            uint64_t& a = acc[(lb * NJ + jx) * 2 + rs];
                             a = add_f32x2(a, pack_u32x2(v[lb][4 * jx + 2 * rs], v[lb][4 * jx + 2 * rs + 1]));
                         }
                 }
@@ -425,73 +461,93 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
             for (int lb = 0; lb < 2; ++lb)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int col = nc0 + 8 * j + 2 * tig;
-                    float2 b = make_float2(0.f, 0.f);
-                    if (p.bias && col < p.N) b = unpack2<T>(__ldg(reinterpret_cast<const uint32_t*>(static_cast<const T*>(p.bias) + col)));
+                for (int j = 0; j < NJ; ++j) {
+                    const float2 b = unpack2<T>(bias_w[j]);
 #pragma unroll
                     for (int rs = 0; rs < 2; ++rs) {
-                        float2 a = unpack_f32x2(acc[(lb * 8 + j) * 2 + rs]);
+                        float2 a = unpack_f32x2(acc[(lb * NJ + j) * 2 + rs]);
                         a.x += b.x;
                         a.y += b.y;
-                        acc[(lb * 8 + j) * 2 + rs] = pack_f32x2(a.x, a.y);
+                        acc[(lb * NJ + j) * 2 + rs] = pack_f32x2(a.x, a.y);
                         if (EPI == NB_EPI_QK_NORM_ROPE) sumsq[lb * 2 + rs] = fmaf(a.x, a.x, fmaf(a.y, a.y, sumsq[lb * 2 + rs]));
                     }
                 }
-            if (EPI == NB_EPI_QK_NORM_ROPE) {
-                // the 128-column tile is one head: the 4 lanes of a quad share a row inside the warp, and the
-                // warp that owns the other 64 columns of the same rows is the one with the other `half`
-                const int part = n0 / (p.N / 3);
+            if (EPI == NB_EPI_QK_NORM_ROPE && qk_part < 2) {
+                // The 128-column tile is one head.  The rotary values of the first 16-lane block are requested before the
+                // exchange of the row sums, those of the second while the first is rotated: their L2 latency is hidden.
+                const float2* rp[4];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const int m = m0 + q * 32 + r * 8 + gid;
+                    int mr = m < p.actual_m ? m : 0;
+                    if (mr >= p.rot_rows) mr %= p.rot_rows;
+                    rp[r] = reinterpret_cast<const float2*>(p.rot + (long long)mr * p.stride_rm + half * COLS + 2 * tig);
+                }
+                float2 sc[2][NJ];
+#pragma unroll
+                for (int rs = 0; rs < 2; ++rs)
+#pragma unroll
+                    for (int j = 0; j < NJ; ++j) sc[rs][j] = __ldg(rp[rs] + 4 * j);
+                // the 4 lanes of a quad share a row; the other column slices of the same rows are in the warps with the same q
+                float* xb = xch + (xph & 1) * (DRAIN_WARPS * 32);
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     float s = sumsq[r];
                     s += __shfl_xor_sync(0xffffffffu, s, 1);
                     s += __shfl_xor_sync(0xffffffffu, s, 2);
-                    sumsq[r] = s;
-                    if (tig == 0) xch[pw * 32 + (r >> 1) * 16 + (r & 1) * 8 + gid] = s;
+                    if (tig == 0) xb[pw * 32 + r * 8 + gid] = s;
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_XCH + q));
                 if (!mbar_wait_warp(bar(B_XCH + q), xph & 1, abort_s, E_DRAIN | 4, 100)) { ok = false; break; }
+                // (the buffer of this parity is written again two exchanges later, and no warp gets there before every
+                // warp of the quarter has arrived at the exchange in between, i.e. after it has read this one)
                 ++xph;
-                if (part < 2) {
-                    float rstd[4];
+                float rstd[4];
 #pragma unroll
-                    for (int r = 0; r < 4; ++r)
-                        rstd[r] = rsqrtf((sumsq[r] + xch[(pw ^ 4) * 32 + (r >> 1) * 16 + (r & 1) * 8 + gid]) / 128.0f + p.eps);
-                    const T* wn = static_cast<const T*>(part == 0 ? p.norm_q : p.norm_k);
+                for (int r = 0; r < 4; ++r) {
+                    float tot = 0.f;  // every slice adds the partial sums in the same order
 #pragma unroll
-                    for (int lb = 0; lb < 2; ++lb)
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const int hc = half * COLS + 8 * j + 2 * tig;  // column inside the head (even)
-                            const float2 w = unpack2<T>(__ldg(reinterpret_cast<const uint32_t*>(wn + hc)));
-#pragma unroll
-                            for (int rs = 0; rs < 2; ++rs) {
-                                const int m = m0 + q * 32 + lb * 16 + rs * 8 + gid;
-                                const int mr = m < p.actual_m ? m % p.rot_rows : 0;
-                                const float2 sc = __ldg(reinterpret_cast<const float2*>(p.rot + (long long)mr * p.stride_rm + hc));
-                                const float2 a = unpack_f32x2(acc[(lb * 8 + j) * 2 + rs]);
-                                const float xe = a.x * rstd[lb * 2 + rs] * w.x, xo = a.y * rstd[lb * 2 + rs] * w.y;
-                                acc[(lb * 8 + j) * 2 + rs] = pack_f32x2(xe * sc.y - xo * sc.x, xe * sc.x + xo * sc.y);
-                            }
-                        }
+                    for (int c = 0; c < NCQ; ++c) tot += xb[(c * 4 + q) * 32 + r * 8 + gid];
+                    rstd[r] = rsqrtf(tot / 128.0f + p.eps);
                 }
-                // the partner must have read this warp's sums before the next tile overwrites them
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(B_XCH + q));
-                if (!mbar_wait_warp(bar(B_XCH + q), xph & 1, abort_s, E_DRAIN | 5, 100)) { ok = false; break; }
-                ++xph;
+#pragma unroll
+                for (int lb = 0; lb < 2; ++lb) {
+                    float2 scn[2][NJ];
+                    if (lb == 0) {
+#pragma unroll
+                        for (int rs = 0; rs < 2; ++rs)
+#pragma unroll
+                            for (int j = 0; j < NJ; ++j) scn[rs][j] = __ldg(rp[2 + rs] + 4 * j);
+                    }
+#pragma unroll
+                    for (int j = 0; j < NJ; ++j) {
+                        const float2 w = unpack2<T>(norm_w[j]);
+#pragma unroll
+                        for (int rs = 0; rs < 2; ++rs) {
+                            const float2 a = unpack_f32x2(acc[(lb * NJ + j) * 2 + rs]);
+                            const float xe = a.x * rstd[lb * 2 + rs] * w.x, xo = a.y * rstd[lb * 2 + rs] * w.y;
+                            const float2 c = sc[rs][j];
+                            acc[(lb * NJ + j) * 2 + rs] = pack_f32x2(xe * c.y - xo * c.x, xe * c.x + xo * c.y);
+                        }
+                    }
+                    if (lb == 0) {
+#pragma unroll
+                        for (int rs = 0; rs < 2; ++rs)
+#pragma unroll
+                            for (int j = 0; j < NJ; ++j) sc[rs][j] = scn[rs][j];
+                    }
+                }
             }
             // round, transpose through the per-warp staging tile, store whole 128-byte row segments
             __syncwarp();
 #pragma unroll
             for (int lb = 0; lb < 2; ++lb)
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
+                for (int j = 0; j < NJ; ++j)
 #pragma unroll
                     for (int rs = 0; rs < 2; ++rs) {
-                        const float2 a = unpack_f32x2(acc[(lb * 8 + j) * 2 + rs]);
+                        const float2 a = unpack_f32x2(acc[(lb * NJ + j) * 2 + rs]);
                         *reinterpret_cast<uint32_t*>(stg + (lb * 16 + rs * 8 + gid) * C::STG_PITCH + (8 * j + 2 * tig) * 2) = pack2<T>(a.x, a.y);
                     }
             __syncwarp();
@@ -529,8 +585,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 struct PrepackParams {
     const uint8_t* act; const uint8_t* wgt;
     const void* ascales; const void* wscales; const float* lora_act;
-    int8_t* a8; int8_t* w8; float* asf; float* wsf; void* la16;
-    int M, N, K, R, Np;  // Np: N rounded up to 128
+    int8_t* a8; int8_t* w8; float* asf; void* wsf; void* la16;
+    int M, N, K, R, Np, Mp;  // Np, Mp: N, M rounded up to 128
     int act_unsigned;
     long long stride_am, stride_wn, stride_asg, stride_wsg, stride_lam;
 };
@@ -554,7 +610,7 @@ __global__ void __launch_bounds__(256) prepack_kernel(const PrepackParams p) {
     const int upr = p.K / 32;  // 16-byte packed units per row
     const long long a_units = (long long)p.M * upr, w_units = (long long)p.N * upr;
     const int G = p.K / 64;
-    const long long as_units = (long long)G * p.M, ws_units = (long long)G * p.Np;
+    const long long as_units = (long long)G * p.Mp, ws_units = (long long)G * p.Np;
     const long long la_units = p.R ? (long long)p.M * (p.R / 8) : 0;
     if (tid < a_units + w_units) {
         const bool is_w = tid >= a_units;
@@ -580,9 +636,10 @@ __global__ void __launch_bounds__(256) prepack_kernel(const PrepackParams p) {
     }
     long long u = tid - (a_units + w_units);
     if (u < as_units) {
-        const int g = (int)(u / p.M), m = (int)(u % p.M);
-        const float a = to_f32<T>(static_cast<const T*>(p.ascales)[(long long)g * p.stride_asg + m]);
-        reinterpret_cast<float2*>(p.asf)[u] = make_float2(a, a);
+        const int g = (int)(u / p.Mp), m = (int)(u % p.Mp);
+        const float a = m < p.M ? to_f32<T>(static_cast<const T*>(p.ascales)[(long long)g * p.stride_asg + m]) : 0.f;
+        const int r32 = m & 31;  // row r * 8 + gid of its 32-row block -> position gid * 4 + r
+        p.asf[(long long)g * p.Mp + (m & ~31) + (r32 & 7) * 4 + (r32 >> 3)] = a;
         return;
     }
     u -= as_units;
@@ -590,11 +647,11 @@ __global__ void __launch_bounds__(256) prepack_kernel(const PrepackParams p) {
         // column n of its 128-wide tile -> [tile][warp half][pair of 8-col blocks][tig][4]: one 128-bit load of a drain
         // thread is (cols c, c+1 of block j, cols c, c+1 of block j+1)
         const int g = (int)(u / p.Np), n = (int)(u % p.Np);
-        const float w = n < p.N ? to_f32<T>(static_cast<const T*>(p.wscales)[(long long)g * p.stride_wsg + n]) : 0.f;
+        const T w = n < p.N ? static_cast<const T*>(p.wscales)[(long long)g * p.stride_wsg + n] : from_f32<T>(0.f);
         const int tile = n / BN, i = n % BN;
         const int hf = i / COLS, cc = i % COLS;
         const int blk = cc >> 3, tg = (cc >> 1) & 3, e = cc & 1;
-        p.wsf[(long long)g * p.Np + tile * BN + hf * COLS + (blk >> 1) * 16 + tg * 4 + (blk & 1) * 2 + e] = w;
+        static_cast<T*>(p.wsf)[(long long)g * p.Np + tile * BN + hf * COLS + tg * (COLS / 4) + blk * 2 + e] = w;
         return;
     }
     u -= ws_units;
@@ -646,7 +703,7 @@ static inline size_t up256(size_t x) { return (x + 255) & ~size_t(255); }
 
 struct Scratch {
     size_t a8, w8, asf, wsf, la16, total;
-    int Np;
+    int Np, Mp;
 };
 static Scratch scratch_layout(const nb_gemm_args* a) {
     Scratch s;
@@ -655,8 +712,9 @@ static Scratch scratch_layout(const nb_gemm_args* a) {
     size_t off = 0;
     s.a8 = off; off += up256((size_t)a->M * a->K);
     s.w8 = off; off += up256((size_t)a->N * a->K);
-    s.asf = off; off += up256(G * a->M * 8);
-    s.wsf = off; off += up256(G * s.Np * 4);
+    s.Mp = (a->M + BM - 1) / BM * BM;
+    s.asf = off; off += up256(G * s.Mp * 4);
+    s.wsf = off; off += up256(G * s.Np * 2);
     s.la16 = off; off += up256((size_t)a->M * a->R * 2);
     s.total = off;
     return s;
@@ -673,14 +731,14 @@ static int launch_t(const nb_gemm_args* a, const TcParams& p, cudaStream_t s) {
     pp.act = static_cast<const uint8_t*>(a->act); pp.wgt = static_cast<const uint8_t*>(a->wgt);
     pp.ascales = a->ascales; pp.wscales = a->wscales; pp.lora_act = static_cast<const float*>(a->lora_act);
     pp.a8 = reinterpret_cast<int8_t*>(base + sc.a8); pp.w8 = reinterpret_cast<int8_t*>(base + sc.w8);
-    pp.asf = reinterpret_cast<float*>(base + sc.asf); pp.wsf = reinterpret_cast<float*>(base + sc.wsf);
+    pp.asf = reinterpret_cast<float*>(base + sc.asf); pp.wsf = base + sc.wsf; pp.Mp = sc.Mp;
     pp.la16 = base + sc.la16;
     pp.act_unsigned = a->act_unsigned;
     pp.M = a->M; pp.N = a->N; pp.K = a->K; pp.R = a->R; pp.Np = sc.Np;
     pp.stride_am = a->stride_am; pp.stride_wn = a->stride_wn; pp.stride_asg = a->stride_asg;
     pp.stride_wsg = a->stride_wsg; pp.stride_lam = a->stride_lam;
     const long long G = a->K / 64;
-    const long long units = (long long)(a->M + a->N) * (a->K / 32) + G * a->M + G * sc.Np +
+    const long long units = (long long)(a->M + a->N) * (a->K / 32) + G * sc.Mp + G * sc.Np +
                             (a->R ? (long long)a->M * (a->R / 8) : 0);
     prepack_kernel<T><<<(unsigned)((units + 255) / 256), 256, 0, s>>>(pp);
     NB_CUDA_CHECK(cudaGetLastError());
@@ -690,10 +748,9 @@ static int launch_t(const nb_gemm_args* a, const TcParams& p, cudaStream_t s) {
                                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     bool ok = make_map(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, pp.a8, a->K, a->M, a->K, 128, BM, CU_TENSOR_MAP_SWIZZLE_128B) &&
               make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, pp.w8, a->K, a->N, a->K, 128, BN, CU_TENSOR_MAP_SWIZZLE_128B) &&
-              make_map(&tm_as, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, pp.asf, (uint64_t)a->M * 2, G, (uint64_t)a->M * 8, 2 * BM, 2,
+              make_map(&tm_as, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, pp.asf, (uint64_t)sc.Mp, G, (uint64_t)sc.Mp * 4, BM, 2,
                        CU_TENSOR_MAP_SWIZZLE_NONE) &&
-              make_map(&tm_ws, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, pp.wsf, sc.Np, G, (uint64_t)sc.Np * 4, BN, 2,
-                       CU_TENSOR_MAP_SWIZZLE_NONE);
+              make_map(&tm_ws, t16, pp.wsf, sc.Np, G, (uint64_t)sc.Np * 2, BN, 2, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (ok && a->R > 0)
         ok = make_map(&tm_la, t16, pp.la16, a->R, a->M, (uint64_t)a->R * 2, 32, BM, CU_TENSOR_MAP_SWIZZLE_64B) &&
              make_map(&tm_lu, t16, a->lora_up, a->R, a->N, (uint64_t)a->stride_lun * 2, 32, BN, CU_TENSOR_MAP_SWIZZLE_64B);

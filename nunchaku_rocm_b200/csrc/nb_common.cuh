@@ -256,6 +256,18 @@ __device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t (&v)
         : "memory");
 }
 
+// the same layout, 16 lanes x 32 columns (j = 0..3)
+__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_16x256b(uint32_t taddr, uint32_t (&v)[32]) { tmem_ld_16x256b_x8(taddr, v); }
+__device__ __forceinline__ void tmem_ld_16x256b(uint32_t taddr, uint32_t (&v)[16]) { tmem_ld_16x256b_x4(taddr, v); }
+
 // packed pairs of fp32 in one 64-bit register (low word = first element) and the sm_100 packed FMA / ADD
 __device__ __forceinline__ uint64_t pack_u32x2(uint32_t lo, uint32_t hi) {
     uint64_t r;
