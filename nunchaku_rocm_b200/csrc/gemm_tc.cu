@@ -1,13 +1,14 @@
-// W4A4 int4 GEMM on the 5th-generation tensor cores (tcgen05.mma kind::i8, int32 accumulators in
-// tensor memory), with the low-rank branch and the fused epilogues.
+// W4A4 int4 GEMM on the 5th-generation tensor cores (tcgen05.mma kind::f8f6f4 on e4m3-encoded int4 values, exact
+// integer-valued fp32 group sums in tensor memory), with the low-rank branch and the fused epilogues.
 //
 // Arithmetic contract (reference: nunchaku/ops/triton/gemm_w4a4.py:446-488 and :155-209): for every
 // 64-wide K group g one EXACT int32 dot p_g[m,n]; acc += float(p_g) * as[g,m] * ws[g,n] in fp32;
 // then + T(lora_act) . lora_up^T (16-bit operands, fp32 accumulate), + bias, one rounding to T.
 //
 // Two launches per call:
-//  1. `prepack_kernel` (HBM-bound, a few microseconds): packed nibbles -> one e4m3 byte per value; scales ->
-//     fp32 in the order the drain reads them; lora_act -> T.  Measured on B200: widening inside the GEMM
+//  1. `prepack_kernel` (HBM-bound, a few microseconds): packed nibbles -> one e4m3 byte per value; row scales ->
+//     fp32, column scales kept as T, both in the order a drain thread reads them (one 128-bit load for its 4 rows, two
+//     for its 16 columns); lora_act -> T.  Measured on B200: widening inside the GEMM
 //     through shared memory costs a generic->async proxy fence of ~3000 cycles per K group and competes with
 //     the drain for issue slots and shared-memory bandwidth; with the operands pre-widened every byte the
 //     tensor core reads is written by TMA and the SM's CUDA cores only do the per-group scaling.
@@ -16,7 +17,8 @@
 //       warp 0    TMA producer: A and W rows (128 x 128 B each, 128-byte swizzle) and the two groups' scale
 //                 rows (no multicast, no cluster); low-rank chunks of 32 ranks travel through the same ring.
 //       warp 1    MMA issuer: per ring stage (two groups) four 128 x 128 x 32 kind::f8f6f4 MMAs into two of FOUR
-//                 tensor-memory slots and ONE tcgen05.commit, which publishes both slots and releases the operands:
+//                 tensor-memory slots (the first group's pair goes out before the issuer waits for the second slot)
+//                 and ONE tcgen05.commit, which publishes both slots and releases the operands:
 //                 the issuing thread pays a few hundred cycles per wait and commit, so the work between two of them has
 //                 to be large.  The low-rank product is kind::f16 into an fp32 slot of the same ring.
 //       warps 2-9 drain: a warp owns 32 rows x 64 columns.  tcgen05.ld.16x256b gives a thread the
@@ -330,27 +332,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 tc_fence_after();
                 tmem_ld_16x256b(lane_base + (ait % NSLOT) * BN, v[0]);
             }
-            // The scales of a group are requested one group ahead (raw: 4 row scales as fp32, 2 NJ column scales as T) and
-            // widened at the top of their group, so their shared-memory latency is off the critical path.
-            uint4 as_n, ws_n[NJ / 4];
-            auto load_scales = [&](uint32_t stage, int i) {
-                const uint8_t* st = smem + C::OFF_ST + stage * C::ST_BYTES + C::ST_A + C::ST_W;
-                as_n = *reinterpret_cast<const uint4*>(st + (i * BM + q * 32 + gid * 4) * 4);  // rows gid, +8, +16, +24
-                const uint4* ws_s = reinterpret_cast<const uint4*>(st + C::ST_AS + (i * BN + half * COLS + tig * NJ * 2) * 2);
-#pragma unroll
-                for (int jj = 0; jj < NJ / 4; ++jj) ws_n[jj] = ws_s[jj];
-            };
-            load_scales(it % STAGES, 0);
             for (int g = 0; g < G; ++g, ++ait) {
                 const int slot = ait % NSLOT;
                 const uint32_t itg = it + (g >> 1);
                 const int s = itg % STAGES, i = g & 1;
-                // scales of this group
-                const uint4 as4 = as_n;
+                // scales of this group: the thread's 4 rows (fp32) and 2 NJ columns (T, widened here)
+                const uint8_t* st = smem + C::OFF_ST + s * C::ST_BYTES + C::ST_A + C::ST_W;
+                const uint4 as4 = *reinterpret_cast<const uint4*>(st + (i * BM + q * 32 + gid * 4) * 4);  // rows gid, +8, +16, +24
                 uint64_t as2[4] = {pack_u32x2(as4.x, as4.x), pack_u32x2(as4.y, as4.y), pack_u32x2(as4.z, as4.z), pack_u32x2(as4.w, as4.w)};
+                const uint4* ws_s = reinterpret_cast<const uint4*>(st + C::ST_AS + (i * BN + half * COLS + tig * NJ * 2) * 2);
                 uint32_t w16[NJ];
 #pragma unroll
-                for (int jj = 0; jj < NJ / 4; ++jj) { const uint4 t4 = ws_n[jj]; w16[4 * jj] = t4.x; w16[4 * jj + 1] = t4.y; w16[4 * jj + 2] = t4.z; w16[4 * jj + 3] = t4.w; }
+                for (int jj = 0; jj < NJ / 4; ++jj) { const uint4 t4 = ws_s[jj]; w16[4 * jj] = t4.x; w16[4 * jj + 1] = t4.y; w16[4 * jj + 2] = t4.z; w16[4 * jj + 3] = t4.w; }
                 ulonglong2 w[NJ / 2];
 #pragma unroll
                 for (int jj = 0; jj < NJ / 2; ++jj) {
@@ -391,7 +384,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             tc_fence_after();
                             tmem_ld_16x256b(lane_base + ((ait + 1) % NSLOT) * BN, v[0]);
                         }
-                        if (g + 1 < G) load_scales((it + ((g + 1) >> 1)) % STAGES, (g + 1) & 1);  // (its stage has been waited for)
                         NB_PF(0);
                     }
 #pragma unroll
@@ -580,7 +572,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 }
 
 // ------------------------------------------------------------------------------------------------
-// pre-pass: nibbles -> int8 (16 * value), scales -> fp32 in drain order, lora_act -> T
+// pre-pass: nibbles -> e4m3 bytes, scales in drain order, lora_act -> T
 // ------------------------------------------------------------------------------------------------
 struct PrepackParams {
     const uint8_t* act; const uint8_t* wgt;
