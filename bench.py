@@ -225,6 +225,28 @@ def whole_job_tops(world: int, ops_per_rank: float, ms_step: float) -> float:
     return world * ops_per_rank / (ms_step * 1e-3) / 1e12
 
 
+def bind_to_gpu_cpus(local: int) -> str:
+    """
+    Run this process on the host cores that sit next to its GPU (the PCI device's ``local_cpulist``), so that the pinned
+    host buffers it allocates afterwards land on that NUMA node.  With one process per GPU and eight GPUs on two sockets,
+    copies from the far socket's memory otherwise share the inter-socket link.  Changes only this process's affinity.
+    """
+    try:
+        pr = torch.cuda.get_device_properties(local)
+        path = f"/sys/bus/pci/devices/{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0/local_cpulist"
+        cpus: set[int] = set()
+        for part in open(path).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)  # stay inside what the container allows
+        if not cpus:
+            return "unchanged (no local cpu allowed)"
+        os.sched_setaffinity(0, cpus)
+        return f"{len(cpus)} cpus local to the GPU"
+    except (OSError, ValueError, AttributeError) as e:
+        return f"unchanged ({type(e).__name__})"
+
+
 def run_ours(args) -> None:
     import torch.distributed as dist
 
@@ -238,6 +260,8 @@ def run_ours(args) -> None:
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path for the product kernels)")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    all_cpus = os.sched_getaffinity(0)
+    affinity = bind_to_gpu_cpus(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
@@ -368,6 +392,7 @@ def run_ours(args) -> None:
                 "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": hx[0].numel() * hx[0].element_size(),
                 "pipelining": "3 steps in flight on upload / compute / download streams",
+                "host_affinity": affinity,
                 "d2h_bytes_per_step": hout[0].numel() * hout[0].element_size(),
             },
             # quantizer + operand pre-pass + GEMM per step
@@ -386,6 +411,7 @@ def run_ours(args) -> None:
             },
         }
         if world == 1 and not args.no_cpu_baseline:
+            os.sched_setaffinity(0, all_cpus)  # the CPU baseline may use every core again
             cb = cpu_baseline(budget_s=20.0, steps=3, warmup=1)
             line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line), flush=True)

@@ -99,9 +99,11 @@ def main():
         n = F.layer_norm(x, (HID,), eps=1e-6) * (1 + scale_msa[:, None]) + shift_msa[:, None]
         return n, gate_msa, shift_mlp, scale_mlp, gate_mlp
 
-    def attention(qkv_txt, qkv_img):
-        # joint attention over text + image tokens: (B, S, 3, H, D) views, no copies besides the concatenation
-        qkv = torch.cat([qkv_txt, qkv_img], dim=1).view(B, TXT + IMG, 3, HEADS, HD)
+    qkv_joint = torch.empty(B, TXT + IMG, 3 * HID, dtype=T, device=dev)
+
+    def attention(qkv):
+        # joint attention over text + image tokens: (B, S, 3, H, D) views of the buffer both projections wrote
+        qkv = qkv.view(B, TXT + IMG, 3, HEADS, HD)
         q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
         o = scaled_dot_product_attention(q, k, v)  # (B, H, S, D) view of (B, S, H * D)
         o = o.transpose(1, 2).reshape(B, TXT + IMG, HID)
@@ -110,9 +112,14 @@ def main():
     def double_block(x_img, x_txt):
         n_img, g_msa, sh_mlp, sc_mlp, g_mlp = ada_zero(img.mod, x_img)
         n_txt, cg_msa, csh_mlp, csc_mlp, cg_mlp = ada_zero(txt.mod, x_txt)
-        qkv_img = fused_qkv_norm_rottary(n_img, img.qkv, img.nq, img.nk, rot_img)
-        qkv_txt = fused_qkv_norm_rottary(n_txt, txt.qkv, txt.nq, txt.nk, rot_txt)
-        a_txt, a_img = attention(qkv_txt, qkv_img)
+        if B == 1:  # both GEMMs write their rows of the joint buffer (a row slice of one batch element is contiguous)
+            fused_qkv_norm_rottary(n_img, img.qkv, img.nq, img.nk, rot_img, output=qkv_joint[0, TXT:])
+            fused_qkv_norm_rottary(n_txt, txt.qkv, txt.nq, txt.nk, rot_txt, output=qkv_joint[0, :TXT])
+            qkv = qkv_joint
+        else:
+            qkv = torch.cat([fused_qkv_norm_rottary(n_txt, txt.qkv, txt.nq, txt.nk, rot_txt),
+                             fused_qkv_norm_rottary(n_img, img.qkv, img.nq, img.nk, rot_img)], dim=1)
+        a_txt, a_img = attention(qkv)
         x_img = x_img + g_msa[:, None] * img.out(a_img.contiguous())
         x_txt = x_txt + cg_msa[:, None] * txt.out(a_txt.contiguous())
         n_img = F.layer_norm(x_img, (HID,), eps=1e-6) * (1 + sc_mlp[:, None]) + sh_mlp[:, None]
