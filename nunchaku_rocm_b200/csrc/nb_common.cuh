@@ -84,15 +84,25 @@ __device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
     return __half2float(*reinterpret_cast<__half*>(&h));
 }
 
+__device__ __forceinline__ float exp2f_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // --------------------------------------------------------------------------------------------
 // the reference's activation functions (nunchaku/ops/triton/_common.py:70-94), fp32
 // --------------------------------------------------------------------------------------------
+// gelu_tanh(x) = 0.5 x (1 + tanh(u)), u = 0.79788456 (x + 0.044715 x^3); with tanh(u) = 2 / (1 + exp(-2u)) - 1 (the
+// reference's form) this is x / (1 + exp(-2u)): one ex2, one reciprocal, five FMA-pipe operations.  exp(-2u) overflows to
+// +inf for large negative x and the quotient is then -0, the limit of the function.
 __device__ __forceinline__ float gelu_tanh(float x) {
-    float inner = 0.79788456f * (x + 0.044715f * x * x * x);
-    float t = 2.0f / (1.0f + __expf(-2.0f * inner)) - 1.0f;
-    return 0.5f * x * (1.0f + t);
+    constexpr float A = -2.0f * 0.79788456f * 1.4426950408889634f;  // -2 * sqrt(2/pi) * log2(e)
+    constexpr float B = A * 0.044715f;
+    const float e = exp2f_approx(x * fmaf(x * x, B, A));
+    return __fdividef(x, 1.0f + e);
 }
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 // round-half-even of |x| < 2^22 by the magic-number add (gemm_w4a4.py:1317-1325)
 __device__ __forceinline__ float rint_small(float x) { return __fsub_rn(__fadd_rn(x, 12582912.0f), 12582912.0f); }

@@ -108,6 +108,11 @@ def main():
                                args.iters, args.warmup)
             work = 2 * M * K + M * K // 2 + 2 * (K // 64) * M + 4 * M * R + 2 * K * R
             emit("quantize_kernel", f"M={M} K={K} R={R} signed int4", ms, best, work, "GB/s", "hbm", hbm, src)
+            if K == 12288:  # the GELU + shift + unsigned re-quantisation between fc1 and fc2 of an MLP
+                ms, best = time_ms(lambda p: quantize_kernel_level(p["x"], p["q"][:M], p["s"][:, :M], p["proj_down"], p["l"][:M],
+                                                                   p["smooth"], fuse_gelu=True, shift_value=0.171875,
+                                                                   unsigned=True), sets, args.iters, args.warmup)
+                emit("quantize_kernel", f"M={M} K={K} R={R} GELU + shift, unsigned int4", ms, best, work, "GB/s", "hbm", hbm, src)
             del sets
 
     # ---------------------------------------------------------------- W4A4 GEMM (tensor pipe)
