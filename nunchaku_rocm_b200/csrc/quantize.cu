@@ -168,6 +168,10 @@ __global__ void __launch_bounds__(QT_MAX_WARPS * 32) quantize_kernel(const QPara
         widen8<T>(xr0[1], *reinterpret_cast<float(*)[8]>(&v[0][8]));
         widen8<T>(xr0[2], *reinterpret_cast<float(*)[8]>(&v[1][0]));
         widen8<T>(xr0[3], *reinterpret_cast<float(*)[8]>(&v[1][8]));
+        // the 16-bit words themselves: the LoRA-down operands when no activation function changes the values
+        const uint32_t raw_w[2][8] = {{xr0[0].x, xr0[0].y, xr0[0].z, xr0[0].w, xr0[1].x, xr0[1].y, xr0[1].z, xr0[1].w},
+                                      {xr0[2].x, xr0[2].y, xr0[2].z, xr0[2].w, xr0[3].x, xr0[3].y, xr0[3].z, xr0[3].w}};
+        const bool raw_ok = !p.fuse_glu && !p.fuse_gelu;
 #pragma unroll
         for (int i = 0; i < 4; ++i) { xr0[i] = xr1[i]; xr1[i] = xr2[i]; }
         if (p.fuse_glu) {
@@ -199,10 +203,14 @@ __global__ void __launch_bounds__(QT_MAX_WARPS * 32) quantize_kernel(const QPara
             for (int i = 0; i < 4; ++i) {
                 // A fragment i: k-slots (2 tig, 2 tig + 1) = elements 4i, 4i+1; slots (2 tig + 8, +9) = 4i+2, 4i+3
                 uint32_t a[4];
-                a[0] = pack2<T>(v[0][4 * i], v[0][4 * i + 1]);
-                a[1] = pack2<T>(v[1][4 * i], v[1][4 * i + 1]);
-                a[2] = pack2<T>(v[0][4 * i + 2], v[0][4 * i + 3]);
-                a[3] = pack2<T>(v[1][4 * i + 2], v[1][4 * i + 3]);
+                if (raw_ok) {
+                    a[0] = raw_w[0][2 * i]; a[1] = raw_w[1][2 * i]; a[2] = raw_w[0][2 * i + 1]; a[3] = raw_w[1][2 * i + 1];
+                } else {
+                    a[0] = pack2<T>(v[0][4 * i], v[0][4 * i + 1]);
+                    a[1] = pack2<T>(v[1][4 * i], v[1][4 * i + 1]);
+                    a[2] = pack2<T>(v[0][4 * i + 2], v[0][4 * i + 3]);
+                    a[3] = pack2<T>(v[1][4 * i + 2], v[1][4 * i + 3]);
+                }
                 // k-slot s of fragment i is column (i < 2 ? 0 : 32) + 8 (s % 8 / 2) + 4 (i % 2) + 2 (s / 8) + s % 2
                 // ldmatrix.x4: lanes 0-7 give the rows of matrix 0 (slots 0-7, ranks +0), 8-15 matrix 1
                 // (slots 8-15, ranks +0), 16-23 matrix 2 (slots 0-7, ranks +8), 24-31 matrix 3 (slots 8-15, +8)
@@ -231,12 +239,14 @@ __global__ void __launch_bounds__(QT_MAX_WARPS * 32) quantize_kernel(const QPara
                 for (int i = 0; i < 16; ++i) v[r][i] += p.shift;
         }
         if (smooth) {
-            float s[16];
-            load8<T>(smooth + c0, true, *reinterpret_cast<float(*)[8]>(&s[0]));
-            load8<T>(smooth + c0 + 32, true, *reinterpret_cast<float(*)[8]>(&s[8]));
+            // The 8 lanes with the same tig hold the same 16 columns.  Each of them takes the correctly rounded reciprocal
+            // (as 1.0f / s) of two of those columns and the others fetch it by shuffle: 2 reciprocals per lane, not 16.
+            const int i0 = 2 * gid;  // element index of this lane's pair among the 16
+            const float2 s2 = unpack2<T>(__ldg(reinterpret_cast<const uint32_t*>(smooth + c0 + (i0 < 8 ? i0 : 24 + i0))));
+            const float r0v = __frcp_rn(s2.x), r1v = __frcp_rn(s2.y);
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                const float inv = __frcp_rn(s[i]);  // the correctly rounded reciprocal, as 1.0f / s
+                const float inv = __shfl_sync(0xffffffffu, (i & 1) ? r1v : r0v, (i >> 1) * 4 + tig);
                 v[0][i] *= inv;
                 v[1][i] *= inv;
             }
