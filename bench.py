@@ -179,6 +179,7 @@ def config_dict(n_gpus: int) -> dict:
         "rank": RANK,
         "parallelism": f"dp{n_gpus} (independent replica per GPU, no collective)",
         "l2": f"{N_SETS} rotating buffer sets (~{N_SETS * 106} MB > 126 MB L2)",
+        "weights": "int4 weights widened to the kernel's operand form once per weight tensor (load-time step), activations every step",
     }
 
 

@@ -78,6 +78,8 @@ typedef struct nb_gemm_args {
     void* status;         /* device int32 the kernel sets non-zero if a bounded wait expires; may be null */
     void* scratch;        /* device scratch, see nb_gemm_w4a4_scratch_bytes(); may be null when that is 0 */
     int64_t scratch_bytes;
+    const void* wgt_prepared;     /* optional: what nb_gemm_w4a4_prepare_weights wrote for this wgt / wscales, or null */
+    int64_t wgt_prepared_bytes;
 } nb_gemm_args;
 
 /* Mirrors `QKNormRopeEpilogue::Args` (w4a4_gfx11.hip:440-446; ctypes `_QKArgs`, w4a4.py:106-115). */
@@ -116,6 +118,20 @@ int nb_gemm_w4a4(const nb_gemm_args* args, const void* epi, int epi_kind, void* 
  * The buffer must be 256-byte aligned; its contents are dead when the call's kernels have run.
  */
 int64_t nb_gemm_w4a4_scratch_bytes(const nb_gemm_args* args, const void* epi, int epi_kind);
+
+/*
+ * Load-time half of the int4 tensor-core path.  The weights of a layer do not change between calls, so the form the
+ * kernel's TMA loads read (one e4m3 byte per int4 value, column scales in the drain's order) can be written once instead
+ * of by every call's pre-pass: the role of the reference's load-time weight packing (`NunchakuWeightPacker`,
+ * nunchaku/utils.py) for its MMA layout.  `args` needs wgt, wscales, N, K, dtype and the two strides.
+ * nb_gemm_w4a4_prepared_bytes returns the size of the buffer (0: this weight cannot use the tensor-core kernel, e.g.
+ * NVFP4 or K % 64 != 0); nb_gemm_w4a4_prepare_weights fills it (256-byte aligned) on `stream`.  A later nb_gemm_w4a4 call
+ * with the same wgt / wscales / N / K / dtype may pass it as `wgt_prepared`; it then needs less scratch (ask
+ * nb_gemm_w4a4_scratch_bytes with the field set) and skips that part of the pre-pass.  The generic kernel ignores it.
+ * The caller must drop the buffer when it changes the weights.
+ */
+int64_t nb_gemm_w4a4_prepared_bytes(const nb_gemm_args* args);
+int nb_gemm_w4a4_prepare_weights(const nb_gemm_args* args, void* dst, int64_t dst_bytes, void* stream);
 
 /* 1 when nb_gemm_w4a4 would run this call on the tcgen05 kernel, 0 when on the generic kernel. */
 int64_t nb_gemm_w4a4_uses_tcgen05(const nb_gemm_args* args, const void* epi, int epi_kind);

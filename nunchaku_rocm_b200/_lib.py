@@ -38,6 +38,7 @@ class GemmArgs(C.Structure):
             for n in ("stride_am", "stride_wn", "stride_asg", "stride_wsg", "stride_om", "stride_lam", "stride_lun")
         ]
         + [("status", C.c_void_p), ("scratch", C.c_void_p), ("scratch_bytes", C.c_int64)]
+        + [("wgt_prepared", C.c_void_p), ("wgt_prepared_bytes", C.c_int64)]
     )
 
 
@@ -115,6 +116,10 @@ def lib() -> C.CDLL:
                 l.nb_gemm_w4a4_noalloc.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_int, C.c_void_p]
                 l.nb_gemm_w4a4_uses_tcgen05.restype = C.c_int64
                 l.nb_gemm_w4a4_uses_tcgen05.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_int]
+                l.nb_gemm_w4a4_prepared_bytes.restype = C.c_int64
+                l.nb_gemm_w4a4_prepared_bytes.argtypes = [C.POINTER(GemmArgs)]
+                l.nb_gemm_w4a4_prepare_weights.restype = C.c_int
+                l.nb_gemm_w4a4_prepare_weights.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_int64, C.c_void_p]
                 l.nb_gemm_w4a4_group_sums.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_void_p]
                 l.nb_quantize_w4a4.argtypes = [C.POINTER(QuantArgs), C.c_void_p]
                 l.nb_attention.argtypes = [C.POINTER(AttnArgs), C.c_void_p]

@@ -580,6 +580,7 @@ struct PrepackParams {
     int8_t* a8; int8_t* w8; float* asf; void* wsf; void* la16;
     int M, N, K, R, Np, Mp;  // Np, Mp: N, M rounded up to 128
     int act_unsigned;
+    int do_act, do_wgt;      // which half of the work this launch does (activation side / weight side)
     long long stride_am, stride_wn, stride_asg, stride_wsg, stride_lam;
 };
 
@@ -600,10 +601,10 @@ template <typename T>
 __global__ void __launch_bounds__(256) prepack_kernel(const PrepackParams p) {
     const long long tid = (long long)blockIdx.x * 256 + threadIdx.x;
     const int upr = p.K / 32;  // 16-byte packed units per row
-    const long long a_units = (long long)p.M * upr, w_units = (long long)p.N * upr;
+    const long long a_units = p.do_act ? (long long)p.M * upr : 0, w_units = p.do_wgt ? (long long)p.N * upr : 0;
     const int G = p.K / 64;
-    const long long as_units = (long long)G * p.Mp, ws_units = (long long)G * p.Np;
-    const long long la_units = p.R ? (long long)p.M * (p.R / 8) : 0;
+    const long long as_units = p.do_act ? (long long)G * p.Mp : 0, ws_units = p.do_wgt ? (long long)G * p.Np : 0;
+    const long long la_units = (p.do_act && p.R) ? (long long)p.M * (p.R / 8) : 0;
     if (tid < a_units + w_units) {
         const bool is_w = tid >= a_units;
         const long long u = is_w ? tid - a_units : tid;
@@ -693,8 +694,27 @@ static bool make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, u
 
 static inline size_t up256(size_t x) { return (x + 255) & ~size_t(255); }
 
+// The weight side (w8, wsf) lives in the caller's prepared buffer when there is one, else in the call's scratch after the
+// activation side.
+struct Prepared {
+    size_t w8, wsf, total;
+    int Np;
+};
+static Prepared prepared_layout(const nb_gemm_args* a) {
+    Prepared s;
+    s.Np = (a->N + BN - 1) / BN * BN;
+    size_t off = 0;
+    s.w8 = off; off += up256((size_t)a->N * a->K);
+    s.wsf = off; off += up256((size_t)(a->K / 64) * s.Np * 2);
+    s.total = off;
+    return s;
+}
+static bool has_prepared(const nb_gemm_args* a) {
+    return a->wgt_prepared && a->wgt_prepared_bytes >= (int64_t)prepared_layout(a).total &&
+           (reinterpret_cast<uintptr_t>(a->wgt_prepared) & 255) == 0;
+}
 struct Scratch {
-    size_t a8, w8, asf, wsf, la16, total;
+    size_t a8, asf, la16, wside, total;
     int Np, Mp;
 };
 static Scratch scratch_layout(const nb_gemm_args* a) {
@@ -703,13 +723,35 @@ static Scratch scratch_layout(const nb_gemm_args* a) {
     s.Np = (a->N + BN - 1) / BN * BN;
     size_t off = 0;
     s.a8 = off; off += up256((size_t)a->M * a->K);
-    s.w8 = off; off += up256((size_t)a->N * a->K);
     s.Mp = (a->M + BM - 1) / BM * BM;
     s.asf = off; off += up256(G * s.Mp * 4);
-    s.wsf = off; off += up256(G * s.Np * 2);
     s.la16 = off; off += up256((size_t)a->M * a->R * 2);
+    s.wside = off;
+    if (!has_prepared(a)) off += prepared_layout(a).total;
     s.total = off;
     return s;
+}
+
+static void fill_prepack_params(PrepackParams& pp, const nb_gemm_args* a) {
+    pp.act = static_cast<const uint8_t*>(a->act); pp.wgt = static_cast<const uint8_t*>(a->wgt);
+    pp.ascales = a->ascales; pp.wscales = a->wscales; pp.lora_act = static_cast<const float*>(a->lora_act);
+    pp.act_unsigned = a->act_unsigned;
+    pp.M = a->M; pp.N = a->N; pp.K = a->K; pp.R = a->R;
+    pp.Np = (a->N + BN - 1) / BN * BN; pp.Mp = (a->M + BM - 1) / BM * BM;
+    pp.stride_am = a->stride_am; pp.stride_wn = a->stride_wn; pp.stride_asg = a->stride_asg;
+    pp.stride_wsg = a->stride_wsg; pp.stride_lam = a->stride_lam;
+}
+
+template <typename T>
+static int launch_prepack(const PrepackParams& pp, cudaStream_t s) {
+    const long long G = pp.K / 64;
+    long long units = 0;
+    if (pp.do_act) units += (long long)pp.M * (pp.K / 32) + G * pp.Mp + (pp.R ? (long long)pp.M * (pp.R / 8) : 0);
+    if (pp.do_wgt) units += (long long)pp.N * (pp.K / 32) + G * pp.Np;
+    if (units == 0) return NB_OK;
+    prepack_kernel<T><<<(unsigned)((units + 255) / 256), 256, 0, s>>>(pp);
+    NB_CUDA_CHECK(cudaGetLastError());
+    return NB_OK;
 }
 
 template <int EPI, typename T, bool DEBUG_P>
@@ -719,22 +761,21 @@ static int launch_t(const nb_gemm_args* a, const TcParams& p, cudaStream_t s) {
     if (!a->scratch || a->scratch_bytes < (int64_t)sc.total || (reinterpret_cast<uintptr_t>(a->scratch) & 255))
         return NB_ERR_INVALID;
     uint8_t* base = static_cast<uint8_t*>(a->scratch);
+    const bool prepared = has_prepared(a);
+    const Prepared pl = prepared_layout(a);
+    uint8_t* wbase = prepared ? const_cast<uint8_t*>(static_cast<const uint8_t*>(a->wgt_prepared)) : base + sc.wside;
     PrepackParams pp;
-    pp.act = static_cast<const uint8_t*>(a->act); pp.wgt = static_cast<const uint8_t*>(a->wgt);
-    pp.ascales = a->ascales; pp.wscales = a->wscales; pp.lora_act = static_cast<const float*>(a->lora_act);
-    pp.a8 = reinterpret_cast<int8_t*>(base + sc.a8); pp.w8 = reinterpret_cast<int8_t*>(base + sc.w8);
-    pp.asf = reinterpret_cast<float*>(base + sc.asf); pp.wsf = base + sc.wsf; pp.Mp = sc.Mp;
+    fill_prepack_params(pp, a);
+    pp.a8 = reinterpret_cast<int8_t*>(base + sc.a8); pp.asf = reinterpret_cast<float*>(base + sc.asf);
     pp.la16 = base + sc.la16;
-    pp.act_unsigned = a->act_unsigned;
-    pp.M = a->M; pp.N = a->N; pp.K = a->K; pp.R = a->R; pp.Np = sc.Np;
-    pp.stride_am = a->stride_am; pp.stride_wn = a->stride_wn; pp.stride_asg = a->stride_asg;
-    pp.stride_wsg = a->stride_wsg; pp.stride_lam = a->stride_lam;
-    const long long G = a->K / 64;
-    const long long units = (long long)(a->M + a->N) * (a->K / 32) + G * sc.Mp + G * sc.Np +
-                            (a->R ? (long long)a->M * (a->R / 8) : 0);
-    prepack_kernel<T><<<(unsigned)((units + 255) / 256), 256, 0, s>>>(pp);
-    NB_CUDA_CHECK(cudaGetLastError());
+    pp.w8 = reinterpret_cast<int8_t*>(wbase + pl.w8); pp.wsf = wbase + pl.wsf;
+    pp.do_act = 1; pp.do_wgt = prepared ? 0 : 1;
+    {
+        const int st = launch_prepack<T>(pp, s);
+        if (st != NB_OK) return st;
+    }
 
+    const long long G = a->K / 64;
     CUtensorMap tm_a, tm_w, tm_as, tm_ws, tm_la, tm_lu;
     const CUtensorMapDataType t16 = std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -768,6 +809,27 @@ extern "C" int nb_debug_set_prof(void* ptr) {
     return cudaMemcpyToSymbol(tc::g_prof, &v, sizeof(v)) == cudaSuccess ? 0 : 3;
 }
 #endif
+
+// What a weight must satisfy for the tensor-core kernel, whatever the call around it looks like.
+static bool tc_weight_ok(const nb_gemm_args* a) {
+    return a && a->wgt && a->wscales && !a->fp4 && a->N > 0 && a->K > 0 && a->K % 64 == 0 && a->N % 8 == 0 &&
+           aligned16(a->wgt) && a->stride_wn % 16 == 0 && (a->dtype == NB_DTYPE_BF16 || a->dtype == NB_DTYPE_FP16);
+}
+
+int64_t tc_prepared_bytes(const nb_gemm_args* a) { return tc_weight_ok(a) ? (int64_t)tc::prepared_layout(a).total : 0; }
+
+int tc_prepare_weights(const nb_gemm_args* a, void* dst, int64_t dst_bytes, cudaStream_t s) {
+    if (!tc_weight_ok(a)) return NB_ERR_UNSUPPORTED;
+    const tc::Prepared pl = tc::prepared_layout(a);
+    if (!dst || dst_bytes < (int64_t)pl.total || (reinterpret_cast<uintptr_t>(dst) & 255)) return NB_ERR_INVALID;
+    tc::PrepackParams pp = {};
+    pp.wgt = static_cast<const uint8_t*>(a->wgt); pp.wscales = a->wscales;
+    pp.N = a->N; pp.K = a->K; pp.Np = pl.Np;
+    pp.stride_wn = a->stride_wn; pp.stride_wsg = a->stride_wsg;
+    pp.w8 = reinterpret_cast<int8_t*>(static_cast<uint8_t*>(dst) + pl.w8); pp.wsf = static_cast<uint8_t*>(dst) + pl.wsf;
+    pp.do_act = 0; pp.do_wgt = 1;
+    return a->dtype == NB_DTYPE_BF16 ? tc::launch_prepack<__nv_bfloat16>(pp, s) : tc::launch_prepack<__half>(pp, s);
+}
 
 // Why the tcgen05 kernel cannot take this call, or nullptr (the role of `unsupported_reason`,
 // nunchaku/ops/triton/native/w4a4.py:164-231).

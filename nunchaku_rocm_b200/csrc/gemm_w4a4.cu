@@ -28,6 +28,8 @@ int launch_requant_rows(const float* lin, int M, int N, int mode, int dtype, con
 const char* tc_unsupported_reason(const nb_gemm_args* a, const void* epi, int epi_kind);
 int launch_tc(const nb_gemm_args* a, const void* epi, int epi_kind, int32_t* p_out, cudaStream_t s);
 int64_t tc_scratch_bytes(const nb_gemm_args* a);
+int64_t tc_prepared_bytes(const nb_gemm_args* a);
+int tc_prepare_weights(const nb_gemm_args* a, void* dst, int64_t dst_bytes, cudaStream_t s);
 const char* tc_fp4_unsupported_reason(const nb_gemm_args* a, const void* epi, int epi_kind);
 int launch_tc_fp4(const nb_gemm_args* a, cudaStream_t s);
 int64_t tc_fp4_scratch_bytes(const nb_gemm_args* a);
@@ -117,6 +119,12 @@ extern "C" int nb_gemm_w4a4(const nb_gemm_args* a, const void* epi, int epi_kind
                               static_cast<const nb_qk_args*>(epi), s);
     return launch_requant_rows(p.acc_out, a->M, a->N, epi_kind == NB_EPI_GELU_QUANT ? 0 : 1, a->dtype,
                                static_cast<const nb_requant_args*>(epi), s);
+}
+
+extern "C" int64_t nb_gemm_w4a4_prepared_bytes(const nb_gemm_args* a) { return nb::tc_prepared_bytes(a); }
+
+extern "C" int nb_gemm_w4a4_prepare_weights(const nb_gemm_args* a, void* dst, int64_t dst_bytes, void* stream) {
+    return nb::tc_prepare_weights(a, dst, dst_bytes, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int64_t nb_gemm_w4a4_uses_tcgen05(const nb_gemm_args* a, const void* epi, int epi_kind) {

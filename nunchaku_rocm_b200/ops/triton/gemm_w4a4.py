@@ -12,7 +12,9 @@ Layouts are the natural ones of nunchaku/ops/triton/gemm_w4a4.py:4-19: ``act`` `
 
 from __future__ import annotations
 
+import collections
 import ctypes as C
+import os
 
 import torch
 
@@ -203,8 +205,76 @@ def _checks(act, wgt, out2d, ascales, wscales, bias, lora_act_in, lora_up, wcsca
             raise ValueError("LoRA tensors need unit inner stride")
 
 
-def _run(a, epi, epi_kind, act):
+# ------------------------------------------------------------------------------------------------
+# Load-time form of the weights for the int4 tensor-core kernel
+# ------------------------------------------------------------------------------------------------
+# A layer's weights do not change between calls, so the form the kernel's TMA loads read (one e4m3 byte per int4 value,
+# column scales in the drain's order) is written once per weight and kept: the counterpart of the reference's load-time
+# weight packing.  An entry keeps the weight and scale tensors alive (so their addresses cannot be handed to other
+# tensors while it exists) and is dropped when either has been modified in place (torch's version counter) or when the
+# prepared buffers exceed the budget (least recently used first).  NUNCHAKU_B200_PREPARED_WEIGHTS_MB=0 turns it off.
+_PREPARED: "collections.OrderedDict[tuple, tuple]" = collections.OrderedDict()
+_PREPARED_BYTES = 0
+
+
+def _prepared_budget(device) -> int:
+    mb = os.environ.get("NUNCHAKU_B200_PREPARED_WEIGHTS_MB")
+    if mb is not None:
+        return int(mb) << 20
+    return torch.cuda.get_device_properties(device).total_memory // 4
+
+
+def clear_prepared_weights() -> None:
+    """Drop every prepared weight buffer (and the references to the weights they were made from)."""
+    global _PREPARED_BYTES
+    _PREPARED.clear()
+    _PREPARED_BYTES = 0
+
+
+def _attach_prepared(a, wgt, wscales) -> None:
+    global _PREPARED_BYTES
+    budget = _prepared_budget(wgt.device)
+    if budget <= 0:
+        return
+    key = (wgt.device.index, wgt.data_ptr(), wscales.data_ptr(), a.N, a.K, a.stride_wn, a.stride_wsg, a.dtype)
+    stream = torch.cuda.current_stream(wgt.device)
+    e = _PREPARED.get(key)
+    if e is not None and (e[1] != wgt._version or e[3] != wscales._version):
+        _PREPARED_BYTES -= e[4].numel()
+        del _PREPARED[key]
+        e = None
+    if e is None:
+        if torch.cuda.is_current_stream_capturing():
+            return  # no allocation that outlives a graph capture: this call runs the whole pre-pass
+        lib = L.lib()
+        nbytes = lib.nb_gemm_w4a4_prepared_bytes(C.byref(a))
+        if nbytes <= 0 or nbytes > budget:
+            return
+        while _PREPARED and _PREPARED_BYTES + nbytes > budget:
+            _, old = _PREPARED.popitem(last=False)
+            _PREPARED_BYTES -= old[4].numel()
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=wgt.device)
+        with torch.cuda.device(wgt.device):
+            L.check(lib.nb_gemm_w4a4_prepare_weights(C.byref(a), L.ptr(buf), nbytes, L.stream_of(wgt)), "prepare_weights")
+        done = torch.cuda.Event()
+        done.record(stream)
+        e = (wgt, wgt._version, wscales, wscales._version, buf, done, stream)
+        _PREPARED[key] = e
+        _PREPARED_BYTES += nbytes
+    else:
+        _PREPARED.move_to_end(key)
+        # Another stream must not read the buffer before the kernel that wrote it has run.  (Inside a graph capture no
+        # dependency on outside work can be recorded; a capture starts after the capturing stream has joined the
+        # streams whose results it uses, which covers a buffer prepared before.)
+        if e[6] != stream and not torch.cuda.is_current_stream_capturing() and not e[5].query():
+            stream.wait_event(e[5])
+    a.wgt_prepared, a.wgt_prepared_bytes = L.ptr(e[4]), e[4].numel()
+
+
+def _run(a, epi, epi_kind, act, wgt=None, wscales=None):
     lib = L.lib()
+    if wgt is not None and not a.fp4 and lib.nb_gemm_w4a4_uses_tcgen05(C.byref(a), epi, epi_kind) == 1:
+        _attach_prepared(a, wgt, wscales)
     need = lib.nb_gemm_w4a4_scratch_bytes(C.byref(a), epi, epi_kind)
     scratch = None
     if need > 0:
@@ -276,7 +346,7 @@ def gemm_w4a4(
         qout2d = qout.reshape(-1, qout.shape[-1])
         a = _gemm_args(act, wgt, None, ascales, wscales, bias, la, lu, None, act_unsigned, False, False, 1.0, dtype, _impl)
         q = _requant_args(qout2d, oscales, smooth_factor, lora_down, lora_act_out, 0.0, N // 2, M, dtype)
-        _run(a, C.byref(q), L.EPI_SWIGLU_QUANT, act)
+        _run(a, C.byref(q), L.EPI_SWIGLU_QUANT, act, wgt, wscales)
         return None
 
     want_quant = qout is not None or oscales is not None
@@ -314,7 +384,7 @@ def gemm_w4a4(
         q = _requant_args(qout2d, oscales, smooth_factor, lora_down, lora_act_out, GELU_SHIFT, N, M, dtype)
         fused_fast = L.lib().nb_gemm_w4a4_uses_tcgen05(C.byref(a), C.byref(q), L.EPI_GELU_QUANT) == 1
         if fused_fast or _impl == L.IMPL_GENERIC:
-            _run(a, C.byref(q), L.EPI_GELU_QUANT, act)
+            _run(a, C.byref(q), L.EPI_GELU_QUANT, act, wgt, wscales)
             return out
         # no fused tensor-core kernel for this call: GEMM to a 16-bit tile, then the quantizer with the
         # GELU fused in, as the reference does for calls its fused kernel does not take (gemm_w4a4.py:1298-1312)
@@ -334,9 +404,9 @@ def gemm_w4a4(
         if nq.dtype != dtype or nk.dtype != dtype or nq.numel() != HEAD_DIM or nk.numel() != HEAD_DIM:
             raise ValueError(f"norm_q/norm_k must be ({HEAD_DIM},) tensors of the output dtype")
         q = L.QKArgs(L.ptr(nq), L.ptr(nk), L.ptr(rot), rot.stride(0), S, 1e-6)
-        _run(a, C.byref(q), L.EPI_QK, act)
+        _run(a, C.byref(q), L.EPI_QK, act, wgt, wscales)
     else:
-        _run(a, None, L.EPI_STORE, act)
+        _run(a, None, L.EPI_STORE, act, wgt, wscales)
         if want_qk:
             _apply_rmsnorm_rope_qk(out2d, norm_q, norm_k, rotary_emb)
 

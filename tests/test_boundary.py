@@ -28,7 +28,7 @@ def test_struct_sizes_match_the_header():
     # natural alignment, no packing pragmas: sizes computed from the header's field lists
     from nunchaku_rocm_b200 import _lib
 
-    assert ctypes_size(_lib.GemmArgs) == 9 * 8 + 10 * 4 + 4 + 4 + 7 * 8 + 3 * 8  # pad after alpha to 8
+    assert ctypes_size(_lib.GemmArgs) == 9 * 8 + 10 * 4 + 4 + 4 + 7 * 8 + 3 * 8 + 2 * 8  # pad after alpha to 8
     assert ctypes_size(_lib.QKArgs) == 3 * 8 + 8 + 4 + 4
     assert ctypes_size(_lib.RequantArgs) == 5 * 8 + 4 + 4 + 4 * 8
     assert ctypes_size(_lib.QuantArgs) == 6 * 8 + 8 * 4 + 4 + 4 + 5 * 8

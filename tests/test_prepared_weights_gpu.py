@@ -1,0 +1,93 @@
+"""
+Load-time weight preparation of the int4 tensor-core GEMM (`nb_gemm_w4a4_prepare_weights`): a call that is handed the
+prepared buffer must give bit-identical results to one that widens the weights in its own pre-pass, and the operator
+layer's cache must notice in-place weight updates.
+"""
+
+import ctypes as C
+
+import pytest
+import torch
+
+from nunchaku_rocm_b200 import _lib as L
+from nunchaku_rocm_b200.ops.triton import gemm_w4a4 as G
+
+pytestmark = pytest.mark.gpu
+T = torch.bfloat16
+
+
+def _inputs(dev, M=300, N=384, K=512, R=32, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    p = dict(
+        act=torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, generator=g),
+        wgt=torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g),
+        ascales=(torch.rand(K // 64, M, generator=g) * 0.05 + 0.01).to(T),
+        wscales=(torch.rand(K // 64, N, generator=g) * 0.02 + 0.005).to(T),
+        bias=(torch.randn(N, generator=g) * 0.1).to(T),
+        lora_act=torch.randn(M, R, generator=g) * 0.1,
+        lora_up=(torch.randn(N, R, generator=g) * 0.05).to(T),
+    )
+    return {k: v.to(dev) for k, v in p.items()}
+
+
+def _call(p, monkeypatch=None, disabled=False):
+    if disabled:
+        monkeypatch.setenv("NUNCHAKU_B200_PREPARED_WEIGHTS_MB", "0")
+    elif monkeypatch is not None:
+        monkeypatch.delenv("NUNCHAKU_B200_PREPARED_WEIGHTS_MB", raising=False)
+    out = torch.empty(p["act"].shape[0], p["wgt"].shape[0], dtype=T, device=p["act"].device)
+    G.gemm_w4a4(p["act"], p["wgt"], out, p["ascales"], p["wscales"], p["bias"], p["lora_act"], p["lora_up"])
+    return out
+
+
+def test_prepared_and_unprepared_calls_agree_bit_for_bit(cuda_dev, monkeypatch):
+    p = _inputs(cuda_dev)
+    G.clear_prepared_weights()
+    ref = _call(p, monkeypatch, disabled=True)
+    assert not G._PREPARED
+    first = _call(p, monkeypatch)   # prepares
+    assert len(G._PREPARED) == 1
+    second = _call(p, monkeypatch)  # reuses
+    assert len(G._PREPARED) == 1
+    assert torch.equal(ref, first) and torch.equal(ref, second)
+    assert L.device_status(cuda_dev) == 0
+
+
+def test_in_place_weight_update_invalidates_the_entry(cuda_dev, monkeypatch):
+    p = _inputs(cuda_dev, seed=1)
+    G.clear_prepared_weights()
+    before = _call(p, monkeypatch)
+    g = torch.Generator().manual_seed(2)
+    p["wgt"].copy_(torch.randint(0, 256, p["wgt"].shape, dtype=torch.uint8, generator=g).to(cuda_dev))
+    after = _call(p, monkeypatch)
+    assert not torch.equal(before, after)
+    assert torch.equal(after, _call(p, monkeypatch, disabled=True))
+    # scales too
+    p["wscales"].mul_(2)
+    assert torch.equal(_call(p, monkeypatch), _call(p, monkeypatch, disabled=True))
+    # a view of the same memory (the int8 parameter seen as uint8) shares the entry
+    n = len(G._PREPARED)
+    q = dict(p, wgt=p["wgt"].view(torch.int8).view(torch.uint8))
+    assert torch.equal(_call(q, monkeypatch), _call(p, monkeypatch)) and len(G._PREPARED) == n
+    G.clear_prepared_weights()
+    assert not G._PREPARED
+
+
+def test_c_abi_prepared_bytes_and_scratch(cuda_dev):
+    p = _inputs(cuda_dev, M=256, N=256, K=256)
+    out = torch.empty(256, 256, dtype=T, device=cuda_dev)
+    a = G._gemm_args(p["act"], p["wgt"], out, p["ascales"], p["wscales"], p["bias"], p["lora_act"], p["lora_up"], None,
+                     False, False, False, 1.0, T, L.IMPL_AUTO)
+    lib = L.lib()
+    nbytes = lib.nb_gemm_w4a4_prepared_bytes(C.byref(a))
+    assert nbytes >= 256 * 256 + (256 // 64) * 256 * 2
+    need_plain = lib.nb_gemm_w4a4_scratch_bytes(C.byref(a), None, L.EPI_STORE)
+    buf = torch.empty(nbytes, dtype=torch.uint8, device=cuda_dev)
+    assert lib.nb_gemm_w4a4_prepare_weights(C.byref(a), L.ptr(buf), nbytes - 1, None) != 0  # too small
+    assert lib.nb_gemm_w4a4_prepare_weights(C.byref(a), L.ptr(buf), nbytes, L.stream_of(out)) == 0
+    a.wgt_prepared, a.wgt_prepared_bytes = L.ptr(buf), nbytes
+    need_prepared = lib.nb_gemm_w4a4_scratch_bytes(C.byref(a), None, L.EPI_STORE)
+    assert need_prepared == need_plain - nbytes
+    # NVFP4 weights have no prepared form
+    a.fp4 = 1
+    assert lib.nb_gemm_w4a4_prepared_bytes(C.byref(a)) == 0
