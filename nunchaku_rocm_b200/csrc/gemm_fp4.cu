@@ -14,10 +14,16 @@
 // chunks with one bulk copy and moves each chunk into tensor memory with tcgen05.cp (32 x 128 bit, broadcast to the
 // four lane quarters) right before the MMA that uses it.
 //
-// Roles: warp 0 producer, warp 1 MMA issuer and tensor-memory owner, warps 2-5 epilogue (one per lane quarter).  Tensor
-// memory: two accumulator slots of 128 columns (the epilogue of tile t overlaps the main loop of tile t + 1), one
-// low-rank slot, and 32 columns of scales per ring stage.  Every mbarrier wait is bounded; on expiry the CTA records a
-// code in the status word and unwinds.
+// Roles: warp 0 producer, warp 1 MMA issuer and tensor-memory owner, warps 2-5 epilogue (one per lane quarter).
+//
+// Two tile widths.  The kernel is bound by operand delivery (TMA from L2 reaches about 25 B/clk/SM on B200, the MMAs of a
+// 256-k stage need a sixth of the time its 36 KB take to arrive), so the wide variant, 128 x 256, loads the A rows once
+// for twice the output columns: 54 KB per stage for twice the work.  Tensor memory, 128 x 128: two accumulator slots (the
+// epilogue of tile t overlaps the main loop of tile t + 1), a low-rank slot, 32 columns of scales per ring stage.
+// 128 x 256: one accumulator slot of 256 columns (the ring keeps filling during the epilogue, which is shorter than the
+// ring is deep), a 128-column low-rank slot that serves the two column halves one after the other (the low-rank K loop
+// runs once per half), two buffers of 48 scale columns (tcgen05.cp and tcgen05.mma of one thread execute in issue order).
+// Every mbarrier wait is bounded; on expiry the CTA records a code in the status word and unwinds.
 #include <cuda.h>
 
 #include <type_traits>
@@ -27,21 +33,34 @@
 namespace nb {
 namespace fp4 {
 
-constexpr int BM = 128, BN = 128;
-constexpr int STAGES = 4;
+constexpr int BM = 128;
 constexpr int KSTAGE = 256;                 // k per ring stage = 128 bytes of packed codes per row
 constexpr int EPI_WARPS = 4;
 constexpr int NTHREADS = 64 + EPI_WARPS * 32;
-constexpr int ST_A = BM * 128, ST_W = BN * 128, ST_SF = 4 * 512;  // four 64-k steps per stage
-constexpr int ST_BYTES = ST_A + ST_W + 2 * ST_SF;
-constexpr int OFF_BAR = STAGES * ST_BYTES;
-constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-constexpr uint32_t TM_ACC = 0, TM_LORA = 2 * BN, TM_SF = 3 * BN;  // tensor-memory columns
-static_assert(ST_BYTES % 1024 == 0, "stage buffers must stay 1 KB aligned for the 128-byte swizzle");
-static_assert(TM_SF + STAGES * 32 <= 512, "tensor memory budget");
+constexpr int MAX_STAGES = 4;
+template <int BN_>
+struct Cfg {
+    static constexpr int BN = BN_;
+    static constexpr int NH = BN / 128;                  // 128-column halves of a tile
+    static constexpr int STAGES = 4;
+    static constexpr int ST_A = BM * 128, ST_W = BN * 128;
+    static constexpr int ST_SFA = 4 * 512, ST_SFB = NH * 4 * 512;  // four 64-k steps per stage
+    static constexpr int ST_BYTES = ST_A + ST_W + ST_SFA + ST_SFB;
+    static constexpr int OFF_BAR = STAGES * ST_BYTES;
+    static constexpr int OFF_EPI = OFF_BAR + 256;           // per epilogue warp: wcscale and bias of the tile's columns, fp32
+    static constexpr int EPI_BYTES = EPI_WARPS * 2 * BN * 4;
+    static constexpr int SMEM_BYTES = OFF_EPI + EPI_BYTES + 1024;
+    static constexpr int ACC_SLOTS = BN == 128 ? 2 : 1;
+    static constexpr uint32_t TM_ACC = 0, TM_LORA = 256, TM_SF = 384;  // tensor-memory columns
+    static constexpr int SF_STEP = 4 + 4 * NH;           // scale columns of one 64-k step: A, then B per half
+    static constexpr int SF_BUFS = BN == 128 ? STAGES : 2;
+    static_assert(ST_BYTES % 1024 == 0, "stage buffers must stay 1 KB aligned for the 128-byte swizzle");
+    static_assert(TM_SF + SF_BUFS * 4 * SF_STEP <= 512, "tensor memory budget");
+    static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+};
 
-enum { B_FULL = 0, B_EMPTY = B_FULL + STAGES, B_ACC_FULL = B_EMPTY + STAGES, B_ACC_EMPTY = B_ACC_FULL + 2,
-       B_LR_EMPTY = B_ACC_EMPTY + 2, B_COUNT = B_LR_EMPTY + 1 };
+enum { B_FULL = 0, B_EMPTY = B_FULL + MAX_STAGES, B_ACC_FULL = B_EMPTY + MAX_STAGES, B_ACC_EMPTY = B_ACC_FULL + 2,
+       B_LR_FULL = B_ACC_EMPTY + 2, B_LR_EMPTY = B_LR_FULL + 1, B_COUNT = B_LR_EMPTY + 1 };
 enum { E_PROD = 0x110, E_MMA = 0x130, E_EPI = 0x140 };
 
 struct Params {
@@ -107,10 +126,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "memory");
 }
 
-template <typename T>
+template <typename T, int BN_>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                 const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lu, const Params p) {
+    using C = Cfg<BN_>;
+    constexpr int BN = C::BN, NH = C::NH, STAGES = C::STAGES, ST_BYTES = C::ST_BYTES, ST_A = C::ST_A, ST_W = C::ST_W;
+    constexpr int OFF_BAR = C::OFF_BAR, ACC_SLOTS = C::ACC_SLOTS;
+    constexpr uint32_t TM_ACC = C::TM_ACC, TM_LORA = C::TM_LORA, TM_SF = C::TM_SF;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t s_base = smem_u32(smem);
@@ -123,6 +146,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), EPI_WARPS); }
+        mbar_init(bar(B_LR_FULL), 1);
         mbar_init(bar(B_LR_EMPTY), EPI_WARPS);
         *abort_s = 0;
         fence_barrier_init();
@@ -153,20 +177,28 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             bool ok = true;
             for (int t = t_begin; t < t_end && ok; ++t) {
                 const int mt = t / NT, nt = t % NT;
-                for (int j = 0; j < KS + LCH; ++j, ++it) {
+                // 128 x 128: the K loop, then the low-rank K loop.  128 x 256: the low-rank K loop of the first 128-column
+                // half, the K loop, then the low-rank K loop of the second half (the issuer consumes them in this order)
+                for (int jj = 0; jj < KS + NH * LCH; ++jj, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(bar(B_EMPTY + s), ((it / STAGES) & 1) ^ 1, abort_s, E_PROD | 1, 500)) { ok = false; break; }
                     const uint32_t dst = s_base + s * ST_BYTES;
+                    // position in the old order (K loop first): j < KS is a K-loop stage, else low-rank stage j - KS
+                    const int j = NH == 1 ? jj : (jj < LCH ? KS + jj : (jj < LCH + KS ? jj - LCH : jj));
                     if (j < KS) {
                         mbar_expect_tx(bar(B_FULL + s), ST_BYTES);
                         tma_load_2d(dst, &tm_a, bar(B_FULL + s), j * 128, mt * BM);
                         tma_load_2d(dst + ST_A, &tm_w, bar(B_FULL + s), j * 128, nt * BN);
-                        bulk_load_1d(dst + ST_A + ST_W, p.sfa + ((size_t)mt * KS4 + j * 4) * 512, ST_SF, bar(B_FULL + s));
-                        bulk_load_1d(dst + ST_A + ST_W + ST_SF, p.sfb + ((size_t)nt * KS4 + j * 4) * 512, ST_SF, bar(B_FULL + s));
+                        bulk_load_1d(dst + ST_A + ST_W, p.sfa + ((size_t)mt * KS4 + j * 4) * 512, C::ST_SFA, bar(B_FULL + s));
+#pragma unroll
+                        for (int hh = 0; hh < NH; ++hh)
+                            bulk_load_1d(dst + ST_A + ST_W + C::ST_SFA + hh * 2048,
+                                         p.sfb + ((size_t)(nt * NH + hh) * KS4 + j * 4) * 512, 2048, bar(B_FULL + s));
                     } else {
+                        const int h = (j - KS) / LCH, c = (j - KS) % LCH;
                         mbar_expect_tx(bar(B_FULL + s), 2 * 128 * 64);
-                        tma_load_2d(dst, &tm_la, bar(B_FULL + s), (j - KS) * 32, mt * BM);
-                        tma_load_2d(dst + ST_A, &tm_lu, bar(B_FULL + s), (j - KS) * 32, nt * BN);
+                        tma_load_2d(dst, &tm_la, bar(B_FULL + s), c * 32, mt * BM);
+                        tma_load_2d(dst + ST_A, &tm_lu, bar(B_FULL + s), c * 32, nt * BN + h * 128);
                     }
                 }
             }
@@ -186,89 +218,117 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         if (lane == 0) {
             const uint32_t idesc = idesc_mxf4nvf4(BN);
             const uint32_t f16fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-            const uint32_t idesc_lr = umma_idesc(1u, f16fmt, f16fmt, BN);
-            uint32_t it = 0, tl = 0;
+            const uint32_t idesc_lr = umma_idesc(1u, f16fmt, f16fmt, 128);
+            uint32_t it = 0, tl = 0, lrn = 0;  // ring stages, tiles, uses of the low-rank slot
             bool ok = true;
             for (int t = t_begin; t < t_end && ok; ++t, ++tl) {
-                const int slot = tl & 1;
-                if (!mbar_wait(bar(B_ACC_EMPTY + slot), ((tl >> 1) & 1) ^ 1, abort_s, E_MMA | 2, 100)) { ok = false; break; }
+                const int slot = tl % ACC_SLOTS;
                 const uint32_t d = tmem_base + TM_ACC + slot * BN;
+                // low-rank product of one 128-column half into the single low-rank slot
+                auto low_rank_half = [&]() {
+                    if (!mbar_wait(bar(B_LR_EMPTY), (lrn & 1) ^ 1, abort_s, E_MMA | 3, 100)) return false;  // previous contents read
+                    for (int c = 0; c < LCH; ++c, ++it) {
+                        const int s = it % STAGES;
+                        if (!mbar_wait(bar(B_FULL + s), (it / STAGES) & 1, abort_s, E_MMA | 4, 100)) return false;
+                        tc_fence_after();
+                        const uint32_t a_addr = s_base + s * ST_BYTES, w_addr = a_addr + ST_A;
+#pragma unroll
+                        for (int kk = 0; kk < 2; ++kk)
+                            mma_f16(tmem_base + TM_LORA, desc_sw64(a_addr + kk * 32), desc_sw64(w_addr + kk * 32), idesc_lr,
+                                    (c | kk) ? 1u : 0u);
+                        tc_commit(bar(B_EMPTY + s));
+                    }
+                    tc_commit(bar(B_LR_FULL));
+                    ++lrn;
+                    return true;
+                };
+                // wide tile: the first half's product goes first; its slot and the accumulator were released together
+                if (LCH > 0 && NH == 2 && !low_rank_half()) { ok = false; break; }
+                if (!mbar_wait(bar(B_ACC_EMPTY + slot), ((tl / ACC_SLOTS) & 1) ^ 1, abort_s, E_MMA | 2, 100)) { ok = false; break; }
                 for (int j = 0; j < KS && ok; ++j, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(bar(B_FULL + s), (it / STAGES) & 1, abort_s, E_MMA | 1, 100)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = s_base + s * ST_BYTES;
                     const uint64_t da = desc_sw128(a_addr), dw = desc_sw128(a_addr + ST_A);
-                    const uint32_t sfa_s = a_addr + ST_A + ST_W, sfb_s = sfa_s + ST_SF;
+                    const uint32_t sfa_s = a_addr + ST_A + ST_W, sfb_s = sfa_s + C::ST_SFA;
 #pragma unroll
                     for (int st = 0; st < 4; ++st) {
-                        // this step's scale chunks -> tensor memory, then the MMA that reads them (issue order is kept)
-                        const uint32_t tsf = tmem_base + TM_SF + s * 32 + st * 8;
+                        // this step's scale chunks -> tensor memory, then the MMA that reads them (issue order is kept):
+                        // four columns for the 128 rows of A, four per 128 rows of W
+                        const uint32_t tsf = tmem_base + TM_SF + (it % C::SF_BUFS) * (4 * C::SF_STEP) + st * C::SF_STEP;
                         tmem_cp_32x128b_warpx4(tsf, umma_desc_kmajor(sfa_s + st * 512, 16, 128));
-                        tmem_cp_32x128b_warpx4(tsf + 4, umma_desc_kmajor(sfb_s + st * 512, 16, 128));
+#pragma unroll
+                        for (int hh = 0; hh < NH; ++hh)
+                            tmem_cp_32x128b_warpx4(tsf + 4 + 4 * hh, umma_desc_kmajor(sfb_s + (hh * 4 + st) * 512, 16, 128));
                         mma_mxf4nvf4(d, da + 2 * st, dw + 2 * st, idesc, tsf, tsf + 4, (j | st) ? 1u : 0u);
                     }
                     tc_commit(bar(B_EMPTY + s));
                 }
-                if (ok && LCH > 0) {
-                    // the low-rank slot is single: the previous tile's epilogue must have read it
-                    if (!mbar_wait(bar(B_LR_EMPTY), (tl & 1) ^ 1, abort_s, E_MMA | 3, 100)) { ok = false; break; }
-                    for (int c = 0; c < LCH && ok; ++c, ++it) {
-                        const int s = it % STAGES;
-                        if (!mbar_wait(bar(B_FULL + s), (it / STAGES) & 1, abort_s, E_MMA | 4, 100)) { ok = false; break; }
-                        tc_fence_after();
-                        const uint32_t a_addr = s_base + s * ST_BYTES, w_addr = a_addr + ST_A;
-#pragma unroll
-                        for (int h = 0; h < 2; ++h)
-                            mma_f16(tmem_base + TM_LORA, desc_sw64(a_addr + h * 32), desc_sw64(w_addr + h * 32), idesc_lr,
-                                    (c | h) ? 1u : 0u);
-                        tc_commit(bar(B_EMPTY + s));
-                    }
-                }
                 if (ok) tc_commit(bar(B_ACC_FULL + slot));
+                if (ok && LCH > 0 && !low_rank_half()) { ok = false; break; }
             }
         }
     } else {
         // ================================ epilogue ================================
         // a warp reads its lane quarter: lane = row, 32 columns per load
         const int q = warp & 3;
-        uint32_t tl = 0;
+        uint32_t tl = 0, lrn = 0;
         bool ok = true;
         const float alpha = p.alpha;
         for (int t = t_begin; t < t_end && ok; ++t, ++tl) {
             const int m0 = (t / NT) * BM, n0 = (t % NT) * BN;
-            const int slot = tl & 1;
-            if (!mbar_wait_warp(bar(B_ACC_FULL + slot), (tl >> 1) & 1, abort_s, E_EPI | 1, 100)) { ok = false; break; }
+            const int slot = tl % ACC_SLOTS;
+            // the tile's per-column scale and bias, widened once per warp while the K loop runs
+            float* epi_s = reinterpret_cast<float*>(smem + C::OFF_EPI) + (warp - 2) * 2 * BN;
+            __syncwarp();
+            for (int i = lane; i < BN; i += 32) {
+                const int n = n0 + i;
+                epi_s[i] = (p.wcscales && n < p.N) ? to_f32<T>(__ldg(static_cast<const T*>(p.wcscales) + n)) : 1.0f;
+                epi_s[BN + i] = (p.bias && n < p.N) ? to_f32<T>(__ldg(static_cast<const T*>(p.bias) + n)) : 0.0f;
+            }
+            __syncwarp();
+            if (!mbar_wait_warp(bar(B_ACC_FULL + slot), (tl / ACC_SLOTS) & 1, abort_s, E_EPI | 1, 100)) { ok = false; break; }
             tc_fence_after();
             const int m = m0 + q * 32 + lane;
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
             for (int ch = 0; ch < BN / 32; ++ch) {
+                if (LCH > 0 && (ch & 3) == 0) {
+                    // the low-rank product of this 128-column half
+                    if (!mbar_wait_warp(bar(B_LR_FULL), lrn & 1, abort_s, E_EPI | 2, 100)) { ok = false; break; }
+                    ++lrn;
+                    tc_fence_after();
+                }
                 uint32_t v[32], lr[32];
                 tmem_ld32(lane_addr + TM_ACC + slot * BN + ch * 32, v);
-                if (LCH > 0) tmem_ld32(lane_addr + TM_LORA + ch * 32, lr);
+                if (LCH > 0) tmem_ld32(lane_addr + TM_LORA + (ch & 3) * 32, lr);
                 tmem_wait_ld();
-                if (ch == BN / 32 - 1) {
-                    // both slots are read out
+                if ((ch & 3) == 3) {
+                    // this half of the low-rank slot, and after the last half the accumulator slot, are read out
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) {
-                        mbar_arrive(bar(B_ACC_EMPTY + slot));
                         if (LCH > 0) mbar_arrive(bar(B_LR_EMPTY));
+                        if (ch == BN / 32 - 1) mbar_arrive(bar(B_ACC_EMPTY + slot));
                     }
                 }
 #pragma unroll
                 for (int c8 = 0; c8 < 4; ++c8) {
                     const int n = n0 + ch * 32 + c8 * 8;
                     if (n < p.N) {  // N is a multiple of 8
-                        float o[8];
+                        float o[8], cs[8], bs[8];
+                        *reinterpret_cast<float4*>(&cs[0]) = *reinterpret_cast<const float4*>(epi_s + ch * 32 + c8 * 8);
+                        *reinterpret_cast<float4*>(&cs[4]) = *reinterpret_cast<const float4*>(epi_s + ch * 32 + c8 * 8 + 4);
+                        *reinterpret_cast<float4*>(&bs[0]) = *reinterpret_cast<const float4*>(epi_s + BN + ch * 32 + c8 * 8);
+                        *reinterpret_cast<float4*>(&bs[4]) = *reinterpret_cast<const float4*>(epi_s + BN + ch * 32 + c8 * 8 + 4);
 #pragma unroll
                         for (int e = 0; e < 8; ++e) {
                             float x = __uint_as_float(v[c8 * 8 + e]);
-                            if (p.wcscales) x *= to_f32<T>(__ldg(static_cast<const T*>(p.wcscales) + n + e));
+                            if (p.wcscales) x *= cs[e];
                             x *= alpha;
                             if (LCH > 0) x += __uint_as_float(lr[c8 * 8 + e]);
-                            if (p.bias) x += to_f32<T>(__ldg(static_cast<const T*>(p.bias) + n + e));
+                            if (p.bias) x += bs[e];
                             o[e] = x;
                         }
                         if (m < p.actual_m) {
@@ -307,7 +367,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) prepack_fp4_kernel(const PrepackParams p) {
     const long long tid = (long long)blockIdx.x * 256 + threadIdx.x;
     const int KS4 = p.K / 64;
-    const int Mp = (p.M + 127) / 128 * 128, Np = (p.N + 127) / 128 * 128;
+    const int Mp = (p.M + 127) / 128 * 128, Np = (p.N + 255) / 256 * 256;  // whole 128-row chunks; W: whole wide tiles
     const long long a_units = (long long)KS4 * Mp, w_units = (long long)KS4 * Np;
     if (tid < a_units + w_units) {
         // one thread per (64-k step, row): four scales -> one 32-bit word of the chunk
@@ -376,10 +436,36 @@ static Scratch scratch_layout(const nb_gemm_args* a) {
     const size_t KS4 = a->K / 64;
     size_t off = 0;
     s.sfa = off; off += up256((size_t)((a->M + 127) / 128) * KS4 * 512);
-    s.sfb = off; off += up256((size_t)((a->N + 127) / 128) * KS4 * 512);
+    s.sfb = off; off += up256((size_t)((a->N + 255) / 256 * 2) * KS4 * 512);
     s.la16 = off; off += up256((size_t)a->M * a->R * 2);
     s.total = off;
     return s;
+}
+
+template <typename T, int BN_>
+static int launch_kernel(const nb_gemm_args* a, const Params& p, const void* la16, cudaStream_t s) {
+    using C = Cfg<BN_>;
+    CUtensorMap tm_a, tm_w, tm_la, tm_lu;
+    const CUtensorMapDataType t16 = std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                          : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    bool ok = make_map(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->act, a->K / 2, a->M, a->stride_am, 128, BM, CU_TENSOR_MAP_SWIZZLE_128B) &&
+              make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->wgt, a->K / 2, a->N, a->stride_wn, 128, C::BN, CU_TENSOR_MAP_SWIZZLE_128B);
+    // the low-rank operands travel in 128-row boxes for both tile widths (one 128-column half at a time)
+    if (ok && a->R > 0)
+        ok = make_map(&tm_la, t16, la16, a->R, a->M, (uint64_t)a->R * 2, 32, BM, CU_TENSOR_MAP_SWIZZLE_64B) &&
+             make_map(&tm_lu, t16, a->lora_up, a->R, a->N, (uint64_t)a->stride_lun * 2, 32, 128, CU_TENSOR_MAP_SWIZZLE_64B);
+    else if (ok) { tm_la = tm_a; tm_lu = tm_w; }
+    if (!ok) return NB_ERR_UNSUPPORTED;
+    int dev = 0, sms = 0;
+    NB_CUDA_CHECK(cudaGetDevice(&dev));
+    NB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int total = ((a->M + BM - 1) / BM) * ((a->N + C::BN - 1) / C::BN);
+    const int grid = total < sms ? total : sms;
+    auto kern = gemm_fp4_kernel<T, BN_>;
+    NB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    kern<<<grid, NTHREADS, C::SMEM_BYTES, s>>>(tm_a, tm_w, tm_la, tm_lu, p);
+    NB_CUDA_CHECK(cudaGetLastError());
+    return NB_OK;
 }
 
 template <typename T>
@@ -395,21 +481,10 @@ static int launch_t(const nb_gemm_args* a, cudaStream_t s) {
     pp.M = a->M; pp.N = a->N; pp.K = a->K; pp.R = a->R;
     pp.stride_asg = a->stride_asg; pp.stride_wsg = a->stride_wsg; pp.stride_lam = a->stride_lam;
     const long long KS4 = a->K / 64;
-    const long long units = KS4 * ((a->M + 127) / 128 * 128) + KS4 * ((a->N + 127) / 128 * 128) +
+    const long long units = KS4 * ((a->M + 127) / 128 * 128) + KS4 * ((a->N + 255) / 256 * 256) +
                             (a->R ? (long long)a->M * (a->R / 8) : 0);
     prepack_fp4_kernel<T><<<(unsigned)((units + 255) / 256), 256, 0, s>>>(pp);
     NB_CUDA_CHECK(cudaGetLastError());
-
-    CUtensorMap tm_a, tm_w, tm_la, tm_lu;
-    const CUtensorMapDataType t16 = std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                                          : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    bool ok = make_map(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->act, a->K / 2, a->M, a->stride_am, 128, BM, CU_TENSOR_MAP_SWIZZLE_128B) &&
-              make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->wgt, a->K / 2, a->N, a->stride_wn, 128, BN, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (ok && a->R > 0)
-        ok = make_map(&tm_la, t16, pp.la16, a->R, a->M, (uint64_t)a->R * 2, 32, BM, CU_TENSOR_MAP_SWIZZLE_64B) &&
-             make_map(&tm_lu, t16, a->lora_up, a->R, a->N, (uint64_t)a->stride_lun * 2, 32, BN, CU_TENSOR_MAP_SWIZZLE_64B);
-    else if (ok) { tm_la = tm_a; tm_lu = tm_w; }
-    if (!ok) return NB_ERR_UNSUPPORTED;
 
     Params p = {};
     p.out = a->out; p.bias = a->bias; p.wcscales = a->wcscales;
@@ -417,16 +492,9 @@ static int launch_t(const nb_gemm_args* a, cudaStream_t s) {
     p.M = a->M; p.N = a->N; p.K = a->K; p.actual_m = a->actual_m; p.R = a->R;
     p.alpha = a->alpha; p.stride_om = a->stride_om;
     p.status = static_cast<int*>(a->status);
-    int dev = 0, sms = 0;
-    NB_CUDA_CHECK(cudaGetDevice(&dev));
-    NB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    const int total = ((a->M + BM - 1) / BM) * ((a->N + BN - 1) / BN);
-    const int grid = total < sms ? total : sms;
-    auto kern = gemm_fp4_kernel<T>;
-    NB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    kern<<<grid, NTHREADS, SMEM_BYTES, s>>>(tm_a, tm_w, tm_la, tm_lu, p);
-    NB_CUDA_CHECK(cudaGetLastError());
-    return NB_OK;
+    // the wide tile when it does not waste columns, or when the matrix is wide enough for the waste not to matter
+    const bool wide = a->N % 256 == 0 || a->N >= 2048;
+    return wide ? launch_kernel<T, 256>(a, p, pp.la16, s) : launch_kernel<T, 128>(a, p, pp.la16, s);
 }
 
 }  // namespace fp4

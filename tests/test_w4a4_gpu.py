@@ -391,7 +391,11 @@ def test_gemm_fp4_wcscales_alpha(cuda_dev, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("impl", [GENERIC, 0])  # 0 = automatic: the block-scaled tensor-core kernel when the shape allows
-@pytest.mark.parametrize("M,N,K,R", [(128, 128, 256, 0), (200, 264, 512, 32), (384, 640, 1024, 16), (130, 136, 768, 48)])
+@pytest.mark.parametrize("M,N,K,R", [
+    (128, 128, 256, 0), (200, 264, 512, 32), (384, 640, 1024, 16), (130, 136, 768, 48),
+    # N % 256 == 0 or N >= 2048: the 128 x 256 tile (low-rank slot served per 128-column half, ragged last tile)
+    (128, 256, 256, 0), (300, 512, 512, 32), (257, 768, 1024, 80), (130, 2056, 512, 16),
+])
 def test_gemm_fp4_shapes_lora_bias(cuda_dev, dtype, impl, M, N, K, R):
     Kn = _ops()
     g = torch.Generator().manual_seed(M + N + K + R)
