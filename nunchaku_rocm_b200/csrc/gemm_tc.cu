@@ -386,15 +386,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         }
                         NB_PF(0);
                     }
+                    if (EPI == NB_EPI_QK_NORM_ROPE) {
 #pragma unroll
-                    for (int jx = 0; jx < NJ; ++jx) {
-                        const uint64_t wj = (jx & 1) ? w[jx >> 1].y : w[jx >> 1].x;
+                        for (int jx = 0; jx < NJ; ++jx) {
+                            const uint64_t wj = (jx & 1) ? w[jx >> 1].y : w[jx >> 1].x;
 #pragma unroll
-                        for (int rs = 0; rs < 2; ++rs) {
-                            const int vi = 4 * jx + 2 * rs;
-                            const uint64_t tt = mul_f32x2(pack_u32x2(vv[vi], vv[vi + 1]), as2[lb * 2 + rs]);
-                            uint64_t& a = acc[(lb * NJ + jx) * 2 + rs];
-                            a = fma_f32x2(tt, wj, a);
+                            for (int rs = 0; rs < 2; ++rs) {
+                                const int vi = 4 * jx + 2 * rs;
+                                const uint64_t tt = mul_f32x2(pack_u32x2(vv[vi], vv[vi + 1]), as2[lb * 2 + rs]);
+                                uint64_t& a = acc[(lb * NJ + jx) * 2 + rs];
+                                a = fma_f32x2(tt, wj, a);
+                            }
+                        }
+                    } else {
+                        // All products p * as of the half group first, then the FMAs: measured 4 % faster than the interleaved
+                        // order above for the plain epilogue and 5 % slower for the Q/K one (whose instantiation has fewer
+                        // registers to spare), hence the two forms.
+                        uint64_t tt[NJ][2];
+#pragma unroll
+                        for (int jx = 0; jx < NJ; ++jx)
+#pragma unroll
+                            for (int rs = 0; rs < 2; ++rs) {
+                                const int vi = 4 * jx + 2 * rs;
+                                tt[jx][rs] = mul_f32x2(pack_u32x2(vv[vi], vv[vi + 1]), as2[lb * 2 + rs]);
+                            }
+                        asm volatile("" ::: "memory");
+#pragma unroll
+                        for (int jx = 0; jx < NJ; ++jx) {
+                            const uint64_t wj = (jx & 1) ? w[jx >> 1].y : w[jx >> 1].x;
+#pragma unroll
+                            for (int rs = 0; rs < 2; ++rs) {
+                                uint64_t& a = acc[(lb * NJ + jx) * 2 + rs];
+                                a = fma_f32x2(tt[jx][rs], wj, a);
+                            }
                         }
                     }
                     if (DEBUG_P) {
