@@ -226,9 +226,10 @@ int64_t nb_attention_scratch_bytes(const nb_attn_args* args);
 /*
  * Self-test on the current device, the role of the reference's native self-test (nunchaku/ops/triton/native/w4a4.py:537-651):
  * a small seeded W4A4 problem with bias and a rank-16 branch runs on the tensor-core kernel and on the generic kernel;
- * the exact integer group sums must be equal and the 16-bit outputs must agree to two rounding steps.  Allocates and
- * frees its own few hundred KB of device memory and synchronises the device.  Returns NB_OK, or NB_ERR_DEVICE on a
- * mismatch.
+ * the exact integer group sums must be equal and the 16-bit outputs must agree to two rounding steps; the same call with
+ * load-time prepared weights must reproduce the tensor-core output bit for bit; an NVFP4 problem (wide tile, per-channel
+ * scales, alpha, rank 16) must agree between the block-scaled and the generic kernel.  Allocates and frees its own few MB
+ * of device memory and synchronises the device.  Returns NB_OK, or NB_ERR_DEVICE on a mismatch.
  */
 int nb_selftest(void);
 
