@@ -113,8 +113,9 @@ typedef struct nb_requant_args {
 int nb_gemm_w4a4(const nb_gemm_args* args, const void* epi, int epi_kind, void* stream);
 
 /*
- * Bytes of device scratch nb_gemm_w4a4 needs for this call: the tensor-core kernel keeps the operands widened
- * to int8 and the scales converted to fp32 there, the generic kernel the fp32 tile of a fused row epilogue.
+ * Bytes of device scratch nb_gemm_w4a4 needs for this call: the tensor-core kernel keeps its operand form there (one
+ * e4m3 byte per int4 value, the scale rows in the order its drain reads them, lora_act rounded to T), the generic
+ * kernel the fp32 tile of a fused row epilogue.
  * The buffer must be 256-byte aligned; its contents are dead when the call's kernels have run.
  */
 int64_t nb_gemm_w4a4_scratch_bytes(const nb_gemm_args* args, const void* epi, int epi_kind);
@@ -123,7 +124,7 @@ int64_t nb_gemm_w4a4_scratch_bytes(const nb_gemm_args* args, const void* epi, in
  * Load-time half of the int4 tensor-core path.  The weights of a layer do not change between calls, so the form the
  * kernel's TMA loads read (one e4m3 byte per int4 value, column scales in the drain's order) can be written once instead
  * of by every call's pre-pass: the role of the reference's load-time weight packing (`NunchakuWeightPacker`,
- * nunchaku/utils.py) for its MMA layout.  `args` needs wgt, wscales, N, K, dtype and the two strides.
+ * nunchaku/lora/flux/packer.py:165-517) for its MMA layout.  `args` needs wgt, wscales, N, K, dtype and the two strides.
  * nb_gemm_w4a4_prepared_bytes returns the size of the buffer (0: this weight cannot use the tensor-core kernel, e.g.
  * NVFP4 or K % 64 != 0); nb_gemm_w4a4_prepare_weights fills it (256-byte aligned) on `stream`.  A later nb_gemm_w4a4 call
  * with the same wgt / wscales / N / K / dtype may pass it as `wgt_prepared`; it then needs less scratch (ask
@@ -149,6 +150,8 @@ int64_t nb_gemm_w4a4_uses_tcgen05(const nb_gemm_args* args, const void* epi, int
  *     launches nothing (for the tensor-core kernel the need is about (M + N) * K bytes plus the converted scales).
  *   - First call on a device: the address of the array is looked up once (cudaGetSymbolAddress, which may load the
  *     module).  Make that first call during set-up, outside any stream capture; later calls only launch kernels.
+ *     The address is remembered per device for the primary context it was looked up in: a process that destroys
+ *     that context (cudaDeviceReset) must not call this entry point on the device again.
  *   - The array is shared by every caller on the device: two calls that can overlap in time (different streams or
  *     threads without ordering between them) race on it.  Order such calls on one stream or with events.
  *   - Nothing in the array has to start at zero and nothing is cleared: each call's first kernel writes every byte its
@@ -232,6 +235,15 @@ int64_t nb_attention_scratch_bytes(const nb_attn_args* args);
  * of device memory and synchronises the device.  Returns NB_OK, or NB_ERR_DEVICE on a mismatch.
  */
 int nb_selftest(void);
+
+/*
+ * Failure-path check: launches one warp that waits, with the kernels' own bounded wait, on a barrier nothing arrives
+ * on.  After `limit_us` microseconds (1 .. 1,000,000) the wait gives up and the kernel stores a non-zero code in the
+ * device int32 `status`, as the GEMM and attention kernels do when a wait of theirs expires; the context stays usable.
+ * The reference surfaces runtime failures of its native module as exceptions (nunchaku/ops/triton/native/hip.py:110-116);
+ * this is the hook that lets a host test that plumbing without faulting or hanging a GPU.
+ */
+int nb_debug_expire_wait(void* status, int64_t limit_us, void* stream);
 
 /* Diagnostics (the reference's `status()` / error plumbing, nunchaku/ops/triton/native/hip.py:110-116). */
 const char* nb_strerror(int status);

@@ -88,7 +88,7 @@ class AttnArgs(C.Structure):
     )
 
 
-_lock = threading.Lock()
+_lock = threading.RLock()
 _lib = None
 
 
@@ -125,6 +125,7 @@ def lib() -> C.CDLL:
                 l.nb_attention.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
                 l.nb_attention_scratch_bytes.argtypes = [C.POINTER(AttnArgs)]
                 l.nb_attention_scratch_bytes.restype = C.c_int64
+                l.nb_debug_expire_wait.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
                 l.nb_qk_norm_rope.argtypes = [
                     C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_int32, C.POINTER(QKArgs), C.c_void_p,
                 ]
@@ -156,8 +157,40 @@ def stream_of(t: torch.Tensor) -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 
+_selftested: set[int] = set()
+
+
+def ensure_selftest(dev: torch.device) -> None:
+    """
+    Run the library's self-test once per device before the first kernel call on it, as the reference does when its
+    native module is first loaded (nunchaku/ops/triton/native/w4a4.py:371-389, 533-704): small seeded problems on the
+    tensor-core kernels against the CUDA-core kernel.  A mismatch raises; nothing is silently switched off.
+    The test allocates and synchronises, so a first call that happens inside a stream capture postpones it to the next
+    call outside one.  ``NUNCHAKU_B200_SELFTEST=0`` skips it.
+    """
+    i = dev.index if dev.index is not None else torch.cuda.current_device()
+    if i in _selftested:
+        return
+    if os.environ.get("NUNCHAKU_B200_SELFTEST", "1") == "0":
+        _selftested.add(i)
+        return
+    if torch.cuda.is_current_stream_capturing():
+        return
+    with _lock:
+        if i in _selftested:
+            return
+        with torch.cuda.device(i):
+            rc = lib().nb_selftest()
+        if rc != NB_OK:
+            raise RuntimeError(
+                f"libnunchaku_b200 self-test failed on cuda:{i} ({lib().nb_strerror(rc).decode()}): the tensor-core "
+                "kernels disagree with the CUDA-core kernel on this device"
+            )
+        _selftested.add(i)
+
+
 def require_cuda(*tensors: torch.Tensor | None) -> torch.device:
-    """All given tensors must live on one CUDA device; there is no CPU path."""
+    """All given tensors must live on one CUDA device; there is no CPU path.  First use of a device runs the self-test."""
     dev = None
     for t in tensors:
         if t is None:
@@ -168,6 +201,8 @@ def require_cuda(*tensors: torch.Tensor | None) -> torch.device:
             dev = t.device
         elif t.device != dev:
             raise ValueError("tensors on different devices")
+    if dev is not None:
+        ensure_selftest(dev)
     return dev
 
 
@@ -189,3 +224,24 @@ def device_status(dev: torch.device | None = None) -> int:
     if dev is None:
         dev = torch.device("cuda", torch.cuda.current_device())
     return int(status_word(dev).item())
+
+
+class KernelWaitExpired(RuntimeError):
+    """A kernel gave up on a bounded wait: its results are void (nb_status NB_ERR_DEVICE)."""
+
+
+def check_device_status(dev: torch.device | None = None, reset: bool = True) -> None:
+    """
+    Synchronise and raise :class:`KernelWaitExpired` if any kernel since the last check set the device's status word
+    (the error convention of nunchaku/ops/triton/native/hip.py:110-116: a runtime failure becomes an exception and the
+    stored error is cleared).  ``reset`` zeroes the word so that later work starts clean.
+    """
+    if dev is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    code = device_status(dev)
+    if code:
+        if reset:
+            status_word(dev).zero_()
+        raise KernelWaitExpired(
+            f"{lib().nb_strerror(NB_ERR_DEVICE).decode()} on {dev}: status {code:#x} (role/barrier code of the kernel)"
+        )

@@ -34,3 +34,34 @@ extern "C" int nb_num_sms(void) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
     return n;
 }
+
+// ------------------------------------------------------------------------------------------------
+// nb_debug_expire_wait: the bounded-wait path of the kernels, exercised on purpose.  One warp waits on an mbarrier that
+// nothing will ever arrive on, with the limit the caller gives; the wait gives up after that time, the kernel stores the
+// code in *status exactly as the GEMM and attention kernels do, and returns.  Nothing spins beyond the limit and the
+// context stays usable.
+// ------------------------------------------------------------------------------------------------
+namespace nb {
+__global__ void expire_wait_kernel(int* status, unsigned long long limit_ns, int code) {
+    __shared__ uint64_t barrier;
+    __shared__ int abort_word;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&barrier), 1);
+        abort_word = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    bool ok = true;
+    if (threadIdx.x == 0) ok = mbar_wait(smem_u32(&barrier), 0, &abort_word, code, 200, limit_ns);
+    __syncthreads();
+    if (threadIdx.x == 0 && !ok && status) atomicCAS(status, 0, abort_word);
+}
+}  // namespace nb
+
+extern "C" int nb_debug_expire_wait(void* status, int64_t limit_us, void* stream) {
+    if (!status || limit_us < 1 || limit_us > 1000000) return NB_ERR_INVALID;  // at most one second
+    nb::expire_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<int*>(status),
+                                                                             (unsigned long long)limit_us * 1000ull, 0x7E1);
+    NB_CUDA_CHECK(cudaGetLastError());
+    return NB_OK;
+}

@@ -534,9 +534,10 @@ static int launch_t(const nb_attn_args* a, cudaStream_t s) {
             if (d[i].role == 0) box[i + 1] = BN;
         }
         kperm = make_int4(pos[0], pos[1], pos[2], 0);
-        // a dimension of size 1 may carry any stride; give it a valid one
+        // a dimension of size 1 may carry any stride; give it a valid one.  (A zero or unaligned stride on a larger
+        // dimension -- K expanded over heads or batch -- never gets here: attn_tc_unsupported_reason refuses it.)
         for (int i = 0; i < 3; ++i)
-            if (str[i] == 0 || str[i] % 16) str[i] = 16;
+            if (dims[i + 1] == 1 && (str[i] == 0 || str[i] % 16)) str[i] = 16;
         ok = ok && make_map(&tm_k, t16, 4, a->k, dims, str, box);
     }
     if (!ok) return NB_ERR_UNSUPPORTED;
@@ -561,6 +562,13 @@ const char* attn_tc_unsupported_reason(const nb_attn_args* a) {
     if (a->Tq < 1 || a->Tkv < 1) return "empty";
     if (!aligned16(a->o) || a->stride_om % 8 || a->stride_ob % 8) return "output alignment";
     if (a->B > 65535 || a->H > 65535) return "grid";
+    // K is read through a 4-D tensor map on the caller's view: every dimension larger than 1 needs a non-zero stride of
+    // whole 16-byte units (a K broadcast over heads or batch by `expand` has stride 0 there)
+    const long long ks[3] = {a->stride_kn, a->stride_kh, a->stride_kb};
+    const int kn[3] = {a->Tkv, a->H, a->B};
+    for (int i = 0; i < 3; ++i)
+        if (kn[i] > 1 && (ks[i] <= 0 || ks[i] % 8)) return "K stride (broadcast or unaligned view)";
+    if (!aligned16(a->k)) return "K alignment";
     return nullptr;
 }
 int64_t attn_tc_scratch_bytes(const nb_attn_args* a) { return (int64_t)atc::scratch_layout(a).total; }

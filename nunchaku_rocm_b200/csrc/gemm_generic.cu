@@ -1,7 +1,7 @@
 // Generic W4A4 GEMM on CUDA cores plus the row-wise epilogue kernels.
 //
-// This is the kernel for calls the tcgen05 kernel does not take (NVFP4 until its block-scaled
-// kernel lands, unaligned strides, ranks or widths off the tile grid); it plays the role of the
+// This is the kernel for calls the tcgen05 kernels do not take (NVFP4 calls outside the block-scaled
+// kernel's shapes, unaligned strides, ranks or widths off the tile grid); it plays the role of the
 // reference's generic `_gemm_w4a4_kernel` (nunchaku/ops/triton/gemm_w4a4.py:230-373) next to its int4
 // fast path.  Arithmetic: one exact int32 dot (dp4a) per 64-group, `acc += float(p) * as * ws`
 // (gemm_w4a4.py:477-483); NVFP4: exact fp32 dot per 16-group of decoded e2m1 values, scales decoded

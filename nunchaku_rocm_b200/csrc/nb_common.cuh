@@ -168,7 +168,7 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 // Every poll is one operation on the shared-memory barrier unit, which all warps of the CTA share, so a
 // waiter parks in the hardware (`hint_ns`) instead of polling in a tight loop.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
-                                          unsigned hint_ns = 200) {
+                                          unsigned hint_ns = 200, uint64_t limit_ns = 2000000000ull) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = 0;
     for (uint32_t spin = 1;; ++spin) {
@@ -177,7 +177,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag) return false;
             uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;
-            if (now - t0 > 2000000000ull) {
+            if (now - t0 > limit_ns) {
                 *abort_flag = code;
                 return false;
             }

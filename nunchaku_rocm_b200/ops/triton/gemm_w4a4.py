@@ -15,6 +15,7 @@ from __future__ import annotations
 import collections
 import ctypes as C
 import os
+import threading
 
 import torch
 
@@ -211,10 +212,21 @@ def _checks(act, wgt, out2d, ascales, wscales, bias, lora_act_in, lora_up, wcsca
 # A layer's weights do not change between calls, so the form the kernel's TMA loads read (one e4m3 byte per int4 value,
 # column scales in the drain's order) is written once per weight and kept: the counterpart of the reference's load-time
 # weight packing.  An entry keeps the weight and scale tensors alive (so their addresses cannot be handed to other
-# tensors while it exists) and is dropped when either has been modified in place (torch's version counter) or when the
-# prepared buffers exceed the budget (least recently used first).  NUNCHAKU_B200_PREPARED_WEIGHTS_MB=0 turns it off.
-_PREPARED: "collections.OrderedDict[tuple, tuple]" = collections.OrderedDict()
+# tensors while it exists; their bytes count against the budget together with the prepared buffer) and is dropped when
+# either has been modified in place (torch's version counter) or when the budget is exceeded (least recently used
+# first).  NUNCHAKU_B200_PREPARED_WEIGHTS_MB=0 turns it off.
+#
+# CUDA graphs: a call made while the current stream is capturing bakes the buffer's address into the graph.  Such an
+# entry is PINNED: it is never evicted, and if it has to be replaced (weights updated in place) the old buffer is parked
+# in `_PINNED_BUFFERS`, so a replay never reads freed memory -- it reads the weights as they were at capture time.
+# Re-capture after changing weights; `clear_prepared_weights(release_pinned=True)` frees everything once no graph that
+# used the buffers will be replayed again.
+_PREPARED: "collections.OrderedDict[tuple, list]" = collections.OrderedDict()
 _PREPARED_BYTES = 0
+_PINNED_BUFFERS: list = []
+_PREPARED_LOCK = threading.RLock()
+# entry fields
+_E_WGT, _E_WVER, _E_WSC, _E_SVER, _E_BUF, _E_EVENT, _E_STREAM, _E_PINNED, _E_BYTES = range(9)
 
 
 def _prepared_budget(device) -> int:
@@ -224,11 +236,29 @@ def _prepared_budget(device) -> int:
     return torch.cuda.get_device_properties(device).total_memory // 4
 
 
-def clear_prepared_weights() -> None:
-    """Drop every prepared weight buffer (and the references to the weights they were made from)."""
+def clear_prepared_weights(release_pinned: bool = False) -> None:
+    """
+    Drop the prepared weight buffers (and the references to the weights they were made from).  Buffers that a CUDA
+    graph capture has used stay alive unless ``release_pinned`` is set: only pass it when no such graph will run again.
+    """
     global _PREPARED_BYTES
-    _PREPARED.clear()
-    _PREPARED_BYTES = 0
+    with _PREPARED_LOCK:
+        for key in list(_PREPARED):
+            e = _PREPARED[key]
+            if e[_E_PINNED] and not release_pinned:
+                _PINNED_BUFFERS.append(e[_E_BUF])
+            del _PREPARED[key]
+        _PREPARED_BYTES = 0
+        if release_pinned:
+            _PINNED_BUFFERS.clear()
+
+
+def _drop_entry(key) -> None:
+    global _PREPARED_BYTES
+    e = _PREPARED.pop(key)
+    _PREPARED_BYTES -= e[_E_BYTES]
+    if e[_E_PINNED]:
+        _PINNED_BUFFERS.append(e[_E_BUF])  # a captured graph may still read it
 
 
 def _attach_prepared(a, wgt, wscales) -> None:
@@ -236,42 +266,56 @@ def _attach_prepared(a, wgt, wscales) -> None:
     budget = _prepared_budget(wgt.device)
     if budget <= 0:
         return
+    try:
+        wver, sver = wgt._version, wscales._version
+    except RuntimeError:
+        return  # inference-mode tensors carry no version counter: an in-place update could not be seen, so no cache
+    capturing = torch.cuda.is_current_stream_capturing()
     key = (wgt.device.index, wgt.data_ptr(), wscales.data_ptr(), a.N, a.K, a.stride_wn, a.stride_wsg, a.dtype)
     stream = torch.cuda.current_stream(wgt.device)
-    e = _PREPARED.get(key)
-    if e is not None and (e[1] != wgt._version or e[3] != wscales._version):
-        _PREPARED_BYTES -= e[4].numel()
-        del _PREPARED[key]
-        e = None
-    if e is None:
-        if torch.cuda.is_current_stream_capturing():
-            return  # no allocation that outlives a graph capture: this call runs the whole pre-pass
-        lib = L.lib()
-        nbytes = lib.nb_gemm_w4a4_prepared_bytes(C.byref(a))
-        if nbytes <= 0 or nbytes > budget:
-            return
-        while _PREPARED and _PREPARED_BYTES + nbytes > budget:
-            _, old = _PREPARED.popitem(last=False)
-            _PREPARED_BYTES -= old[4].numel()
-        buf = torch.empty(nbytes, dtype=torch.uint8, device=wgt.device)
-        with torch.cuda.device(wgt.device):
-            L.check(lib.nb_gemm_w4a4_prepare_weights(C.byref(a), L.ptr(buf), nbytes, L.stream_of(wgt)), "prepare_weights")
-        done = torch.cuda.Event()
-        done.record(stream)
-        e = (wgt, wgt._version, wscales, wscales._version, buf, done, stream)
-        _PREPARED[key] = e
-        _PREPARED_BYTES += nbytes
-    else:
-        _PREPARED.move_to_end(key)
-        # Another stream must not read the buffer before the kernel that wrote it has run.  (Inside a graph capture no
-        # dependency on outside work can be recorded; a capture starts after the capturing stream has joined the
-        # streams whose results it uses, which covers a buffer prepared before.)
-        if e[6] != stream and not torch.cuda.is_current_stream_capturing() and not e[5].query():
-            stream.wait_event(e[5])
-    a.wgt_prepared, a.wgt_prepared_bytes = L.ptr(e[4]), e[4].numel()
+    with _PREPARED_LOCK:
+        e = _PREPARED.get(key)
+        if e is not None and (e[_E_WVER] != wver or e[_E_SVER] != sver):
+            _drop_entry(key)
+            e = None
+        if e is None:
+            if capturing:
+                return  # no allocation that outlives a graph capture: this call runs the whole pre-pass
+            lib = L.lib()
+            nbytes = lib.nb_gemm_w4a4_prepared_bytes(C.byref(a))
+            held = nbytes + wgt.numel() * wgt.element_size() + wscales.numel() * wscales.element_size()
+            if nbytes <= 0 or held > budget:
+                return
+            for old_key in list(_PREPARED):
+                if _PREPARED_BYTES + held <= budget:
+                    break
+                if not _PREPARED[old_key][_E_PINNED]:
+                    _drop_entry(old_key)
+            if _PREPARED_BYTES + held > budget:
+                return  # what is left is pinned by graph captures
+            buf = torch.empty(nbytes, dtype=torch.uint8, device=wgt.device)
+            with torch.cuda.device(wgt.device):
+                L.check(lib.nb_gemm_w4a4_prepare_weights(C.byref(a), L.ptr(buf), nbytes, L.stream_of(wgt)), "prepare_weights")
+            done = torch.cuda.Event()
+            done.record(stream)
+            e = [wgt, wver, wscales, sver, buf, done, stream, False, held]
+            _PREPARED[key] = e
+            _PREPARED_BYTES += held
+        else:
+            _PREPARED.move_to_end(key)
+            if capturing:
+                e[_E_PINNED] = True
+            # Another stream must not read the buffer before the kernel that wrote it has run.  (Inside a graph capture no
+            # dependency on outside work can be recorded; a capture starts after the capturing stream has joined the
+            # streams whose results it uses, which covers a buffer prepared before.)
+            elif e[_E_STREAM] != stream and not e[_E_EVENT].query():
+                stream.wait_event(e[_E_EVENT])
+        a.wgt_prepared, a.wgt_prepared_bytes = L.ptr(e[_E_BUF]), e[_E_BUF].numel()
 
 
-def _run(a, epi, epi_kind, act, wgt=None, wscales=None):
+def _run(a, epi, epi_kind, act, wgt=None, wscales=None, keep=None):
+    """Launch one GEMM call.  ``keep``: tensors whose pointers sit in ``a`` / ``epi`` and that nothing else references
+    (contiguous copies); holding them here keeps their memory from being handed to the scratch allocation below."""
     lib = L.lib()
     if wgt is not None and not a.fp4 and lib.nb_gemm_w4a4_uses_tcgen05(C.byref(a), epi, epi_kind) == 1:
         _attach_prepared(a, wgt, wscales)
@@ -345,8 +389,8 @@ def gemm_w4a4(
         _checks(act, wgt, None, ascales, wscales, bias, la, lu, None, False, dtype)
         qout2d = qout.reshape(-1, qout.shape[-1])
         a = _gemm_args(act, wgt, None, ascales, wscales, bias, la, lu, None, act_unsigned, False, False, 1.0, dtype, _impl)
-        q = _requant_args(qout2d, oscales, smooth_factor, lora_down, lora_act_out, 0.0, N // 2, M, dtype)
-        _run(a, C.byref(q), L.EPI_SWIGLU_QUANT, act, wgt, wscales)
+        q, keep = _requant_args(qout2d, oscales, smooth_factor, lora_down, lora_act_out, 0.0, N // 2, M, dtype)
+        _run(a, C.byref(q), L.EPI_SWIGLU_QUANT, act, wgt, wscales, keep)
         return None
 
     want_quant = qout is not None or oscales is not None
@@ -381,10 +425,10 @@ def gemm_w4a4(
     if fuse_quant:
         a = _gemm_args(act, wgt, out2d, ascales, wscales, bias, la, lu, None, act_unsigned, False, False, 1.0, dtype, _impl)
         qout2d = qout.reshape(-1, qout.shape[-1])
-        q = _requant_args(qout2d, oscales, smooth_factor, lora_down, lora_act_out, GELU_SHIFT, N, M, dtype)
+        q, keep = _requant_args(qout2d, oscales, smooth_factor, lora_down, lora_act_out, GELU_SHIFT, N, M, dtype)
         fused_fast = L.lib().nb_gemm_w4a4_uses_tcgen05(C.byref(a), C.byref(q), L.EPI_GELU_QUANT) == 1
         if fused_fast or _impl == L.IMPL_GENERIC:
-            _run(a, C.byref(q), L.EPI_GELU_QUANT, act, wgt, wscales)
+            _run(a, C.byref(q), L.EPI_GELU_QUANT, act, wgt, wscales, keep)
             return out
         # no fused tensor-core kernel for this call: GEMM to a 16-bit tile, then the quantizer with the
         # GELU fused in, as the reference does for calls its fused kernel does not take (gemm_w4a4.py:1298-1312)
@@ -404,7 +448,7 @@ def gemm_w4a4(
         if nq.dtype != dtype or nk.dtype != dtype or nq.numel() != HEAD_DIM or nk.numel() != HEAD_DIM:
             raise ValueError(f"norm_q/norm_k must be ({HEAD_DIM},) tensors of the output dtype")
         q = L.QKArgs(L.ptr(nq), L.ptr(nk), L.ptr(rot), rot.stride(0), S, 1e-6)
-        _run(a, C.byref(q), L.EPI_QK, act, wgt, wscales)
+        _run(a, C.byref(q), L.EPI_QK, act, wgt, wscales, (nq, nk))
     else:
         _run(a, None, L.EPI_STORE, act, wgt, wscales)
         if want_qk:
@@ -428,7 +472,8 @@ def _requant_args(qout2d, oscales, smooth, lora_down, lora_act_out, shift, Nq, M
         raise ValueError("smooth_factor must be a (N,) tensor of the output dtype")
     q = L.RequantArgs()
     q.qout, q.oscales = L.ptr(qout2d), L.ptr(oscales)
-    q.smooth = L.ptr(smooth.contiguous()) if smooth is not None else None
+    smooth = smooth.contiguous() if smooth is not None else None  # returned: the caller keeps a copy alive over the launch
+    q.smooth = L.ptr(smooth)
     if lora_down is not None:
         R2 = lora_down.shape[1]
         if lora_down.dtype != dtype or lora_down.shape[0] != Nq or lora_down.stride(-1) != 1:
@@ -439,7 +484,7 @@ def _requant_args(qout2d, oscales, smooth, lora_down, lora_act_out, shift, Nq, M
         q.stride_ld, q.stride_lom = lora_down.stride(0), lora_act_out.stride(0)
     q.shift = shift
     q.stride_qm, q.stride_osg = qout2d.stride(0), oscales.stride(0)
-    return q
+    return q, (smooth,)
 
 
 def gemm_w4a4_group_sums(act, wgt, act_unsigned: bool = False, _impl: int = L.IMPL_AUTO) -> torch.Tensor:

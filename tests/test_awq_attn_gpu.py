@@ -115,6 +115,27 @@ def test_attention(cuda_dev, dtype, impl, B, H, TQ, TKV, D):
     torch.testing.assert_close(o.float().cpu(), awq_attn.attention(q, k, v, D**-0.5), rtol=2 * eps, atol=2 * eps)
 
 
+def test_attention_with_keys_broadcast_over_heads(cuda_dev):
+    # one K / V head expanded over all query heads (stride 0 on the head axis): the strides are the contract
+    # (nunchaku/ops/triton/attention.py:120-169 passes them to the kernel as they are)
+    from nunchaku_rocm_b200 import _lib
+    from nunchaku_rocm_b200.ops.triton.attention import attention_fp16
+
+    B, H, TQ, TKV, D = 2, 4, 160, 200, 128
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(B, H, TQ, D, generator=g).to(torch.bfloat16)
+    k1 = torch.randn(B, 1, TKV, D, generator=g).to(torch.bfloat16)
+    v1 = torch.randn(B, 1, TKV, D, generator=g).to(torch.bfloat16)
+    kd, vd = k1.to(cuda_dev).expand(B, H, TKV, D), v1.to(cuda_dev).expand(B, H, TKV, D)
+    assert kd.stride(1) == 0
+    o = torch.empty(B, TQ, H * D, dtype=torch.bfloat16, device=cuda_dev)
+    attention_fp16(q.to(cuda_dev), kd, vd, o, D**-0.5)
+    torch.cuda.synchronize(cuda_dev)
+    assert _lib.device_status(cuda_dev) == 0
+    want = awq_attn.attention(q, k1.expand(B, H, TKV, D), v1.expand(B, H, TKV, D), D**-0.5)
+    torch.testing.assert_close(o.float().cpu(), want, rtol=2.0**-6, atol=2.0**-6)
+
+
 def test_sdpa_wrapper_strided_views_and_fallback(cuda_dev):
     # (B, S, 3 * H * D) fused projection viewed as q, k, v, the way the FLUX processor slices it
     from nunchaku_rocm_b200.ops.dispatch import scaled_dot_product_attention

@@ -34,6 +34,47 @@ def test_struct_sizes_match_the_header():
     assert ctypes_size(_lib.QuantArgs) == 6 * 8 + 8 * 4 + 4 + 4 + 5 * 8
 
 
+def _header_struct_fields(name: str) -> list[str]:
+    """Field names of `typedef struct <name> {...}` in the header, in declaration order."""
+    header = open(os.path.join(ROOT, "include", "nunchaku_b200.h")).read()
+    body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (name, name), header, re.S).group(1)
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    names = []
+    for decl in body.split(";"):
+        decl = decl.strip()
+        if not decl:
+            continue
+        # "const void* a"  /  "int32_t M, N, K"  /  "int64_t stride_am, stride_wn"
+        first, *rest = decl.split(",")
+        names.append(re.search(r"([A-Za-z_][A-Za-z0-9_]*)\s*$", first).group(1))
+        names += [r.strip().lstrip("*").strip() for r in rest]
+    return names
+
+
+def _integration_snippet_fields() -> list[str]:
+    """Field names of the `GemmArgs` ctypes structure shown in INTEGRATION.md, by evaluating that snippet."""
+    import ctypes
+
+    md = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    code = re.search(r"class GemmArgs\(C\.Structure\):.*?\n\n", md, re.S).group(0)
+    ns = {"C": ctypes}
+    exec(code, ns)
+    return [f[0] for f in ns["GemmArgs"]._fields_], ctypes.sizeof(ns["GemmArgs"])
+
+
+def test_struct_fields_match_the_header_and_the_integration_snippet():
+    # a binding that is one field short makes the library read past the caller's struct
+    from nunchaku_rocm_b200 import _lib
+
+    for cname, ctype in (("nb_gemm_args", _lib.GemmArgs), ("nb_qk_args", _lib.QKArgs),
+                         ("nb_requant_args", _lib.RequantArgs), ("nb_quant_args", _lib.QuantArgs),
+                         ("nb_attn_args", _lib.AttnArgs)):
+        assert _header_struct_fields(cname) == [f[0] for f in ctype._fields_], cname
+    names, size = _integration_snippet_fields()
+    assert names == _header_struct_fields("nb_gemm_args")
+    assert size == ctypes_size(_lib.GemmArgs)
+
+
 def ctypes_size(t):
     import ctypes
 
@@ -112,3 +153,39 @@ def test_product_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh")):
                 src = open(os.path.join(dirpath, f)).read()
                 assert not re.search(r"^\s*(from|import)\s+oracle\b", src, re.M), f"{f} imports the oracle"
+
+
+def test_a_failing_self_test_raises_on_first_use(monkeypatch):
+    # the reference refuses to use its native module when the load-time self-test fails
+    # (nunchaku/ops/triton/native/w4a4.py:371-389); here the first op on a device raises
+    import contextlib
+
+    from nunchaku_rocm_b200 import _lib
+
+    class FakeLib:
+        calls = 0
+
+        def nb_selftest(self):
+            FakeLib.calls += 1
+            return _lib.NB_ERR_DEVICE
+
+        def nb_strerror(self, rc):
+            return b"a kernel gave up on a bounded wait"
+
+    monkeypatch.setattr(_lib, "lib", lambda: FakeLib())
+    monkeypatch.setattr(_lib, "_selftested", set())
+    monkeypatch.setattr(torch.cuda, "device", lambda i: contextlib.nullcontext())
+    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: False)
+    monkeypatch.delenv("NUNCHAKU_B200_SELFTEST", raising=False)
+    with pytest.raises(RuntimeError, match="self-test failed on cuda:3"):
+        _lib.ensure_selftest(torch.device("cuda", 3))
+    assert FakeLib.calls == 1 and 3 not in _lib._selftested
+    # a passing test is remembered per device and not repeated
+    FakeLib.nb_selftest = lambda self: 0
+    _lib.ensure_selftest(torch.device("cuda", 3))
+    _lib.ensure_selftest(torch.device("cuda", 3))
+    assert 3 in _lib._selftested
+    # inside a stream capture the test is postponed, not skipped for good
+    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: True)
+    _lib.ensure_selftest(torch.device("cuda", 4))
+    assert 4 not in _lib._selftested

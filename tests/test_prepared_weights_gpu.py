@@ -73,6 +73,36 @@ def test_in_place_weight_update_invalidates_the_entry(cuda_dev, monkeypatch):
     assert not G._PREPARED
 
 
+def test_buffers_used_inside_a_graph_capture_outlive_the_cache(cuda_dev, monkeypatch):
+    # a captured call bakes the prepared buffer's address into the graph: clearing or evicting the cache must not free it
+    p = _inputs(cuda_dev, seed=3)
+    G.clear_prepared_weights(release_pinned=True)
+    want = _call(p, monkeypatch)  # prepares the entry outside the capture
+    out = torch.zeros_like(want)
+    side = torch.cuda.Stream(cuda_dev)
+    side.wait_stream(torch.cuda.current_stream(cuda_dev))
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            G.gemm_w4a4(p["act"], p["wgt"], out, p["ascales"], p["wscales"], p["bias"], p["lora_act"], p["lora_up"])
+    torch.cuda.current_stream(cuda_dev).wait_stream(side)
+    (entry,) = G._PREPARED.values()
+    assert entry[G._E_PINNED]
+    monkeypatch.setenv("NUNCHAKU_B200_PREPARED_WEIGHTS_MB", "1")  # a budget that evicts everything evictable
+    q = _inputs(cuda_dev, M=128, N=256, K=256, seed=4)
+    _call(q)
+    assert entry in G._PREPARED.values(), "a pinned entry was evicted"
+    G.clear_prepared_weights()
+    assert not G._PREPARED and len(G._PINNED_BUFFERS) == 1
+    filler = [torch.full((entry[G._E_BUF].numel(),), 0xAB, dtype=torch.uint8, device=cuda_dev) for _ in range(4)]
+    graph.replay()
+    torch.cuda.synchronize(cuda_dev)
+    assert torch.equal(out, want), "the replay read a buffer that had been released"
+    del filler, graph
+    G.clear_prepared_weights(release_pinned=True)
+    assert not G._PINNED_BUFFERS
+
+
 def test_c_abi_prepared_bytes_and_scratch(cuda_dev):
     p = _inputs(cuda_dev, M=256, N=256, K=256)
     out = torch.empty(256, 256, dtype=T, device=cuda_dev)
