@@ -42,9 +42,11 @@ enum {
 
 /* kernel selector (nb_gemm_args.impl) */
 enum {
-    NB_IMPL_AUTO = 0,    /* tcgen05 kernel when the call meets its alignment rules, else the generic kernel */
-    NB_IMPL_TCGEN05 = 1, /* tcgen05 kernel or NB_ERR_UNSUPPORTED */
-    NB_IMPL_GENERIC = 2  /* CUDA-core kernel that takes every shape the op accepts */
+    NB_IMPL_AUTO = 0,    /* a tcgen05 kernel when the call meets its alignment rules, else the generic kernel */
+    NB_IMPL_TCGEN05 = 1, /* a tcgen05 kernel (chosen as under AUTO) or NB_ERR_UNSUPPORTED */
+    NB_IMPL_GENERIC = 2, /* CUDA-core kernel that takes every shape the op accepts */
+    NB_IMPL_TCGEN05_PAIR = 3,  /* int4: the CTA-pair kernel (256 x 256 tiles) or NB_ERR_UNSUPPORTED */
+    NB_IMPL_TCGEN05_SINGLE = 4 /* int4: the single-CTA kernel (128 x 128 tiles) or NB_ERR_UNSUPPORTED */
 };
 
 /*

@@ -21,7 +21,7 @@ LIB_PATH = os.environ.get("NUNCHAKU_B200_LIB") or os.path.join(_HERE, "libnuncha
 NB_OK, NB_ERR_INVALID, NB_ERR_UNSUPPORTED, NB_ERR_LAUNCH, NB_ERR_DEVICE, NB_ERR_TOO_LARGE = range(6)
 DTYPE_CODE = {torch.bfloat16: 0, torch.float16: 1}
 EPI_STORE, EPI_QK, EPI_GELU_QUANT, EPI_SWIGLU_QUANT = range(4)
-IMPL_AUTO, IMPL_TCGEN05, IMPL_GENERIC = range(3)
+IMPL_AUTO, IMPL_TCGEN05, IMPL_GENERIC, IMPL_TCGEN05_PAIR, IMPL_TCGEN05_SINGLE = range(5)
 NOALLOC_SCRATCH_BYTES = 16 << 20  # NB_NOALLOC_SCRATCH_BYTES
 
 

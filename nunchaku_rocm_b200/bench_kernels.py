@@ -1,12 +1,12 @@
 """
-Per-kernel timings of the hot path on one GPU (a script, not a pytest file), after the reference's
+Per-kernel timings of the hot path on one GPU, after the reference's
 ``tests/triton/bench_kernels.py`` (:36-44: warm-up, timed iterations, TFLOP/s = 2MNK/t for GEMMs, 4BHT^2D/t for
 attention, GB/s for the quantizer).  Differences: CUDA events around a CUDA graph of the launches instead of wall clock, inputs
 rotated over several buffer sets so that HBM-bound kernels do not run out of L2, and every line carries the roofline
 that bounds the kernel and the fraction of the measured peak (``MEASURED_PEAKS.json`` beside the repository root, else
 the stated fallback).
 
-    python tests/bench_kernels.py [--iters 50] [--warmup 10] [--only quantize,gemm,mlp,fp4,awq,attention]
+    python -m nunchaku_rocm_b200.bench_kernels [--iters 50] [--warmup 10] [--only quantize,gemm,mlp,fp4,awq,attention]
 
 Prints one JSON object per kernel and shape.  Synthetic seeded inputs with the benchmark configurations' shapes.
 """
@@ -23,9 +23,10 @@ import sys
 import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-sys.path.insert(0, ROOT)
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
 
-from bench import make_cfg_inputs, measured_peaks  # noqa: E402
+from bench import make_cfg_inputs, measured_peaks  # noqa: E402  (bench.py sits at the repository root)
 
 
 def time_ms(fn, sets, iters, warmup):
@@ -132,7 +133,7 @@ def main():
             kw = (lambda p: dict(norm_q=p["norm_q"], norm_k=p["norm_k"], rotary_emb=p["rotary_emb"])) if name == "qk_norm_rope" else (lambda p: {})
             ms, best = time_ms(lambda p: gemm_w4a4(p["q"], p["qweight"], p["out"], p["s"], p["wscales"], p["bias"], p["l"],
                                                    p["proj_up"], act_unsigned=uns, **kw(p)), sets, args.iters, args.warmup)
-            emit("prepack_kernel + gemm_tc_kernel", f"{name}: M={M} K={K} N={N} R={R}", ms, best, 2.0 * M * N * K, "TFLOP/s",
+            emit("activation pre-pass + tcgen05 int4 GEMM", f"{name}: M={M} K={K} N={N} R={R}", ms, best, 2.0 * M * N * K, "TFLOP/s",
                  "tensor", i8, src + " x2 (8-bit pipe)")
             del sets
 
@@ -187,16 +188,12 @@ def main():
 
     # ---------------------------------------------------------------- AWQ W4A16 GEMV (HBM)
     if "awq" in only:
-        sys.path.insert(0, ROOT)
-        from oracle import awq_attn  # packing helper only (test infrastructure; this script is not product code)
-
         n, k = 18432, 3072
         g = torch.Generator().manual_seed(0)
         sets = []
         for i in range(8):  # 8 x 32 MB of weights > L2
-            q = torch.randint(0, 16, (n, k), dtype=torch.int32, generator=g)
-            sets.append(dict(
-                w=awq_attn.awq_pack(q).to(dev),
+            sets.append(dict(  # every 4-bit pattern is a valid code, so random words are a valid packed weight
+                w=torch.randint(-(2**31), 2**31 - 1, (n // 4, k // 2), dtype=torch.int32, generator=g).to(dev),
                 s=(torch.rand(k // 64, n, generator=g) * 0.1 + 0.01).to(T).to(dev),
                 z=(torch.randn(k // 64, n, generator=g) * 0.1).to(T).to(dev)))
         for m in (1, 2, 4, 8):

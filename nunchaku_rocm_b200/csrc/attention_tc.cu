@@ -41,17 +41,6 @@ constexpr int OFF_BAR = OFF_XCH + 6 * 128 * 4;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
 constexpr uint32_t TM_S = 0, TM_O = 256, TM_P = 384;
 
-#ifdef NB_PROF
-// Cycle accounting (debug builds only): the softmax warps of CTA (0, 0, 0) add up the clock() ticks they spend per phase.
-__device__ unsigned long long g_attn_prof[64];
-#define AT_PF_DECL unsigned pf_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; unsigned pf_t_ = clock();
-#define AT_PF(i) do { unsigned n_ = clock(); pf_[i] += n_ - pf_t_; pf_t_ = n_; } while (0)
-#define AT_PF_DUMP(w) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0) for (int i_ = 0; i_ < 8; ++i_) g_attn_prof[(w) * 8 + i_] = pf_[i_]; } while (0)
-#else
-#define AT_PF_DECL
-#define AT_PF(i) do {} while (0)
-#define AT_PF_DUMP(w) do {} while (0)
-#endif
 enum { B_Q = 0, B_KF = 1, B_KE = 3, B_VF = 5, B_VE = 7, B_SF = 9, B_SE = 11, B_PF = 13, B_PV = 15, B_XM = 17, B_COUNT = 21 };
 enum { E_PROD = 0x210, E_MMA = 0x230, E_SM = 0x240 };
 
@@ -250,13 +239,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         float m_used = -INFINITY, l = 0.f;
         uint32_t xph = 0;
         bool ok = true;
-        AT_PF_DECL
         for (int j = 0; j < NT && ok; ++j) {
             const int b = j & 1;
             const uint32_t par = (j >> 1) & 1;
-            AT_PF(7);
             if (!mbar_wait_warp(bar(B_SF + b), par, abort_s, E_SM | 1, 100)) { ok = false; break; }
-            AT_PF(0);
             tc_fence_after();
             float s[64];
 #pragma unroll
@@ -266,7 +252,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_SE + b));  // the score slot may be overwritten by tile j + 2
-            AT_PF(1);
             if (j == NT - 1 && (p.Tkv & (BN - 1))) {
                 const int valid = p.Tkv - j * BN - hf * 64;
 #pragma unroll
@@ -311,7 +296,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 }
                 m_used = m_new;
             }
-            AT_PF(2);
             // probabilities: fp32 for the (partial) row sum, rounded to T for the product
             uint32_t pk[32];
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -322,19 +306,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 pk[i] = pack2<T>(p0, p1);
             }
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            AT_PF(3);
             // the P slot is free once the product that read it two tiles ago has completed
             if (j >= 2 && !mbar_wait_warp(bar(B_PV + b), ((j - 2) >> 1) & 1, abort_s, E_SM | 3, 100)) { ok = false; break; }
-            AT_PF(4);
             tc_fence_after();
             tmem_st32(lane_addr + TM_P + b * 64 + hf * 32, pk);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_PF + b));
-            AT_PF(5);
         }
-        AT_PF_DUMP(warp - 2);
         if (ok && NT > 0) {
             // total row sum = the two halves' partial sums
             xsum[hf * 128 + row] = l;
@@ -578,8 +558,3 @@ int launch_attention_tc(const nb_attn_args* a, cudaStream_t s) {
 
 }  // namespace nb
 
-#ifdef NB_PROF
-extern "C" int nb_debug_attn_prof(unsigned long long* host64) {
-    return cudaMemcpyFromSymbol(host64, nb::atc::g_attn_prof, 64 * sizeof(unsigned long long)) == cudaSuccess ? 0 : 3;
-}
-#endif

@@ -106,17 +106,6 @@ struct TcParams {
     float eps;
 };
 
-#ifdef NB_PROF
-// Cycle accounting (debug builds only): every warp of CTA 0 adds up the clock() ticks it spends per phase.
-__device__ unsigned long long* g_prof = nullptr;
-#define NB_PF_DECL unsigned pf_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; unsigned pf_t_ = clock();
-#define NB_PF(i) do { unsigned n_ = clock(); pf_[i] += n_ - pf_t_; pf_t_ = n_; } while (0)
-#define NB_PF_DUMP() do { if (g_prof && blockIdx.x == 0 && (threadIdx.x & 31) == 0) for (int i_ = 0; i_ < 8; ++i_) g_prof[(threadIdx.x >> 5) * 8 + i_] = pf_[i_]; } while (0)
-#else
-#define NB_PF_DECL
-#define NB_PF(i) do {} while (0)
-#define NB_PF_DUMP() do {} while (0)
-#endif
 
 // error codes written to *status: role * 16 + barrier kind
 enum { E_PROD = 0x10, E_MMA = 0x30, E_DRAIN = 0x40 };
@@ -193,12 +182,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             uint32_t it = 0;
             uint32_t sc_uses = 0;  // 8 bits per stage: how many int8 fills the stage has had (mod 256)
             bool ok = true;
-            NB_PF_DECL
             for (int t = t_begin; t < t_end && ok; ++t) {
                 const int m0 = (t / NT) * BM, n0 = (t % NT) * BN;
                 for (int j = 0; j < GS + LCH; ++j, ++it) {
                     const int s = it % STAGES;
-                    NB_PF(7);
                     if (!mbar_wait(bar(B_DONE + s), ((it / STAGES) & 1) ^ 1, abort_s, E_PROD | 1, 500)) { ok = false; break; }
                     {
                         // the drain must also be done with the scales of the stage's last int8 fill
@@ -206,7 +193,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         if (!mbar_wait(bar(B_SCDONE + s), (n & 1) ^ 1, abort_s, E_PROD | 2, 500)) { ok = false; break; }
                         if (j < GS) sc_uses = (sc_uses & ~(0xFFu << (8 * s))) | (((n + 1) & 0xFFu) << (8 * s));
                     }
-                    NB_PF(0);
                     const uint32_t dst = s_base + C::OFF_ST + s * C::ST_BYTES;
                     if (j < GS) {
                         mbar_expect_tx(bar(B_FULL + s), C::ST_A + C::ST_W + C::ST_AS + C::ST_WS_TX);
@@ -222,7 +208,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                 }
             }
-            NB_PF_DUMP();
             if (!ok) {
                 // let copies already in flight land before the CTA goes away (bounded)
                 for (int s = 0; s < STAGES; ++s) {
@@ -242,20 +227,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const uint32_t idesc_lr = umma_idesc(1u, f16fmt, f16fmt, BN);
             uint32_t it = 0, ait = 0;
             bool ok = true;
-            NB_PF_DECL
             // One batch per ring stage: both K groups of the stage (four MMAs) and ONE commit.  The issuing thread
             // pays a few hundred cycles per wait / commit, so the work between two of them has to be large.
             for (int t = t_begin; t < t_end && ok; ++t) {
                 for (int j = 0; j < GS && ok; ++j, ++it) {
                     const int s = it % STAGES;
                     const int ng = min(2, G - 2 * j);
-                    NB_PF(7);
                     if (!mbar_wait(bar(B_FULL + s), (it / STAGES) & 1, abort_s, E_MMA | 1, 100)) { ok = false; break; }
-                    NB_PF(0);
                     // the first group's slot is released half a stage before the second's: its MMAs go out before the
                     // issuer waits for the second slot
                     if (!mbar_wait(bar(B_ACC_EMPTY + ait % NSLOT), ((ait / NSLOT) & 1) ^ 1, abort_s, E_MMA | 2, 100)) { ok = false; break; }
-                    NB_PF(1);
                     tc_fence_after();
                     const uint32_t a_addr = s_base + C::OFF_ST + s * C::ST_BYTES;
                     const uint64_t da = umma_desc_sw128(a_addr), dw = umma_desc_sw128(a_addr + C::ST_A);
@@ -266,9 +247,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         mma_f8(d, da + 2, dw + 2, idesc_f8, 1u);
                     }
                     if (ng == 2) {
-                        NB_PF(2);
                         if (!mbar_wait(bar(B_ACC_EMPTY + (ait + 1) % NSLOT), (((ait + 1) / NSLOT) & 1) ^ 1, abort_s, E_MMA | 2, 100)) { ok = false; break; }
-                        NB_PF(1);
                         tc_fence_after();
                         const uint32_t d = tmem_base + ((ait + 1) % NSLOT) * BN;
                         mma_f8(d, da + 4, dw + 4, idesc_f8, 0u);
@@ -276,7 +255,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                     tc_commit(bar(B_DONE + s));
                     ait += ng;
-                    NB_PF(2);
                 }
                 if (ok && LCH > 0) {
                     const int slot = ait % NSLOT;
@@ -293,10 +271,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         tc_commit(bar(B_DONE + s));
                     }
                     if (ok) { tc_commit(bar(B_LR)); ++ait; }
-                    NB_PF(3);
                 }
             }
-            NB_PF_DUMP();
         }
     } else {
         // ================================ drain + epilogue ================================
@@ -315,7 +291,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         bool ok = true;
         uint64_t acc[NV];  // [lane block lb][j][row select] pairs of fp32
         uint32_t v[2][NV];
-        NB_PF_DECL
 
         for (int t = t_begin; t < t_end && ok; ++t) {
             const int m0 = (t / NT) * BM, n0 = (t % NT) * BN;
@@ -326,9 +301,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             // loads of the next are in flight.  `v[0]` holds lane block 0, `v[1]` lane block 1 of a group.  The MMA warp
             // completes a ring stage (two groups) at a time, so there is one wait per stage.
             {
-                NB_PF(7);
                 if (!mbar_wait_warp(bar(B_DONE + it % STAGES), (it / STAGES) & 1, abort_s, E_DRAIN | 1, 100)) { ok = false; break; }
-                NB_PF(0);
                 tc_fence_after();
                 tmem_ld_16x256b(lane_base + (ait % NSLOT) * BN, v[0]);
             }
@@ -350,9 +323,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     const float2 f0 = unpack2<T>(w16[2 * jj]), f1 = unpack2<T>(w16[2 * jj + 1]);
                     w[jj] = make_ulonglong2(pack_f32x2(f0.x, f0.y), pack_f32x2(f1.x, f1.y));
                 }
-                NB_PF(1);
                 tmem_wait_ld();  // v[0] has landed
-                NB_PF(2);
                 tmem_ld_16x256b(lane_base + (16u << 16) + slot * BN, v[1]);
 #pragma unroll
                 for (int lb = 0; lb < 2; ++lb) {
@@ -370,7 +341,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             asm volatile("" ::"l"(as2[2]), "l"(as2[3]), "l"(w[NJ / 2 - 1].y) : "memory");
                             if (lane == 0) mbar_arrive(bar(B_SCDONE + s));
                         }
-                        NB_PF(3);
                         // next accumulator: the stage's second group, the next stage, or the low-rank slot after the last group
                         if (!last_of_stage) {
                             tmem_ld_16x256b(lane_base + ((ait + 1) % NSLOT) * BN, v[0]);
@@ -380,11 +350,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             const bool more = g + 1 < G;
                             if (!mbar_wait_warp(more ? bar(B_DONE + (itg + 1) % STAGES) : bar(B_LR),
                                                 more ? ((itg + 1) / STAGES) & 1 : (uint32_t)(t - t_begin) & 1, abort_s, E_DRAIN | 2, 100)) { ok = false; break; }
-                            NB_PF(5);
                             tc_fence_after();
                             tmem_ld_16x256b(lane_base + ((ait + 1) % NSLOT) * BN, v[0]);
                         }
-                        NB_PF(0);
                     }
                     if (EPI == NB_EPI_QK_NORM_ROPE) {
 #pragma unroll
@@ -430,7 +398,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                                 p.p_out[((long long)g * p.M + m) * p.N + n] = (int)__uint_as_float(vv[e]);
                         }
                     }
-                    NB_PF(4);
                 }
                 if (!ok) break;
             }
@@ -580,9 +547,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         *reinterpret_cast<uint4*>(static_cast<T*>(p.out) + (long long)mm * p.stride_om + nn) = o;
                 }
             }
-            NB_PF(6);
         }
-        NB_PF_DUMP();
     }
 
     // ---------------- teardown ----------------
@@ -607,19 +572,6 @@ struct PrepackParams {
     int do_act, do_wgt;      // which half of the work this launch does (activation side / weight side)
     long long stride_am, stride_wn, stride_asg, stride_wsg, stride_lam;
 };
-
-// Four nibbles (low 16 bits of `x`, element k in bits 4k..4k+3) -> four e4m3 bytes.  Signed nibbles are two's complement
-// -8..7, unsigned 0..15; every value is exact in e4m3.  Entries 0..7 and 8..15 of the table come from two byte permutes on
-// the low three bits; a third permute turns bit 3 of every nibble into a byte mask (selector 1 -> 0xFF, 0 -> 0x00).
-__device__ __forceinline__ uint32_t e4m3_of_nibbles(uint32_t x, bool uns) {
-    // e4m3: 0 1 2 3 4 5 6 7 -> 00 38 40 44 48 4A 4C 4E;  8..15 -> 50 51 52 53 54 55 56 57;  -8..-1 -> D0 CE CC CA C8 C4 C0 B8
-    const uint32_t lo0 = 0x44403800u, lo1 = 0x4E4C4A48u;
-    const uint32_t hi0 = uns ? 0x53525150u : 0xCACCCED0u, hi1 = uns ? 0x57565554u : 0xB8C0C4C8u;
-    const uint32_t sel = x & 0x7777u;
-    const uint32_t lo = __byte_perm(lo0, lo1, sel), hi = __byte_perm(hi0, hi1, sel);
-    const uint32_t m = __byte_perm(0x0000FF00u, 0u, (x & 0x8888u) >> 3);
-    return lo ^ ((lo ^ hi) & m);
-}
 
 template <typename T>
 __global__ void __launch_bounds__(256) prepack_kernel(const PrepackParams p) {
@@ -720,22 +672,11 @@ static inline size_t up256(size_t x) { return (x + 255) & ~size_t(255); }
 
 // The weight side (w8, wsf) lives in the caller's prepared buffer when there is one, else in the call's scratch after the
 // activation side.
-struct Prepared {
-    size_t w8, wsf, total;
-    int Np;
-};
-static Prepared prepared_layout(const nb_gemm_args* a) {
-    Prepared s;
-    s.Np = (a->N + BN - 1) / BN * BN;
-    size_t off = 0;
-    s.w8 = off; off += up256((size_t)a->N * a->K);
-    s.wsf = off; off += up256((size_t)(a->K / 64) * s.Np * 2);
-    s.total = off;
-    return s;
-}
-static bool has_prepared(const nb_gemm_args* a) {
-    return a->wgt_prepared && a->wgt_prepared_bytes >= (int64_t)prepared_layout(a).total &&
-           (reinterpret_cast<uintptr_t>(a->wgt_prepared) & 255) == 0;
+static bool has_prepared(const nb_gemm_args* a) { return has_prepared_weights(a); }
+struct WeightSide { size_t w8, wsf, total; };
+static WeightSide weight_side(const nb_gemm_args* a) {  // the part of the prepared layout this kernel reads
+    const PreparedLayout pl = nb::prepared_layout(a->N, a->K);
+    return {pl.w8, pl.wsf, pl.wsf2};
 }
 struct Scratch {
     size_t a8, asf, la16, wside, total;
@@ -751,7 +692,7 @@ static Scratch scratch_layout(const nb_gemm_args* a) {
     s.asf = off; off += up256(G * s.Mp * 4);
     s.la16 = off; off += up256((size_t)a->M * a->R * 2);
     s.wside = off;
-    if (!has_prepared(a)) off += prepared_layout(a).total;
+    if (!has_prepared(a)) off += weight_side(a).total;
     s.total = off;
     return s;
 }
@@ -786,7 +727,7 @@ static int launch_t(const nb_gemm_args* a, const TcParams& p, cudaStream_t s) {
         return NB_ERR_INVALID;
     uint8_t* base = static_cast<uint8_t*>(a->scratch);
     const bool prepared = has_prepared(a);
-    const Prepared pl = prepared_layout(a);
+    const WeightSide pl = weight_side(a);
     uint8_t* wbase = prepared ? const_cast<uint8_t*>(static_cast<const uint8_t*>(a->wgt_prepared)) : base + sc.wside;
     PrepackParams pp;
     fill_prepack_params(pp, a);
@@ -827,12 +768,6 @@ static int launch_t(const nb_gemm_args* a, const TcParams& p, cudaStream_t s) {
 
 }  // namespace tc
 
-#ifdef NB_PROF
-extern "C" int nb_debug_set_prof(void* ptr) {
-    unsigned long long* v = static_cast<unsigned long long*>(ptr);
-    return cudaMemcpyToSymbol(tc::g_prof, &v, sizeof(v)) == cudaSuccess ? 0 : 3;
-}
-#endif
 
 // What a weight must satisfy for the tensor-core kernel, whatever the call around it looks like.
 static bool tc_weight_ok(const nb_gemm_args* a) {
@@ -840,19 +775,24 @@ static bool tc_weight_ok(const nb_gemm_args* a) {
            aligned16(a->wgt) && a->stride_wn % 16 == 0 && (a->dtype == NB_DTYPE_BF16 || a->dtype == NB_DTYPE_FP16);
 }
 
-int64_t tc_prepared_bytes(const nb_gemm_args* a) { return tc_weight_ok(a) ? (int64_t)tc::prepared_layout(a).total : 0; }
+int tcp_prepare_scales(const nb_gemm_args* a, void* wsf2, cudaStream_t s);
 
+int64_t tc_prepared_bytes(const nb_gemm_args* a) { return tc_weight_ok(a) ? (int64_t)prepared_layout(a->N, a->K).total : 0; }
+
+// One e4m3 byte per weight value, then the column scales in the order of either tensor-core kernel's drain.
 int tc_prepare_weights(const nb_gemm_args* a, void* dst, int64_t dst_bytes, cudaStream_t s) {
     if (!tc_weight_ok(a)) return NB_ERR_UNSUPPORTED;
-    const tc::Prepared pl = tc::prepared_layout(a);
+    const PreparedLayout pl = prepared_layout(a->N, a->K);
     if (!dst || dst_bytes < (int64_t)pl.total || (reinterpret_cast<uintptr_t>(dst) & 255)) return NB_ERR_INVALID;
     tc::PrepackParams pp = {};
     pp.wgt = static_cast<const uint8_t*>(a->wgt); pp.wscales = a->wscales;
-    pp.N = a->N; pp.K = a->K; pp.Np = pl.Np;
+    pp.N = a->N; pp.K = a->K; pp.Np = pl.Np128;
     pp.stride_wn = a->stride_wn; pp.stride_wsg = a->stride_wsg;
     pp.w8 = reinterpret_cast<int8_t*>(static_cast<uint8_t*>(dst) + pl.w8); pp.wsf = static_cast<uint8_t*>(dst) + pl.wsf;
     pp.do_act = 0; pp.do_wgt = 1;
-    return a->dtype == NB_DTYPE_BF16 ? tc::launch_prepack<__nv_bfloat16>(pp, s) : tc::launch_prepack<__half>(pp, s);
+    const int st = a->dtype == NB_DTYPE_BF16 ? tc::launch_prepack<__nv_bfloat16>(pp, s) : tc::launch_prepack<__half>(pp, s);
+    if (st != NB_OK) return st;
+    return tcp_prepare_scales(a, static_cast<uint8_t*>(dst) + pl.wsf2, s);
 }
 
 // Why the tcgen05 kernel cannot take this call, or nullptr (the role of `unsupported_reason`,

@@ -30,13 +30,34 @@ int launch_tc(const nb_gemm_args* a, const void* epi, int epi_kind, int32_t* p_o
 int64_t tc_scratch_bytes(const nb_gemm_args* a);
 int64_t tc_prepared_bytes(const nb_gemm_args* a);
 int tc_prepare_weights(const nb_gemm_args* a, void* dst, int64_t dst_bytes, cudaStream_t s);
+const char* tcp_unsupported_reason(const nb_gemm_args* a, const void* epi, int epi_kind);
+int launch_tc_pair(const nb_gemm_args* a, const void* epi, int epi_kind, int32_t* p_out, cudaStream_t s);
+int64_t tcp_scratch_bytes(const nb_gemm_args* a, const void* epi, int epi_kind);
 const char* tc_fp4_unsupported_reason(const nb_gemm_args* a, const void* epi, int epi_kind);
 int launch_tc_fp4(const nb_gemm_args* a, cudaStream_t s);
 int64_t tc_fp4_scratch_bytes(const nb_gemm_args* a);
 
-// int4 calls go to the kind::f8f6f4 kernel, NVFP4 calls to the block-scaled kind::mxf4nvf4 kernel
-static const char* tc_reason(const nb_gemm_args* a, const void* epi, int epi_kind) {
-    return a->fp4 ? tc_fp4_unsupported_reason(a, epi, epi_kind) : tc_unsupported_reason(a, epi, epi_kind);
+// Which kernel takes the call.  NVFP4 calls go to the block-scaled kind::mxf4nvf4 kernel.  int4 calls go to one of the two
+// kind::f8f6f4 kernels: the CTA-pair kernel (256 x 256 tiles over half as many schedulable units, twice the throughput
+// per operand byte, the only one with the fused GELU re-quantisation) when the problem fills at least two thirds of the
+// pairs of a 148-SM device or needs its epilogue, else the single-CTA kernel (128 x 128 tiles).
+enum Kernel { K_GENERIC = 0, K_TC_SINGLE, K_TC_PAIR, K_TC_FP4 };
+static Kernel choose_kernel(const nb_gemm_args* a, const void* epi, int epi_kind, const char** why) {
+    *why = nullptr;
+    if (a->impl == NB_IMPL_GENERIC) return K_GENERIC;
+    if (a->fp4) {
+        *why = tc_fp4_unsupported_reason(a, epi, epi_kind);
+        return *why ? K_GENERIC : K_TC_FP4;
+    }
+    const char* single = tc_unsupported_reason(a, epi, epi_kind);
+    const char* pair = tcp_unsupported_reason(a, epi, epi_kind);
+    if (a->impl == NB_IMPL_TCGEN05_PAIR) { *why = pair; return pair ? K_GENERIC : K_TC_PAIR; }
+    if (a->impl == NB_IMPL_TCGEN05_SINGLE) { *why = single; return single ? K_GENERIC : K_TC_SINGLE; }
+    const long long pair_tiles = (long long)((a->M + 255) / 256) * ((a->N + 255) / 256);
+    if (!pair && (single || pair_tiles >= 48)) return K_TC_PAIR;
+    if (!single) return K_TC_SINGLE;
+    *why = single;
+    return K_GENERIC;
 }
 
 static int validate(const nb_gemm_args* a, const void* epi, int epi_kind) {
@@ -64,14 +85,20 @@ static int validate(const nb_gemm_args* a, const void* epi, int epi_kind) {
 }
 
 static bool uses_tc(const nb_gemm_args* a, const void* epi, int epi_kind) {
-    return a->impl != NB_IMPL_GENERIC && tc_reason(a, epi, epi_kind) == nullptr;
+    const char* why;
+    return choose_kernel(a, epi, epi_kind, &why) != K_GENERIC;
 }
 
-// The tensor-core kernel keeps its pre-widened operands and fp32 scales in scratch; the generic kernel keeps the
-// fp32 tile there when a row-wise epilogue follows.
+// The tensor-core kernels keep their operand form (e4m3 bytes, ordered scales, rounded lora_act, epilogue inputs) in
+// scratch; the generic kernel keeps the fp32 tile there when a row-wise epilogue follows.
 static int64_t scratch_bytes(const nb_gemm_args* a, const void* epi, int epi_kind) {
-    if (uses_tc(a, epi, epi_kind)) return a->fp4 ? tc_fp4_scratch_bytes(a) : tc_scratch_bytes(a);
-    return epi_kind == NB_EPI_STORE ? 0 : (int64_t)a->M * a->N * 4;
+    const char* why;
+    switch (choose_kernel(a, epi, epi_kind, &why)) {
+        case K_TC_FP4: return tc_fp4_scratch_bytes(a);
+        case K_TC_SINGLE: return tc_scratch_bytes(a);
+        case K_TC_PAIR: return tcp_scratch_bytes(a, epi, epi_kind);
+        default: return epi_kind == NB_EPI_STORE ? 0 : (int64_t)a->M * a->N * 4;
+    }
 }
 
 static GenericParams to_generic(const nb_gemm_args* a) {
@@ -100,9 +127,12 @@ extern "C" int nb_gemm_w4a4(const nb_gemm_args* a, const void* epi, int epi_kind
     if (st != NB_OK) return st;
     if (a->M == 0) return NB_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const char* reason = tc_reason(a, epi, epi_kind);
-    if (a->impl == NB_IMPL_TCGEN05 && reason) return NB_ERR_UNSUPPORTED;
-    if (a->impl != NB_IMPL_GENERIC && !reason) return a->fp4 ? launch_tc_fp4(a, s) : launch_tc(a, epi, epi_kind, nullptr, s);
+    const char* reason;
+    const Kernel k = choose_kernel(a, epi, epi_kind, &reason);
+    if (k == K_GENERIC && a->impl != NB_IMPL_AUTO && a->impl != NB_IMPL_GENERIC) return NB_ERR_UNSUPPORTED;
+    if (k == K_TC_FP4) return launch_tc_fp4(a, s);
+    if (k == K_TC_SINGLE) return launch_tc(a, epi, epi_kind, nullptr, s);
+    if (k == K_TC_PAIR) return launch_tc_pair(a, epi, epi_kind, nullptr, s);
 
     GenericParams p = to_generic(a);
     if (epi_kind == NB_EPI_STORE) {
@@ -139,9 +169,11 @@ extern "C" int nb_gemm_w4a4_group_sums(const nb_gemm_args* a, int32_t* p_out, vo
     NB_REQUIRE(p_out && !a->fp4);
     if (a->M == 0) return NB_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const char* reason = tc_unsupported_reason(a, nullptr, NB_EPI_STORE);
-    if (a->impl == NB_IMPL_TCGEN05 && reason) return NB_ERR_UNSUPPORTED;
-    if (a->impl != NB_IMPL_GENERIC && !reason) return launch_tc(a, nullptr, NB_EPI_STORE, p_out, s);
+    const char* reason;
+    const Kernel k = choose_kernel(a, nullptr, NB_EPI_STORE, &reason);
+    if (k == K_GENERIC && a->impl != NB_IMPL_AUTO && a->impl != NB_IMPL_GENERIC) return NB_ERR_UNSUPPORTED;
+    if (k == K_TC_SINGLE) return launch_tc(a, nullptr, NB_EPI_STORE, p_out, s);
+    if (k == K_TC_PAIR) return launch_tc_pair(a, nullptr, NB_EPI_STORE, p_out, s);
     GenericParams p = to_generic(a);
     p.out = a->out;
     p.p_out = p_out;

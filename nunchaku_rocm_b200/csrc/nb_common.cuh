@@ -320,6 +320,43 @@ __device__ __forceinline__ uint64_t umma_desc_kmajor(uint32_t smem_addr, uint32_
     return d;
 }
 
+// Four nibbles (low 16 bits of `x`, element k in bits 4k..4k+3) -> four e4m3 bytes.  Signed nibbles are two's complement
+// -8..7, unsigned 0..15; every value is exact in e4m3.  Entries 0..7 and 8..15 of the table come from two byte permutes on
+// the low three bits; a third permute turns bit 3 of every nibble into a byte mask (selector 1 -> 0xFF, 0 -> 0x00).
+__device__ __forceinline__ uint32_t e4m3_of_nibbles(uint32_t x, bool uns) {
+    // e4m3: 0 1 2 3 4 5 6 7 -> 00 38 40 44 48 4A 4C 4E;  8..15 -> 50 51 52 53 54 55 56 57;  -8..-1 -> D0 CE CC CA C8 C4 C0 B8
+    const uint32_t lo0 = 0x44403800u, lo1 = 0x4E4C4A48u;
+    const uint32_t hi0 = uns ? 0x53525150u : 0xCACCCED0u, hi1 = uns ? 0x57565554u : 0xB8C0C4C8u;
+    const uint32_t sel = x & 0x7777u;
+    const uint32_t lo = __byte_perm(lo0, lo1, sel), hi = __byte_perm(hi0, hi1, sel);
+    const uint32_t m = __byte_perm(0x0000FF00u, 0u, (x & 0x8888u) >> 3);
+    return lo ^ ((lo ^ hi) & m);
+}
+
+// Load-time form of an int4 weight for the tensor-core kernels (nb_gemm_w4a4_prepare_weights): one e4m3 byte per value,
+// then the column scales in the single-CTA kernel's drain order (T, N rounded up to 128) and in the CTA-pair kernel's
+// (fp32, N rounded up to 256).  Offsets in bytes, each region 256-byte aligned.
+struct PreparedLayout {
+    size_t w8, wsf, wsf2, total;
+    int Np128, Np256;
+};
+static inline PreparedLayout prepared_layout(int N, int K) {
+    auto up256 = [](size_t x) { return (x + 255) & ~size_t(255); };
+    PreparedLayout s;
+    s.Np128 = (N + 127) / 128 * 128;
+    s.Np256 = (N + 255) / 256 * 256;
+    size_t off = 0;
+    s.w8 = off; off += up256((size_t)N * K);
+    s.wsf = off; off += up256((size_t)(K / 64) * s.Np128 * 2);
+    s.wsf2 = off; off += up256((size_t)(K / 64) * s.Np256 * 4);
+    s.total = off;
+    return s;
+}
+static inline bool has_prepared_weights(const nb_gemm_args* a) {
+    return a->wgt_prepared && a->wgt_prepared_bytes >= (int64_t)prepared_layout(a->N, a->K).total &&
+           (reinterpret_cast<uintptr_t>(a->wgt_prepared) & 255) == 0;
+}
+
 // Instruction descriptor (dense, K-major A and B, M = 128)
 __device__ __host__ constexpr uint32_t umma_idesc(uint32_t c_fmt, uint32_t a_fmt, uint32_t b_fmt, uint32_t n) {
     return (c_fmt << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);

@@ -117,7 +117,9 @@ def test_c_abi_prepared_bytes_and_scratch(cuda_dev):
     assert lib.nb_gemm_w4a4_prepare_weights(C.byref(a), L.ptr(buf), nbytes, L.stream_of(out)) == 0
     a.wgt_prepared, a.wgt_prepared_bytes = L.ptr(buf), nbytes
     need_prepared = lib.nb_gemm_w4a4_scratch_bytes(C.byref(a), None, L.EPI_STORE)
-    assert need_prepared == need_plain - nbytes
+    # the call no longer keeps the weight side in scratch (the buffer holds the scale order of both tensor-core kernels,
+    # a call needs one of them)
+    assert 256 * 256 <= need_plain - need_prepared <= nbytes
     # NVFP4 weights have no prepared form
     a.fp4 = 1
     assert lib.nb_gemm_w4a4_prepared_bytes(C.byref(a)) == 0

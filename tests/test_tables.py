@@ -1,6 +1,6 @@
 """
 Constants of the CUDA sources that can be checked without a GPU: the byte tables that turn an int4 code into the e4m3
-value the tensor core multiplies (gemm_tc.cu), read from the source text and decoded with torch's float8_e4m3fn.
+value the tensor core multiplies (nb_common.cuh, used by both tensor-core GEMMs), read from the source text and decoded with torch's float8_e4m3fn.
 """
 
 import os
@@ -9,7 +9,7 @@ import re
 import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-SRC = open(os.path.join(ROOT, "nunchaku_rocm_b200", "csrc", "gemm_tc.cu")).read()
+SRC = open(os.path.join(ROOT, "nunchaku_rocm_b200", "csrc", "nb_common.cuh")).read()
 
 
 def _table(lo_name, hi_name=None, pick=None):

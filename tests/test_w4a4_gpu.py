@@ -15,7 +15,7 @@ from tests.conftest import load_golden
 
 pytestmark = pytest.mark.gpu
 
-TC, GENERIC = 1, 2
+TC, GENERIC, PAIR, SINGLE = 1, 2, 3, 4  # nb_gemm_args.impl: any tcgen05 kernel, CUDA cores, CTA-pair kernel, single-CTA kernel
 DTYPES = [torch.bfloat16, torch.float16]
 
 
@@ -61,7 +61,7 @@ def _close(out, ref, what=""):
 # ------------------------------------------------------------------------------------------------
 # golden fixtures (outputs of the reference's own `reference()`), every kernel
 # ------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("impl", [GENERIC, TC])
+@pytest.mark.parametrize("impl", [GENERIC, SINGLE, PAIR])
 @pytest.mark.parametrize("tag", ["a", "b"])
 def test_gemm_matches_golden(cuda_dev, impl, tag):
     K = _ops()
@@ -84,7 +84,7 @@ def test_gemm_matches_golden(cuda_dev, impl, tag):
 # ------------------------------------------------------------------------------------------------
 # the integer contract: exact int32 group sums
 # ------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("impl", [GENERIC, TC])
+@pytest.mark.parametrize("impl", [GENERIC, SINGLE, PAIR])
 @pytest.mark.parametrize("act_unsigned", [False, True])
 @pytest.mark.parametrize("M,N,K", [(256, 512, 512), (136, 264, 256), (8, 8, 128)])
 def test_group_sums_bit_exact(cuda_dev, impl, act_unsigned, M, N, K):
@@ -96,7 +96,7 @@ def test_group_sums_bit_exact(cuda_dev, impl, act_unsigned, M, N, K):
     _status_clean(cuda_dev)
 
 
-@pytest.mark.parametrize("impl", [GENERIC, TC])
+@pytest.mark.parametrize("impl", [GENERIC, SINGLE, PAIR])
 @pytest.mark.parametrize("act_unsigned", [False, True])
 def test_group_sums_extreme_codes_bit_exact(cuda_dev, impl, act_unsigned):
     # The largest sums the format allows (|p| up to 64 * 15 * 8 = 7680) and every code pair at least once: the
@@ -121,7 +121,7 @@ def test_group_sums_extreme_codes_bit_exact(cuda_dev, impl, act_unsigned):
     _status_clean(cuda_dev)
 
 
-@pytest.mark.parametrize("impl", [GENERIC, TC])
+@pytest.mark.parametrize("impl", [GENERIC, SINGLE, PAIR])
 def test_unit_scale_output_is_exact_integer_sum(cuda_dev, impl):
     # with unit scales the fp32 tile is sum_g p_g exactly (tests/triton/test_native_gemm.py:166-179)
     Kn = _ops()
@@ -143,7 +143,7 @@ def test_unit_scale_output_is_exact_integer_sum(cuda_dev, impl):
 # shapes, dtypes, tails, strides, determinism
 # ------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("impl", [GENERIC, TC])
+@pytest.mark.parametrize("impl", [GENERIC, SINGLE, PAIR])
 @pytest.mark.parametrize(
     "M,N,K,R", [(256, 256, 512, 32), (128, 512, 1024, 16), (64, 128, 256, 0), (264, 72, 384, 48), (520, 776, 128, 288)]
 )
@@ -158,7 +158,7 @@ def test_gemm_bias_lora_shapes(cuda_dev, dtype, impl, M, N, K, R):
     _status_clean(cuda_dev)
 
 
-@pytest.mark.parametrize("impl", [GENERIC, TC])
+@pytest.mark.parametrize("impl", [GENERIC, SINGLE, PAIR])
 def test_gemm_strided_views_and_determinism(cuda_dev, impl):
     Kn = _ops()
     M, N, K, R = 200, 320, 256, 32
@@ -196,7 +196,7 @@ def test_tc_and_generic_agree_closely(cuda_dev):
 # ------------------------------------------------------------------------------------------------
 # fused Q/K RMSNorm + RoPE
 # ------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("impl", [GENERIC, TC])
+@pytest.mark.parametrize("impl", [GENERIC, SINGLE, PAIR])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("batch,S,heads", [(1, 130, 2), (2, 72, 1), (1, 256, 4)])
 def test_qk_norm_rope(cuda_dev, impl, dtype, batch, S, heads):
@@ -316,16 +316,20 @@ def test_quantize_op_pads_rows(cuda_dev):
 # ------------------------------------------------------------------------------------------------
 # fused GELU / SwiGLU + next-layer quantisation (generic fused kernel and the unfused composition)
 # ------------------------------------------------------------------------------------------------
-def _check_requant(qout, osc, lao, codes_ref, scale_ref, lora_ref, M, signed):
+def _check_requant(qout, osc, lao, codes_ref, scale_ref, lora_ref, M, signed, fused=False):
+    # bars of the reference's self-test against its torch form (native/w4a4.py:689-702); a kernel that re-quantises
+    # the fp32 tile inside the GEMM is held to a ten times smaller mismatch rate and to scales within one 16-bit step
     codes = _unpack_codes(qout[:M], signed)
     d = (codes - codes_ref).abs()
-    assert d.max() <= 1 and (d != 0).float().mean() < 1e-2
+    rate = (d != 0).float().mean().item()
+    assert d.max() <= 1 and rate < (2e-3 if fused else 1e-2), rate
     s = osc[:, :M].float().cpu()
-    assert ((s - scale_ref).abs() <= 1e-2 * scale_ref.abs() + 1e-6).all()
+    tol = 2.0**-7 if fused else 1e-2
+    assert ((s - scale_ref).abs() <= tol * scale_ref.abs() + 1e-6).all()
     assert (lao[:M].cpu() - lora_ref).abs().max() <= 1e-2 * lora_ref.abs().max()
 
 
-@pytest.mark.parametrize("impl", [0, GENERIC])
+@pytest.mark.parametrize("impl", [0, GENERIC, SINGLE])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("R2", [32, 48])
 def test_gelu_quant(cuda_dev, impl, dtype, R2):
@@ -344,7 +348,7 @@ def test_gelu_quant(cuda_dev, impl, dtype, R2):
         Kn.gemm_w4a4(*_cuda(cuda_dev, act, wgt), None, *_cuda(cuda_dev, asc, wsc, bias, la, lu), qout=qout[:M],
                      oscales=osc, smooth_factor=smooth.to(cuda_dev), lora_down=ld.to(cuda_dev), lora_act_out=lao,
                      act_unsigned=uns, out_dtype=dtype, _impl=impl)
-        _check_requant(qout, osc, lao, cr, sr, lr, M, signed=False)
+        _check_requant(qout, osc, lao, cr, sr, lr, M, signed=False, fused=impl != SINGLE)
         assert bool((qout[M:] == 0).all())
     _status_clean(cuda_dev)
 
