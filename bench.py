@@ -422,6 +422,7 @@ def run_ours(args) -> None:
     del sets, dx, dout
     torch.cuda.empty_cache()
     flux = None if args.no_flux else run_flux(args, dev, world, barrier)
+    qwen = None if args.no_qwen else run_qwen(args, dev, world, barrier)
 
     if rank == 0:
         peaks, src = measured_peaks()
@@ -472,6 +473,8 @@ def run_ours(args) -> None:
         }
         if flux is not None:
             line["flux"] = flux
+        if qwen is not None:
+            line["qwen_image"] = qwen
         if world == 1 and not args.no_cpu_baseline:
             os.sched_setaffinity(0, all_cpus)  # the CPU baseline may use every core again
             cb = cpu_baseline(budget_s=20.0, steps=3, warmup=1)
@@ -559,11 +562,53 @@ def run_flux(args, dev, world: int, barrier) -> dict:
         }
         del step
         torch.cuda.empty_cache()
+    del model
+    torch.cuda.empty_cache()
     best = max(out["batches"].values(), key=lambda r: r["images_per_s"])
     out["images_per_s"] = best["images_per_s"]
     out["e2e_images_per_s"] = best["e2e_images_per_s"]
     out["n_gpus"] = world
     return out
+
+
+def run_qwen(args, dev, world: int, barrier) -> dict:
+    """
+    Qwen-Image-architecture MMDiT with NVFP4 W4A4 layers: 60 blocks, hidden 3072, 24 x 128 heads, MLP 12288, 6889 image +
+    256 text tokens (1328 x 1328 latents), batch 1 per GPU, one forward per CUDA-graph replay.  Reported per transformer
+    forward (the configuration names no step count); `forwards_per_s` sums the ranks over the slowest rank's time.
+    """
+    from nunchaku_rocm_b200.models.qwen_dit import GraphedQwenStep, QwenDiT, QwenDiTConfig
+
+    cfg = QwenDiTConfig()
+    with torch.no_grad():
+        model = QwenDiT(cfg, device=dev).random_init(seed=100 + int(os.environ.get("RANK", "0")))
+        step = GraphedQwenStep(model, batch=1)
+        n = 3
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        step.step()
+        barrier()
+        e0.record()
+        for _ in range(n):
+            out = step.step()
+        e1.record()
+        barrier()
+        ms = max_over_ranks(e0.elapsed_time(e1), dev) / n
+        assert torch.isfinite(out.float()).all(), "the Qwen-Image forward is not finite"
+    tokens = 6889 + 256
+    ops = 60 * (2.0 * tokens * 3072 * (3 * 3072 + 3072 + 8 * 3072)) + 60 * 4.0 * 24 * tokens * tokens * 128
+    res = {
+        "model": "Qwen-Image architecture: 60 MMDiT blocks, hidden 3072, 24 x 128 heads, MLP 12288, rank 32, NVFP4 (e2m1 codes, "
+                 "e4m3 scale per 16, per-channel and per-tensor scales), distinct random-init weights",
+        "tokens": "6889 image + 256 text",
+        "weights_gb": round(model.quantized_bytes() / 2**30, 2),
+        "ms_per_forward": ms,
+        "forwards_per_s": world / (ms * 1e-3),
+        "tops_per_gpu": ops / (ms * 1e-3) / 1e12,
+        "n_gpus": world,
+    }
+    del step, model
+    torch.cuda.empty_cache()
+    return res
 
 
 def main() -> None:
@@ -574,6 +619,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-flux", action="store_true", help="skip the FLUX-architecture images/s measurement")
+    ap.add_argument("--no-qwen", action="store_true", help="skip the Qwen-Image-architecture (NVFP4) forward measurement")
     ap.add_argument("--flux-batches", default="1,4", help="per-GPU image batches to measure")
     ap.add_argument("--flux-images", type=int, default=4, help="image batches per timed region")
     args = ap.parse_args()

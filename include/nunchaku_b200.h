@@ -247,10 +247,19 @@ int nb_selftest(void);
  */
 int nb_debug_expire_wait(void* status, int64_t limit_us, void* stream);
 
+/*
+ * Diagnostics, the role of the reference's `native.status()` (nunchaku/ops/triton/native/w4a4.py:802-810): resource
+ * figures of the CTA-pair GEMM kernel on the current device, ten ints: registers per thread, max threads per block,
+ * static shared bytes, resident CTA pairs the occupancy query reports, that query's cudaError_t, dynamic shared bytes
+ * requested, threads per block, resident CTAs per SM without clusters, that query's cudaError_t, local-memory bytes.
+ */
+int nb_debug_pair_kernel_info(int* out10);
+
 /* Diagnostics (the reference's `status()` / error plumbing, nunchaku/ops/triton/native/hip.py:110-116). */
 const char* nb_strerror(int status);
 int nb_last_cuda_error(void);          /* cudaError_t of the last NB_ERR_LAUNCH, cleared by reading */
 const char* nb_last_cuda_error_string(void);
+const char* nb_last_error_detail(void); /* which check of the launcher refused the last failed call of this thread ("" if none), cleared by reading */
 int nb_version(void);
 int nb_num_sms(void);                  /* SM count of the current device, <= 0 on error */
 

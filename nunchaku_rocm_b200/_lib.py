@@ -110,6 +110,7 @@ def lib() -> C.CDLL:
                 l = C.CDLL(LIB_PATH)
                 l.nb_strerror.restype = C.c_char_p
                 l.nb_last_cuda_error_string.restype = C.c_char_p
+                l.nb_last_error_detail.restype = C.c_char_p
                 l.nb_gemm_w4a4_scratch_bytes.restype = C.c_int64
                 l.nb_gemm_w4a4.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_int, C.c_void_p]
                 l.nb_gemm_w4a4_scratch_bytes.argtypes = [C.POINTER(GemmArgs), C.c_void_p, C.c_int]
@@ -139,6 +140,9 @@ def check(status: int, what: str) -> None:
         return
     l = lib()
     msg = l.nb_strerror(status).decode()
+    detail = l.nb_last_error_detail().decode()
+    if detail:
+        msg += f" ({detail})"
     if status == NB_ERR_LAUNCH:
         msg += ": " + l.nb_last_cuda_error_string().decode()
         l.nb_last_cuda_error()

@@ -3,6 +3,12 @@
 
 namespace nb {
 static thread_local cudaError_t g_last_error = cudaSuccess;
+static thread_local const char* g_detail = "";
+// one static string saying which check of a launcher refused the call (read by nb_last_error_detail)
+int fail_with(int status, const char* detail) {
+    g_detail = detail;
+    return status;
+}
 int record_cuda_error(cudaError_t e) {
     g_last_error = e;
     (void)cudaGetLastError();  // clear the sticky-less error so the next launch starts clean
@@ -27,7 +33,12 @@ extern "C" int nb_last_cuda_error(void) {
     return e;
 }
 extern "C" const char* nb_last_cuda_error_string(void) { return cudaGetErrorString(nb::g_last_error); }
-extern "C" int nb_version(void) { return 100; }
+extern "C" const char* nb_last_error_detail(void) {
+    const char* d = nb::g_detail;
+    nb::g_detail = "";
+    return d;
+}
+extern "C" int nb_version(void) { return 101; }
 extern "C" int nb_num_sms(void) {
     int dev = 0, n = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return -1;

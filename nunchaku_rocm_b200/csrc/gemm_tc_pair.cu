@@ -13,13 +13,13 @@
 // loads into its own shared memory; warp 1 of the second CTA relays "my stage has landed" to the first CTA, whose warp 1
 // issues the MMAs for both; tcgen05.commit signals the barriers of both CTAs.
 //
-// Roles (576 threads per CTA):
+// Roles (640 threads per CTA; warps 2 and 3 only exist to complete the control warp group):
 //   warp 0     TMA producer: per ring stage (two K groups) this CTA's A rows and W rows (128 x 128 B each, 128-byte
 //              swizzle) and the two groups' scale rows; low-rank chunks of 32 ranks travel through the same ring.
 //   warp 1     first CTA: MMA issuer, per K group two 256 x 256 x 32 MMAs into one of TWO 256-column accumulator slots and
 //              one commit ("slot full", both CTAs); after the last group the low-rank product (kind::f16) goes into the next
 //              slot like one more group.  Second CTA: relay.
-//   warps 2-17 drain: sixteen warps = four per scheduler, so that the tensor-memory load of one warp (the longest latency
+//   warps 4-19 drain: sixteen warps = four per scheduler, so that the tensor-memory load of one warp (the longest latency
 //              in the loop) hides behind the arithmetic of the other three.  A warp owns 32 rows x 64 columns = 64 fp32
 //              accumulators per thread and reads a group's sums in four chunks (tcgen05.ld.16x256b.x4: 16 lanes x 32 columns,
 //              16 registers): t = p * as (packed multiply), acc = fma(t, ws, acc) (packed FMA).  Scales sit in shared
@@ -46,7 +46,13 @@ constexpr int BN = 256;   // columns per pair tile; each CTA keeps 128 of its W 
 constexpr int STAGES = 4;
 constexpr int NSLOT = 2;
 constexpr int DRAIN_WARPS = 16;
-constexpr int NTHREADS = 64 + DRAIN_WARPS * 32;
+constexpr int CTRL_WARPS = 4;   // one warp group: TMA producer, MMA issuer / relay, two idle warps
+constexpr int NTHREADS = (CTRL_WARPS + DRAIN_WARPS) * 32;
+constexpr int LAUNCH_REGS = 96;   // what 640 threads per CTA leave per thread (the compiler's cap under the launch bound)
+constexpr int CTRL_REGS = 24, DRAIN_REGS = 112;
+// setmaxnreg.inc can only take what setmaxnreg.dec has put into the CTA's pool: it blocks until the pool has enough, for ever
+// if it never will.  The control warp group must give back at least what the four drain warp groups ask for.
+static_assert((LAUNCH_REGS - CTRL_REGS) * 128 >= (DRAIN_REGS - LAUNCH_REGS) * DRAIN_WARPS * 32, "register pool of the CTA");
 constexpr int COLS = 64;  // columns one drain warp owns
 constexpr int NJ = COLS / 8;
 
@@ -73,12 +79,13 @@ static_assert(Cfg::STG_WARP >= 32 * 32 * 4 + 0, "the staging tile also holds a w
 enum {  // barrier indices
     B_FULL = 0,                     // TMA: this CTA's half of the stage has landed
     B_PFULL = B_FULL + STAGES,      // (first CTA) the second CTA's half of the stage has landed
-    B_SCDONE = B_PFULL + STAGES,    // one arrival per drain warp: the stage's MMAs are complete and its scales have been read
+    B_SCDONE = B_PFULL + STAGES,    // one arrival per drain warp: an int8 stage's MMAs are complete and its scales have been read
     B_ACC_FULL = B_SCDONE + STAGES, // tcgen05.commit: the slot's group is complete (signalled in both CTAs)
     B_ACC_EMPTY = B_ACC_FULL + NSLOT,// (first CTA) one arrival per drain warp of the pair: the slot has been read out
     B_XCH = B_ACC_EMPTY + NSLOT,    // 8: exchange between the warps that share rows (lane quarter x head)
     B_LX = B_XCH + 8,               // 4: the four column slices of a lane quarter (LoRA-down partial sums)
-    B_COUNT = B_LX + 4
+    B_LRDONE = B_LX + 4,            // tcgen05.commit: the MMAs of a low-rank stage have read its operands (both CTAs)
+    B_COUNT = B_LRDONE + STAGES
 };
 enum { E_PROD = 0x310, E_MMA = 0x330, E_DRAIN = 0x340, E_RELAY = 0x350 };
 
@@ -133,8 +140,20 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster
+// Arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster.  What the arrival publishes is
+// "this warp's tcgen05.ld of the slot have completed", which tcgen05.wait::ld + tcgen05.fence::before_thread_sync order;
+// no generic-memory write is handed over, so the arrival carries no cluster-scope release (that form compiles to a
+// memory barrier which, once per warp and K group, was the largest stall of the kernel).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t local_bar, uint32_t rank) {
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\tmapa.shared::cluster.u32 ra, %0, %1;\n\t"
+        "mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [ra];\n\t}"
+        ::"r"(local_bar), "r"(rank)
+        : "memory");
+}
+// The same with release semantics at cluster scope: the relay's "my half of the stage has landed" precedes reads of this
+// CTA's shared memory by the other SM's tensor core (one thread, once per ring stage).
+__device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t local_bar, uint32_t rank) {
     asm volatile(
         "{\n\t.reg .b32 ra;\n\tmapa.shared::cluster.u32 ra, %0, %1;\n\t"
         "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
@@ -184,10 +203,18 @@ __device__ __forceinline__ void mma_sync_16816(float (&d)[4], const uint32_t (&a
                      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// 18 warps x 112 registers = 63 K of the SM's 64 K registers (a launch bound of 576 threads alone makes the compiler
-// budget for 640 threads, i.e. 96 registers, and spill inside the K loop)
+// Registers are handed out per warp group (128 threads): 640 threads start with 96 registers each, the control warp group
+// gives 72 of them back (setmaxnreg.dec to 24: 9216 registers into the CTA's pool) and the four drain warp groups grow to
+// 112 (setmaxnreg.inc: 8192 registers out of that pool).  (576 threads at 112 registers do not launch: the fifth warp
+// group is charged in full.)  The host refuses to launch if the compiled kernel does not start with exactly 96 registers.
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {  // shared-memory load by 32-bit address: no 64-bit pointer kept live
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
 template <int EPI, typename T, bool DEBUG_P>
-__global__ void __maxnreg__(112)
+__global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                     const __grid_constant__ CUtensorMap tm_as, const __grid_constant__ CUtensorMap tm_ws,
                     const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lu, const Params p) {
@@ -208,6 +235,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             mbar_init(bar(B_FULL + i), 1);
             mbar_init(bar(B_PFULL + i), 1);
             mbar_init(bar(B_SCDONE + i), DRAIN_WARPS);
+            mbar_init(bar(B_LRDONE + i), 1);
         }
         for (int i = 0; i < NSLOT; ++i) {
             mbar_init(bar(B_ACC_FULL + i), 1);
@@ -235,19 +263,31 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int GS = (G + 1) / 2;       // int8 stages per tile (two K groups each)
     const int LCH = (p.R + 31) / 32;  // low-rank stages per tile (32 ranks each)
 
+    if (warp < CTRL_WARPS) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(CTRL_REGS));
     if (warp == 0) {
         // ================================ TMA producer (both CTAs) ================================
         if (lane == 0) {
             tma_prefetch_desc(&tm_a); tma_prefetch_desc(&tm_w); tma_prefetch_desc(&tm_as); tma_prefetch_desc(&tm_ws);
             if (LCH) { tma_prefetch_desc(&tm_la); tma_prefetch_desc(&tm_lu); }
             uint32_t it = 0;
+            // per stage (one bit each): the parity of its int8 fills / low-rank fills so far, and what the last fill was.  An int8
+            // fill is released by the sixteen drain warps (they read its scales after its MMAs have completed), a low-rank
+            // fill by the MMAs' own completion: a rank above 128 needs more stages than the ring has, so those must come
+            // free before the drain has seen the low-rank product.
+            uint32_t n_sc = 0, n_lr = 0, last_lr = 0;
             bool ok = true;
             for (int t = t_begin; t < t_end && ok; ++t) {
                 const int m0 = (t / NT) * (2 * BM) + (int)rank * BM, n0 = (t % NT) * BN;
                 for (int j = 0; j < GS + LCH; ++j, ++it) {
                     const int s = it % STAGES;
-                    // every fill of a stage is released by the sixteen drain warps (after the stage's MMAs have completed)
-                    if (!mbar_wait(bar(B_SCDONE + s), ((it / STAGES) & 1) ^ 1, abort_s, E_PROD | 1, 500)) { ok = false; break; }
+                    if (it >= (uint32_t)STAGES) {
+                        const bool was_lr = (last_lr >> s) & 1u;
+                        const uint32_t n = ((was_lr ? n_lr : n_sc) >> s) & 1u;  // parity of the fills of that kind so far (>= 1 fill)
+                        if (!mbar_wait(bar((was_lr ? B_LRDONE : B_SCDONE) + s), n ^ 1u, abort_s, E_PROD | 1, 500)) { ok = false; break; }
+                    }
+                    if (j < GS) { n_sc ^= 1u << s; last_lr &= ~(1u << s); }
+                    else { n_lr ^= 1u << s; last_lr |= 1u << s; }
                     const uint32_t dst = s_base + C::OFF_ST + s * C::ST_BYTES;
                     if (j < GS) {
                         mbar_expect_tx(bar(B_FULL + s), C::ST_BYTES);
@@ -283,7 +323,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 for (int j = 0; j < GS + LCH; ++j, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(bar(B_FULL + s), (it / STAGES) & 1, abort_s, E_RELAY | 1, 100)) { ok = false; break; }
-                    mbar_arrive_cluster(bar(B_PFULL + s), 0);
+                    mbar_arrive_cluster_release(bar(B_PFULL + s), 0);
                 }
         }
     } else if (warp == 1) {
@@ -329,32 +369,34 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
                         for (int h = 0; h < 2; ++h)
                             mma2_f16(d, desc_sw64(a_addr + h * 32), desc_sw64(w_addr + h * 32), idesc_lr, (c | h) ? 1u : 0u);
+                        tc_commit2(bar(B_LRDONE + s));
                     }
                     if (ok) { tc_commit2(bar(B_ACC_FULL + slot)); ++ait; }
                 }
             }
         }
+    }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(DRAIN_REGS));
         // ================================ drain + epilogue (both CTAs, own 128 rows) ================================
         // tcgen05.ld.16x256b.x4 hands a thread, for one 16-lane block and 32 columns, rows {gid, gid + 8} and the column
         // pairs 8 j + 2 tig + {0, 1}, j = 0..3: register 4 j + 2 rs + e.
-        const int dw = warp - 2;
-        const int q = warp & 3;    // TMEM lane quarter this warp may read (warp id mod 4)
-        const int cq = dw >> 2;    // 64-column slice of the tile
-        const int pw = cq * 4 + q; // index of this warp's staging / exchange buffers
+        // (Everything the K loop does not need is computed after it: the loop runs with 64 accumulators, one 16-register
+        // chunk and 12 scale registers out of 112, and a spill inside it costs more than any of this arithmetic.)
+        const int q = warp & 3;                    // TMEM lane quarter this warp may read (warp id mod 4)
+        const int cq = (warp - CTRL_WARPS) >> 2;   // 64-column slice of the tile
         const int gid = lane >> 2, tig = lane & 3;
-        uint8_t* stg = smem + C::OFF_STG + pw * C::STG_WARP;
-        float* xch = reinterpret_cast<float*>(smem + C::OFF_XCH);
         const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16) + cq * COLS;
-        const int m_cta = (int)rank * BM;
+        // byte offsets of this thread's scales inside a stage's scale block: row-scale entry (quarter, lane block 0, gid),
+        // column-scale entry (slice, half 0, tig)
+        const uint32_t sc_off = s_base + C::OFF_ST + C::ST_A + C::ST_W;
+        const uint32_t as_off = (q * 16 + gid) * 16, ws_off = C::ST_AS + (cq * 8 + tig) * 32;
         uint32_t it = 0, ait = 0, xph = 0, lxph = 0;
         bool ok = true;
         // acc[(lb * NJ + jx) * 2 + rs]: rows q*32 + lb*16 + rs*8 + gid, columns cq*64 + 8 jx + 2 tig + {0, 1}
         uint64_t acc[2 * NJ * 2];
 
         for (int t = t_begin; t < t_end && ok; ++t) {
-            const int m0 = (t / NT) * (2 * BM) + m_cta, n0 = (t % NT) * BN;
-            const int nc0 = n0 + cq * COLS;  // first global column of this warp
 #pragma unroll
             for (int i = 0; i < 2 * NJ * 2; ++i) acc[i] = 0ull;
             for (int g = 0; g < G; ++g, ++ait) {
@@ -362,19 +404,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 const int s = (it + (g >> 1)) % STAGES, i = g & 1;
                 if (!mbar_wait_warp(bar(B_ACC_FULL + slot), (ait >> 1) & 1, abort_s, E_DRAIN | 1, 100)) { ok = false; break; }
                 tc_fence_after();
-                const uint8_t* st = smem + C::OFF_ST + s * C::ST_BYTES + C::ST_A + C::ST_W;
-                const uint4* as_s = reinterpret_cast<const uint4*>(st + i * (BM * 8) + (q * 2 * 8 + gid) * 16);
-                const uint4* ws_s = reinterpret_cast<const uint4*>(st + C::ST_AS + i * (BN * 4) + ((cq * 2) * 4 + tig) * 32);
+                const uint32_t st = sc_off + s * C::ST_BYTES + i * 1024;  // both scale blocks keep 1 KB per group
                 const uint32_t taddr = lane_base + slot * BN;
 #pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
-                    const uint4 w0 = ws_s[ch * 8], w1 = ws_s[ch * 8 + 1];  // (ch * 4 tig-entries of 32 B) / 16
+                    const uint4 w0 = lds128(st + ws_off + ch * 128), w1 = lds128(st + ws_off + ch * 128 + 16);
                     const uint64_t wp[4] = {pack_u32x2(w0.x, w0.y), pack_u32x2(w0.z, w0.w), pack_u32x2(w1.x, w1.y), pack_u32x2(w1.z, w1.w)};
 #pragma unroll
                     for (int lb = 0; lb < 2; ++lb) {
                         uint32_t v[16];
                         tmem_ld_16x256b_x4(taddr + ((uint32_t)(lb * 16) << 16) + ch * 32, v);
-                        const uint4 a4 = as_s[lb * 8];
+                        const uint4 a4 = lds128(st + as_off + lb * 128);
                         const uint64_t ap[2] = {pack_u32x2(a4.x, a4.y), pack_u32x2(a4.z, a4.w)};
                         tmem_wait_ld();
                         if (ch == 1 && lb == 1) {
@@ -399,8 +439,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         if (DEBUG_P) {
 #pragma unroll
                             for (int e = 0; e < 16; ++e) {
-                                const int m = m0 + q * 32 + lb * 16 + ((e >> 1) & 1) * 8 + gid;
-                                const int n = nc0 + ch * 32 + (e >> 2) * 8 + 2 * tig + (e & 1);
+                                const int m = (t / NT) * (2 * BM) + (int)rank * BM + q * 32 + lb * 16 + ((e >> 1) & 1) * 8 + gid;
+                                const int n = (t % NT) * BN + cq * COLS + ch * 32 + (e >> 2) * 8 + 2 * tig + (e & 1);
                                 if (m < p.M && n < p.N)
                                     p.p_out[((long long)g * p.M + m) * p.N + n] = (int)__uint_as_float(v[e]);
                             }
@@ -426,10 +466,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         if (ch == 1 && lb == 1) {
                             tc_fence_before();
                             __syncwarp();
-                            if (lane == 0) {
-                                mbar_arrive_cluster(bar(B_ACC_EMPTY + slot), 0);
-                                for (int c = 0; c < LCH; ++c) mbar_arrive(bar(B_SCDONE + (it + c) % STAGES));
-                            }
+                            if (lane == 0) mbar_arrive_cluster(bar(B_ACC_EMPTY + slot), 0);
                         }
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
@@ -445,6 +482,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
             // ---------------- epilogue ----------------
             // element (lb, j, rs, e): row q*32 + lb*16 + rs*8 + gid, column nc0 + 8 j + 2 tig + e
+            const int m0 = (t / NT) * (2 * BM) + (int)rank * BM, n0 = (t % NT) * BN;
+            const int nc0 = n0 + cq * COLS;                   // first global column of this warp
+            const int pw = cq * 4 + q;                        // index of this warp's staging / exchange buffers
+            uint8_t* stg = smem + C::OFF_STG + pw * C::STG_WARP;
+            float* xch = reinterpret_cast<float*>(smem + C::OFF_XCH);
             const int head = cq >> 1;                         // 128-column half of the tile
             const int hc0 = (cq & 1) * COLS;                  // this warp's first column inside its head
             const int qk_part = EPI == NB_EPI_QK_NORM_ROPE ? (n0 + head * 128) / (p.N / 3) : 2;
@@ -532,22 +574,48 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 __syncwarp();
             }
 
-            if (EPI == NB_EPI_GELU_QUANT) {
-                // x = gelu(acc); LoRA-down from T(x) (before shift and smoothing); v = (x + shift) / smooth; per row and
-                // 64-column group (= this warp's columns): scale = max(max v, 0) / 15, code = clamp(rint(v / scale), 0, 15)
+            if (EPI == NB_EPI_GELU_QUANT || EPI == NB_EPI_SWIGLU_QUANT) {
+                // GELU:   x = gelu(acc) on all N columns; unsigned codes, the 64-column group is this warp's slice.
+                // SwiGLU: columns come in blocks of 32 = 16 gate + 16 up (the layer's rows were interleaved at load time);
+                //         y = silu(gate) * up gives N / 2 output columns, 32 per warp; signed codes, a 64-column output
+                //         group spans this warp and its neighbour slice.
+                // Both: LoRA-down from T(x) before shift and smoothing; v = (x + shift) / smooth; scale = max / qmax from the
+                // unrounded maximum, stored rounded; code = clamp(rint(v * (1 / scale))).
+                constexpr bool SWI = EPI == NB_EPI_SWIGLU_QUANT;
+                constexpr int KSTEPS = SWI ? 2 : 4;      // 16 output columns per mma k step
+                const int Nq = SWI ? p.N / 2 : p.N;
+                const int oc0 = SWI ? nc0 / 2 : nc0;     // this warp's first output column
+                if (SWI) {
+                    // gate block j = 4 b + jj (jj < 2) and up block j + 2 hold the same (tig, e) positions: thread-local
 #pragma unroll
-                for (int i = 0; i < 2 * NJ * 2; ++i) {
-                    const float2 a = unpack_f32x2(acc[i]);
-                    acc[i] = pack_f32x2(gelu_tanh(a.x), gelu_tanh(a.y));
+                    for (int lb = 0; lb < 2; ++lb)
+#pragma unroll
+                        for (int b = 0; b < 2; ++b)
+#pragma unroll
+                            for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+                                for (int rs = 0; rs < 2; ++rs) {
+                                    const float2 g2 = unpack_f32x2(acc[(lb * NJ + 4 * b + jj) * 2 + rs]);
+                                    const float2 u2 = unpack_f32x2(acc[(lb * NJ + 4 * b + jj + 2) * 2 + rs]);
+                                    acc[(lb * NJ + 4 * b + jj) * 2 + rs] = pack_f32x2(silu(g2.x) * u2.x, silu(g2.y) * u2.y);
+                                }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 2 * NJ * 2; ++i) {
+                        const float2 a = unpack_f32x2(acc[i]);
+                        acc[i] = pack_f32x2(gelu_tanh(a.x), gelu_tanh(a.y));
+                    }
                 }
+                // accumulator index of output k-step kk, half h (columns 16 kk + 8 h + 2 tig + {0, 1} of this warp's outputs)
+                auto xi = [](int lb, int kk, int h, int rs) { return SWI ? (lb * NJ + 4 * kk + h) * 2 + rs : (lb * NJ + 2 * kk + h) * 2 + rs; };
                 const bool have_lora = p.lora_down_t != nullptr && p.R2 > 0;
                 if (have_lora) {
                     // Two adjacent 8-column blocks of the accumulator fragment ARE the A fragment of mma.m16n8k16 (rows gid,
                     // gid + 8; k = 2 tig + {0, 1} and + 8), so the activated values go to the tensor cores without leaving the
                     // registers.  B comes from the transposed lora_down: rank gid, columns k .. k + 1 are one 32-bit load.
-                    // R2 is handled in slabs of 32 ranks; a slab's 32 x 32 partial of this warp's 64 columns goes through the
-                    // staging tile to the cq = 0 warp of the lane quarter, which adds the four slices in slice order and
-                    // stores the tile's partial sum (the column tiles are added up in tile order by a second kernel).
+                    // R2 is handled in slabs of 32 ranks; a slab's 32 x 32 partial of this warp's columns goes through the
+                    // staging tile to the first slice's warp of the lane quarter, which adds the four slices in slice order
+                    // and stores the tile's partial sum (the column tiles are added up in tile order by a second kernel).
                     const T* ldt = static_cast<const T*>(p.lora_down_t);
                     float* part = p.lora_part + ((long long)(n0 / BN) * p.M) * p.R2;
                     for (int r0 = 0; r0 < p.R2; r0 += 32) {
@@ -559,24 +627,24 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) c[lb][nb][e] = 0.f;
 #pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {  // 16 columns per step
+                        for (int kk = 0; kk < KSTEPS; ++kk) {
                             uint32_t a[2][4];
 #pragma unroll
                             for (int lb = 0; lb < 2; ++lb) {
-                                const float2 x00 = unpack_f32x2(acc[(lb * NJ + 2 * kk) * 2 + 0]), x10 = unpack_f32x2(acc[(lb * NJ + 2 * kk) * 2 + 1]);
-                                const float2 x01 = unpack_f32x2(acc[(lb * NJ + 2 * kk + 1) * 2 + 0]), x11 = unpack_f32x2(acc[(lb * NJ + 2 * kk + 1) * 2 + 1]);
+                                const float2 x00 = unpack_f32x2(acc[xi(lb, kk, 0, 0)]), x10 = unpack_f32x2(acc[xi(lb, kk, 0, 1)]);
+                                const float2 x01 = unpack_f32x2(acc[xi(lb, kk, 1, 0)]), x11 = unpack_f32x2(acc[xi(lb, kk, 1, 1)]);
                                 a[lb][0] = pack2<T>(x00.x, x00.y); a[lb][1] = pack2<T>(x10.x, x10.y);
                                 a[lb][2] = pack2<T>(x01.x, x01.y); a[lb][3] = pack2<T>(x11.x, x11.y);
                             }
 #pragma unroll
                             for (int nb = 0; nb < 4; ++nb) {
                                 const int r = r0 + nb * 8 + gid;
-                                const int col = nc0 + kk * 16 + 2 * tig;
+                                const int col = oc0 + kk * 16 + 2 * tig;
                                 uint32_t b0 = 0u, b1 = 0u;
                                 if (r < p.R2) {
-                                    const T* bp = ldt + (long long)r * p.N + col;
-                                    if (col < p.N) b0 = __ldg(reinterpret_cast<const uint32_t*>(bp));
-                                    if (col + 8 < p.N) b1 = __ldg(reinterpret_cast<const uint32_t*>(bp + 8));
+                                    const T* bp = ldt + (long long)r * Nq + col;
+                                    if (col < Nq) b0 = __ldg(reinterpret_cast<const uint32_t*>(bp));
+                                    if (col + 8 < Nq) b1 = __ldg(reinterpret_cast<const uint32_t*>(bp + 8));
                                 }
                                 mma_sync_16816<T>(c[0][nb], a[0], b0, b1);
                                 mma_sync_16816<T>(c[1][nb], a[1], b0, b1);
@@ -611,7 +679,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                                 if (m < p.M && rr < p.R2) *reinterpret_cast<float4*>(part + (long long)m * p.R2 + rr) = sum;
                             }
                         }
-                        // the staging tiles are rewritten (next slab, or the codes below) only after the cq = 0 warp has read them
+                        // the staging tiles are rewritten (next slab, or the codes below) only after the first slice's warp has read them
                         __syncwarp();
                         if (lane == 0) mbar_arrive(bar(B_LX + q));
                         if (!mbar_wait_warp(bar(B_LX + q), lxph & 1, abort_s, E_DRAIN | 6, 100)) { ok = false; break; }
@@ -619,52 +687,76 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     }
                     if (!ok) break;
                 }
-                // quantise
-                const int grp = nc0 / 64;
-                float isw[NJ][2];
+                // ---- quantise: NH output 8-column blocks per (16-lane block, row select)
+                constexpr int NH = SWI ? 4 : 8;
+                float isw[NH][2];
 #pragma unroll
-                for (int j = 0; j < NJ; ++j) {
-                    const int col = nc0 + 8 * j + 2 * tig;
+                for (int h = 0; h < NH; ++h) {
+                    const int col = oc0 + 8 * h + 2 * tig;
                     float2 is = make_float2(1.f, 1.f);
-                    if (p.inv_smooth && col < p.N) is = __ldg(reinterpret_cast<const float2*>(p.inv_smooth + col));
-                    isw[j][0] = is.x; isw[j][1] = is.y;
+                    if (p.inv_smooth && col < Nq) is = __ldg(reinterpret_cast<const float2*>(p.inv_smooth + col));
+                    isw[h][0] = is.x; isw[h][1] = is.y;
                 }
-                __syncwarp();
+                float vv[4][NH][2], mx[4];
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     const int lb = r >> 1, rs = r & 1;
-                    float vv[NJ][2];
-                    float mx = 0.f;  // max(max v, 0)
+                    mx[r] = 0.f;
 #pragma unroll
-                    for (int j = 0; j < NJ; ++j) {
-                        const float2 a = unpack_f32x2(acc[(lb * NJ + j) * 2 + rs]);
-                        vv[j][0] = __fmul_rn(__fadd_rn(a.x, p.shift), isw[j][0]);
-                        vv[j][1] = __fmul_rn(__fadd_rn(a.y, p.shift), isw[j][1]);
-                        mx = fmaxf(mx, fmaxf(vv[j][0], vv[j][1]));
+                    for (int h = 0; h < NH; ++h) {
+                        const float2 a = unpack_f32x2(acc[SWI ? (lb * NJ + 4 * (h >> 1) + (h & 1)) * 2 + rs : (lb * NJ + h) * 2 + rs]);
+                        vv[r][h][0] = __fmul_rn(__fadd_rn(a.x, p.shift), isw[h][0]);
+                        vv[r][h][1] = __fmul_rn(__fadd_rn(a.y, p.shift), isw[h][1]);
+                        mx[r] = SWI ? fmaxf(mx[r], fmaxf(fabsf(vv[r][h][0]), fabsf(vv[r][h][1])))
+                                    : fmaxf(mx[r], fmaxf(vv[r][h][0], vv[r][h][1]));
                     }
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                    const float scale = __fdiv_rn(mx, 15.0f);
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                }
+                if (SWI) {
+                    // the 64-column output group is shared with the neighbour slice: exchange the row maxima
+                    float* xb = xch + (xph & 1) * (DRAIN_WARPS * 32);
+#pragma unroll
+                    for (int r = 0; r < 4; ++r)
+                        if (tig == 0) xb[pw * 32 + r * 8 + gid] = mx[r];
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(B_XCH + q * 2 + head));
+                    if (!mbar_wait_warp(bar(B_XCH + q * 2 + head), xph & 1, abort_s, E_DRAIN | 7, 100)) { ok = false; break; }
+#pragma unroll
+                    for (int r = 0; r < 4; ++r)
+                        mx[r] = fmaxf(xb[((head * 2) * 4 + q) * 32 + r * 8 + gid], xb[((head * 2 + 1) * 4 + q) * 32 + r * 8 + gid]);
+                    ++xph;
+                }
+                const float qmax = SWI ? 7.0f : 15.0f, qlo = SWI ? -8.0f : 0.0f;
+                const int grp = oc0 / 64;
+                constexpr int RB = SWI ? 16 : 32;   // code bytes per row of this warp
+                constexpr int RP = RB + 16;         // staging pitch
+                __syncwarp();
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const float scale = __fdiv_rn(mx[r], qmax);
                     const float inv = __fdiv_rn(1.0f, scale == 0.f ? 1.0f : scale);
                     const int m = m0 + q * 32 + r * 8 + gid;
-                    if (tig == 0 && m < p.M && nc0 < p.N)
+                    if (tig == 0 && m < p.M && oc0 < Nq && (!SWI || (cq & 1) == 0))
                         static_cast<T*>(p.oscales)[(long long)grp * p.stride_osg + m] = from_f32<T>(scale);
 #pragma unroll
-                    for (int j = 0; j < NJ; ++j) {
-                        const int q0 = (int)fminf(fmaxf(rint_small(__fmul_rn(vv[j][0], inv)), 0.f), 15.f);
-                        const int q1 = (int)fminf(fmaxf(rint_small(__fmul_rn(vv[j][1], inv)), 0.f), 15.f);
-                        stg[(r * 8 + gid) * 48 + 4 * j + tig] = (uint8_t)(q0 | (q1 << 4));
+                    for (int h = 0; h < NH; ++h) {
+                        const int q0 = (int)fminf(fmaxf(rint_small(__fmul_rn(vv[r][h][0], inv)), qlo), qmax);
+                        const int q1 = (int)fminf(fmaxf(rint_small(__fmul_rn(vv[r][h][1], inv)), qlo), qmax);
+                        stg[(r * 8 + gid) * RP + 4 * h + tig] = (uint8_t)((q0 & 0xF) | ((q1 & 0xF) << 4));
                     }
                 }
                 __syncwarp();
                 {
-                    // 32 rows x 32 bytes: two 16-byte units per row
-                    const int rr = lane, mm = m0 + q * 32 + rr;
+                    // 32 rows x RB bytes in 16-byte units
+                    constexpr int UPR = RB / 16;
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * 48 + u * 16);
-                        if (mm < p.M && nc0 + u * 32 < p.N)
-                            *reinterpret_cast<uint4*>(p.qout + (long long)mm * p.stride_qm + nc0 / 2 + u * 16) = o;
+                    for (int u0 = 0; u0 < 32 * UPR; u0 += 32) {
+                        const int idx = u0 + lane, rr = idx / UPR, u = idx % UPR;
+                        const int mm = m0 + q * 32 + rr;
+                        const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * RP + u * 16);
+                        if (mm < p.M && oc0 + u * 32 < Nq)
+                            *reinterpret_cast<uint4*>(p.qout + (long long)mm * p.stride_qm + oc0 / 2 + u * 16) = o;
                     }
                 }
                 __syncwarp();
@@ -828,7 +920,7 @@ static Scratch scratch_layout(const nb_gemm_args* a, const void* epi, int epi_ki
     s.a8 = off; off += up256((size_t)a->M * a->K);
     s.asf = off; off += up256(G * s.Mp * 2 * 4);
     s.la16 = off; off += up256((size_t)a->M * a->R * 2);
-    if (epi_kind == NB_EPI_GELU_QUANT) {
+    if (epi_kind == NB_EPI_GELU_QUANT || epi_kind == NB_EPI_SWIGLU_QUANT) {
         const nb_requant_args* q = static_cast<const nb_requant_args*>(epi);
         const size_t R2 = (q->lora_down && q->lora_act_out) ? q->R2 : 0;
         s.inv_smooth = off; off += up256((size_t)a->N * 4);
@@ -873,7 +965,11 @@ static int max_pairs(K kern, int dev) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess) { (void)cudaGetLastError(); clusters = 0; }
+    if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess) {
+        // the query is advisory: without it the grid is one pair per two SMs and the launch itself reports a misfit
+        (void)cudaGetLastError();
+        clusters = sms / 2;
+    }
     if (clusters > sms / 2) clusters = sms / 2;
     if (dev >= 0 && dev < 64) cache[dev] = clusters;
     return clusters;
@@ -884,7 +980,7 @@ static int launch_t(const nb_gemm_args* a, const void* epi, Params p, cudaStream
     using C = Cfg;
     const Scratch sc = scratch_layout(a, epi, EPI);
     if (!a->scratch || a->scratch_bytes < (int64_t)sc.total || (reinterpret_cast<uintptr_t>(a->scratch) & 255))
-        return NB_ERR_INVALID;
+        return fail_with(NB_ERR_INVALID, "pair kernel: scratch missing, too small or not 256-byte aligned");
     uint8_t* base = static_cast<uint8_t*>(a->scratch);
     const bool prepared = has_prepared_weights(a);
     const PreparedLayout pl = prepared_layout(a->N, a->K);
@@ -904,16 +1000,17 @@ static int launch_t(const nb_gemm_args* a, const void* epi, Params p, cudaStream
         const int st = launch_prepack<T>(pp, s);
         if (st != NB_OK) return st;
     }
-    if (EPI == NB_EPI_GELU_QUANT) {
+    if (EPI == NB_EPI_GELU_QUANT || EPI == NB_EPI_SWIGLU_QUANT) {
         const nb_requant_args* q = static_cast<const nb_requant_args*>(epi);
         const bool lora = q->lora_down && q->lora_act_out && q->R2 > 0;
+        const int Nq = EPI == NB_EPI_SWIGLU_QUANT ? a->N / 2 : a->N;  // re-quantised columns
         p.inv_smooth = reinterpret_cast<const float*>(base + sc.inv_smooth);
         p.lora_down_t = lora ? base + sc.ldt : nullptr;
         p.lora_part = lora ? reinterpret_cast<float*>(base + sc.lora_part) : nullptr;
         p.R2 = lora ? q->R2 : 0;
-        const long long units = (long long)a->N * (lora ? q->R2 : 1);
+        const long long units = (long long)Nq * (lora ? q->R2 : 1);
         prepack_requant_kernel<T><<<(unsigned)((units + 255) / 256), 256, 0, s>>>(
-            static_cast<const T*>(q->smooth), lora ? static_cast<const T*>(q->lora_down) : nullptr, q->stride_ld, a->N,
+            static_cast<const T*>(q->smooth), lora ? static_cast<const T*>(q->lora_down) : nullptr, q->stride_ld, Nq,
             lora ? q->R2 : 0, reinterpret_cast<float*>(base + sc.inv_smooth), reinterpret_cast<T*>(base + sc.ldt));
         NB_CUDA_CHECK(cudaGetLastError());
     }
@@ -932,7 +1029,7 @@ static int launch_t(const nb_gemm_args* a, const void* epi, Params p, cudaStream
         ok = make_map(&tm_la, t16, pp.la16, a->R, a->M, (uint64_t)a->R * 2, 32, BM, CU_TENSOR_MAP_SWIZZLE_64B) &&
              make_map(&tm_lu, t16, a->lora_up, a->R, a->N, (uint64_t)a->stride_lun * 2, 32, 128, CU_TENSOR_MAP_SWIZZLE_64B);
     else if (ok) { tm_la = tm_a; tm_lu = tm_w; }
-    if (!ok) return NB_ERR_UNSUPPORTED;
+    if (!ok) return fail_with(NB_ERR_UNSUPPORTED, "pair kernel: a tensor map could not be encoded");
 
     auto kern = gemm_tc_pair_kernel<EPI, T, DEBUG_P>;
     static bool attr_set[64] = {};  // per instantiation and device: the attribute lives in the device's module
@@ -942,8 +1039,20 @@ static int launch_t(const nb_gemm_args* a, const void* epi, Params p, cudaStream
         NB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
+    {
+        // the register hand-over inside the kernel is balanced for a launch allocation of LAUNCH_REGS per thread
+        static int regs[64] = {};
+        if (dev < 0 || dev >= 64 || !regs[dev]) {
+            cudaFuncAttributes fa;
+            NB_CUDA_CHECK(cudaFuncGetAttributes(&fa, kern));
+            if (dev >= 0 && dev < 64) regs[dev] = fa.numRegs;
+            if (fa.numRegs != LAUNCH_REGS) return fail_with(NB_ERR_UNSUPPORTED, "pair kernel: unexpected register allocation");
+        } else if (regs[dev] != LAUNCH_REGS) {
+            return fail_with(NB_ERR_UNSUPPORTED, "pair kernel: unexpected register allocation");
+        }
+    }
     const int limit = max_pairs(kern, dev);
-    if (limit < 1) return NB_ERR_UNSUPPORTED;
+    if (limit < 1) return fail_with(NB_ERR_UNSUPPORTED, "pair kernel: no CTA pair fits on this device");
     const int total = ((a->M + 2 * BM - 1) / (2 * BM)) * ((a->N + BN - 1) / BN);
     const int pairs = total < limit ? total : limit;
     cudaLaunchConfig_t cfg = {};
@@ -957,7 +1066,7 @@ static int launch_t(const nb_gemm_args* a, const void* epi, Params p, cudaStream
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     NB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tm_a, tm_w, tm_as, tm_ws, tm_la, tm_lu, p));
-    if (EPI == NB_EPI_GELU_QUANT && p.R2 > 0) {
+    if ((EPI == NB_EPI_GELU_QUANT || EPI == NB_EPI_SWIGLU_QUANT) && p.R2 > 0) {
         const nb_requant_args* q = static_cast<const nb_requant_args*>(epi);
         const long long n = (long long)a->M * p.R2;
         lora_part_sum_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(p.lora_part, sc.Np / BN, a->M, p.R2, q->lora_act_out,
@@ -973,11 +1082,13 @@ static int launch_t(const nb_gemm_args* a, const void* epi, Params p, cudaStream
 const char* tcp_unsupported_reason(const nb_gemm_args* a, const void* epi, int epi_kind) {
     if (a->fp4) return "NVFP4 (handled by the block-scaled kernel)";
     if (a->wcscales || a->alpha != 1.0f || a->fuse_silu) return "wcscales / alpha / SiLU";
-    if (epi_kind != NB_EPI_STORE && epi_kind != NB_EPI_QK_NORM_ROPE && epi_kind != NB_EPI_GELU_QUANT) return "epilogue";
+    const bool requant = epi_kind == NB_EPI_GELU_QUANT || epi_kind == NB_EPI_SWIGLU_QUANT;
+    if (epi_kind != NB_EPI_STORE && epi_kind != NB_EPI_QK_NORM_ROPE && !requant) return "epilogue";
     if (a->K % 64 || a->N % 8 || a->M < 1) return "K % 64, N % 8";
     if (!aligned16(a->act) || !aligned16(a->wgt) || a->stride_am % 16 || a->stride_wn % 16) return "act / wgt alignment";
     if (a->out && (!aligned16(a->out) || a->stride_om % 8)) return "out alignment";
-    if (!a->out && epi_kind != NB_EPI_GELU_QUANT) return "no 16-bit output";
+    if (!a->out && !requant) return "no 16-bit output";
+    if (a->out && epi_kind == NB_EPI_SWIGLU_QUANT) return "SwiGLU writes no 16-bit tile";
     if (a->bias && (reinterpret_cast<uintptr_t>(a->bias) & 3)) return "bias alignment";
     if (a->R > 0) {
         if (a->R % 16 || !a->lora_act || !a->lora_up) return "rank";
@@ -990,14 +1101,45 @@ const char* tcp_unsupported_reason(const nb_gemm_args* a, const void* epi, int e
             (reinterpret_cast<uintptr_t>(q->rot) & 7) || q->stride_rm % 2)
             return "QK alignment";
     }
-    if (epi_kind == NB_EPI_GELU_QUANT) {
+    if (requant) {
         const nb_requant_args* q = static_cast<const nb_requant_args*>(epi);
-        if (a->N % 64) return "N % 64 (re-quantisation groups)";
+        if (a->N % (epi_kind == NB_EPI_SWIGLU_QUANT ? 128 : 64)) return "N % 64 (re-quantisation groups)";
         if (!aligned16(q->qout) || q->stride_qm % 16) return "qout alignment";
         if (q->lora_down && q->lora_act_out && (q->R2 % 16 || q->R2 < 16 || !aligned16(q->lora_act_out) || q->stride_lom % 4))
             return "LoRA-down rank / alignment";
     }
     return nullptr;
+}
+
+// Resource figures of the plain-store instantiation as the runtime sees them on the current device:
+// {registers per thread, max threads per block, static shared bytes, occupancy query's cluster count, its error code,
+//  dynamic shared bytes asked for, threads per block}
+int tcp_kernel_info(int* out) {
+    auto kern = tcp::gemm_tc_pair_kernel<NB_EPI_STORE, __nv_bfloat16, false>;
+    cudaFuncAttributes fa;
+    NB_CUDA_CHECK(cudaFuncGetAttributes(&fa, kern));
+    NB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tcp::Cfg::SMEM_BYTES));
+    int dev = 0, sms = 0;
+    NB_CUDA_CHECK(cudaGetDevice(&dev));
+    NB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sms / 2 * 2);
+    cfg.blockDim = dim3(tcp::NTHREADS);
+    cfg.dynamicSmemBytes = tcp::Cfg::SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = -1;
+    const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg);
+    (void)cudaGetLastError();
+    int blocks = -1;
+    const cudaError_t e2 = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kern, tcp::NTHREADS, tcp::Cfg::SMEM_BYTES);
+    (void)cudaGetLastError();
+    out[0] = fa.numRegs; out[1] = fa.maxThreadsPerBlock; out[2] = (int)fa.sharedSizeBytes; out[3] = clusters; out[4] = (int)e;
+    out[5] = tcp::Cfg::SMEM_BYTES; out[6] = tcp::NTHREADS; out[7] = blocks; out[8] = (int)e2; out[9] = (int)fa.localSizeBytes;
+    return NB_OK;
 }
 
 int64_t tcp_scratch_bytes(const nb_gemm_args* a, const void* epi, int epi_kind) {
@@ -1027,7 +1169,7 @@ int launch_tc_pair(const nb_gemm_args* a, const void* epi, int epi_kind, int32_t
         p.norm_q = q->norm_q; p.norm_k = q->norm_k; p.rot = q->rot; p.stride_rm = q->stride_rm;
         p.rot_rows = q->rot_rows; p.eps = q->eps;
     }
-    if (epi_kind == NB_EPI_GELU_QUANT) {
+    if (epi_kind == NB_EPI_GELU_QUANT || epi_kind == NB_EPI_SWIGLU_QUANT) {
         const nb_requant_args* q = static_cast<const nb_requant_args*>(epi);
         p.qout = static_cast<uint8_t*>(q->qout); p.oscales = q->oscales; p.shift = q->shift;
         p.stride_qm = q->stride_qm; p.stride_osg = q->stride_osg;
@@ -1041,6 +1183,9 @@ int launch_tc_pair(const nb_gemm_args* a, const void* epi, int epi_kind, int32_t
     if (epi_kind == NB_EPI_GELU_QUANT)
         return bf ? tcp::launch_t<NB_EPI_GELU_QUANT, __nv_bfloat16, false>(a, epi, p, s)
                   : tcp::launch_t<NB_EPI_GELU_QUANT, __half, false>(a, epi, p, s);
+    if (epi_kind == NB_EPI_SWIGLU_QUANT)
+        return bf ? tcp::launch_t<NB_EPI_SWIGLU_QUANT, __nv_bfloat16, false>(a, epi, p, s)
+                  : tcp::launch_t<NB_EPI_SWIGLU_QUANT, __half, false>(a, epi, p, s);
     return bf ? tcp::launch_t<NB_EPI_STORE, __nv_bfloat16, false>(a, epi, p, s) : tcp::launch_t<NB_EPI_STORE, __half, false>(a, epi, p, s);
 }
 

@@ -151,6 +151,10 @@ extern "C" int nb_gemm_w4a4(const nb_gemm_args* a, const void* epi, int epi_kind
                                static_cast<const nb_requant_args*>(epi), s);
 }
 
+namespace nb { int tcp_kernel_info(int* out); }
+// Diagnostics: how the CTA-pair kernel fits the current device (registers, threads, shared memory, resident pairs).
+extern "C" int nb_debug_pair_kernel_info(int* out10) { return out10 ? nb::tcp_kernel_info(out10) : NB_ERR_INVALID; }
+
 extern "C" int64_t nb_gemm_w4a4_prepared_bytes(const nb_gemm_args* a) { return nb::tc_prepared_bytes(a); }
 
 extern "C" int nb_gemm_w4a4_prepare_weights(const nb_gemm_args* a, void* dst, int64_t dst_bytes, void* stream) {

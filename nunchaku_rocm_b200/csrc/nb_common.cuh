@@ -16,6 +16,7 @@ namespace nb {
 // host-side launch bookkeeping
 // --------------------------------------------------------------------------------------------
 int record_cuda_error(cudaError_t e);  // stores e, returns NB_ERR_LAUNCH (api.cu)
+int fail_with(int status, const char* detail);  // stores a one-line reason for nb_last_error_detail, returns status
 
 #define NB_CUDA_CHECK(expr)                                     \
     do {                                                        \

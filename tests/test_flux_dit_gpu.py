@@ -148,3 +148,89 @@ def test_full_model_forward_is_finite_and_graph_replay_is_deterministic(cuda_dev
     assert torch.equal(out, again) and torch.equal(out, eager)
     x = denoise(step, step.latents.clone(), num_steps=2)
     assert torch.isfinite(x.float()).all()
+
+
+# ------------------------------------------------------------------------------------------------
+# Qwen-Image-architecture block (NVFP4): nunchaku/models/transformers/transformer_qwenimage.py:220-309
+# ------------------------------------------------------------------------------------------------
+def _fp4_params(lin):
+    p = {k: getattr(lin, k).detach().cpu() for k in ("qweight", "wscales", "bias", "smooth_factor", "proj_down", "proj_up", "wcscales")}
+    p["alpha"] = lin.wtscale
+    return p
+
+
+def _o_linear_fp4(x, lin):
+    p = _fp4_params(lin)
+    q, s, l, _ = w4a4.quantize_act(x, p["proj_down"], p["smooth_factor"], fp4=True)
+    return w4a4.gemm_w4a4(q, p["qweight"].view(torch.uint8), s, p["wscales"], p["bias"], l, p["proj_up"], fp4=True,
+                          alpha=p["alpha"], wcscales=p["wcscales"]).to(T)
+
+
+def _o_gelu_mlp_fp4(x, fc1, fc2):
+    # NVFP4: GEMM -> 16-bit tile -> quantizer with the GELU fused in (gemm_w4a4.py:1298-1312), then fc2
+    p2 = _fp4_params(fc2)
+    h = _o_linear_fp4(x, fc1)
+    q, s, l, _ = w4a4.quantize_act(h, p2["proj_down"], p2["smooth_factor"], fp4=True, fuse_gelu=True)
+    return w4a4.gemm_w4a4(q, p2["qweight"].view(torch.uint8), s, p2["wscales"], p2["bias"], l, p2["proj_up"], fp4=True,
+                          alpha=p2["alpha"], wcscales=p2["wcscales"]).to(T)
+
+
+def _o_qwen_block(blk, h, e, temb, img_f, txt_f):
+    from nunchaku_rocm_b200.models.qwen_dit import _rms, _rotate
+
+    cfg = blk.cfg
+    B, S_img, C = h.shape
+    S_txt = e.shape[1]
+
+    def mod(m):
+        x = _o_awq(F.silu(temb), m.linear)
+        return x.view(B, -1, 6).transpose(1, 2).reshape(B, -1).chunk(2, dim=-1)
+
+    def modulate(x, mp):
+        shift, scale, gate = mp.chunk(3, dim=-1)
+        return x * (scale + 1.0)[:, None] + shift[:, None], gate[:, None]
+
+    im1, im2 = mod(blk.img_mod)
+    tm1, tm2 = mod(blk.txt_mod)
+    img_m, ig1 = modulate(F.layer_norm(h, (C,), eps=1e-6), im1)
+    txt_m, tg1 = modulate(F.layer_norm(e, (C,), eps=1e-6), tm1)
+    iq, ik, iv = (t.unflatten(-1, (cfg.heads, -1)) for t in _o_linear_fp4(img_m.reshape(-1, C), blk.to_qkv).view(B, S_img, -1).chunk(3, dim=-1))
+    tq, tk, tv = (t.unflatten(-1, (cfg.heads, -1)) for t in _o_linear_fp4(txt_m.reshape(-1, C), blk.add_qkv_proj).view(B, S_txt, -1).chunk(3, dim=-1))
+    w = lambda n: getattr(blk, n).detach().cpu()
+    iq, ik = _rotate(_rms(iq, w("norm_q")), img_f), _rotate(_rms(ik, w("norm_k")), img_f)
+    tq, tk = _rotate(_rms(tq, w("norm_added_q")), txt_f), _rotate(_rms(tk, w("norm_added_k")), txt_f)
+    q, k, v = torch.cat([tq, iq], 1), torch.cat([tk, ik], 1), torch.cat([tv, iv], 1)
+    attn = awq_attn.attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), cfg.head_dim**-0.5).to(T)
+    ta = _o_linear_fp4(attn[:, :S_txt].reshape(-1, C), blk.to_add_out).view(B, S_txt, C)
+    ia = _o_linear_fp4(attn[:, S_txt:].reshape(-1, C), blk.to_out).view(B, S_img, C)
+    h = h + ig1 * ia
+    e = e + tg1 * ta
+    m2, g2 = modulate(F.layer_norm(h, (C,), eps=1e-6), im2)
+    h = h + g2 * _o_gelu_mlp_fp4(m2.reshape(-1, C), blk.img_mlp.fc1, blk.img_mlp.fc2).view(B, S_img, C)
+    m2, g2 = modulate(F.layer_norm(e, (C,), eps=1e-6), tm2)
+    e = e + g2 * _o_gelu_mlp_fp4(m2.reshape(-1, C), blk.txt_mlp.fc1, blk.txt_mlp.fc2).view(B, S_txt, C)
+    return e, h
+
+
+def test_qwen_image_block_matches_the_oracle_chain(cuda_dev):
+    from nunchaku_rocm_b200 import _lib
+    from nunchaku_rocm_b200.models.qwen_dit import QwenDiT, QwenDiTConfig
+
+    cfg = QwenDiTConfig(hidden=512, heads=4, head_dim=128, n_blocks=1, rank=16)
+    model = QwenDiT(cfg, device=cuda_dev).random_init(seed=9)
+    blk = model.blocks[0]
+    B, S_img, S_txt = 1, 200, 56
+    g = torch.Generator().manual_seed(4)
+    h = torch.randn(B, S_img, cfg.hidden, generator=g).to(T)
+    e = torch.randn(B, S_txt, cfg.hidden, generator=g).to(T)
+    temb = torch.randn(B, cfg.hidden, generator=g).to(T)
+    img_f, txt_f = model.rotary_freqs(S_img, cfg.head_dim, cuda_dev), model.rotary_freqs(S_txt, cfg.head_dim, cuda_dev)
+    with torch.no_grad():
+        e_gpu, h_gpu = blk(h.to(cuda_dev), e.to(cuda_dev), temb.to(cuda_dev), img_f, txt_f)
+        torch.cuda.synchronize(cuda_dev)
+        assert _lib.device_status(cuda_dev) == 0
+        e_ref, h_ref = _o_qwen_block(blk, h, e, temb, img_f.cpu(), txt_f.cpu())
+    errs = {"image": w4a4.rel_fro(h_gpu.float().cpu(), h_ref.float()), "text": w4a4.rel_fro(e_gpu.float().cpu(), e_ref.float())}
+    print("\nQwen-Image block parity (relative Frobenius error vs the oracle chain)", errs)
+    for k, v in errs.items():
+        assert v <= 3e-2, (k, v)

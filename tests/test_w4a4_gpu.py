@@ -353,10 +353,11 @@ def test_gelu_quant(cuda_dev, impl, dtype, R2):
     _status_clean(cuda_dev)
 
 
+@pytest.mark.parametrize("impl", [PAIR, GENERIC])
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_swiglu_quant(cuda_dev, dtype):
+@pytest.mark.parametrize("M,N,K,R,R2", [(144, 256, 256, 16, 48), (300, 1024, 384, 32, 32)])
+def test_swiglu_quant(cuda_dev, impl, dtype, M, N, K, R, R2):
     Kn = _ops()
-    M, N, K, R, R2 = 144, 256, 256, 16, 48
     H = N // 2
     act, wgt, asc, wsc, bias, la, lu = _rand_problem(M, N, K, R, dtype, seed=77)
     g = torch.Generator().manual_seed(78)
@@ -370,8 +371,9 @@ def test_swiglu_quant(cuda_dev, dtype):
     lao = torch.empty(M, R2, device=cuda_dev)
     Kn.gemm_w4a4(act.to(cuda_dev), wgt[idx].to(cuda_dev), None, asc.to(cuda_dev), wsc[:, idx].contiguous().to(cuda_dev),
                  bias[idx].to(cuda_dev), la.to(cuda_dev), lu[idx].to(cuda_dev), qout=qout, oscales=osc,
-                 smooth_factor=smooth.to(cuda_dev), lora_down=ld.to(cuda_dev), lora_act_out=lao, fuse_swiglu=True)
-    _check_requant(qout, osc, lao, cr, sr, lr, M, signed=True)
+                 smooth_factor=smooth.to(cuda_dev), lora_down=ld.to(cuda_dev), lora_act_out=lao, fuse_swiglu=True, _impl=impl)
+    _check_requant(qout, osc, lao, cr, sr, lr, M, signed=True, fused=True)
+    _status_clean(cuda_dev)
 
 
 # ------------------------------------------------------------------------------------------------
