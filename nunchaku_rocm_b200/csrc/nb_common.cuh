@@ -147,6 +147,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// one test by every lane of the (converged) warp and the warp's vote on it: a warp-uniform verdict in three instructions
+__device__ __forceinline__ bool mbar_try_wait_all(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "vote.sync.all.pred q, p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // try_wait that lets the hardware park the thread for up to `hint_ns` before it reports "not yet"
 __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
     uint32_t ok;
@@ -185,14 +198,30 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
     }
 }
-// The same wait done by lane 0 for its warp (one poller per warp); every lane gets the verdict.
+// The same wait by a whole (converged) warp with a warp-uniform verdict.  Every lane tests and the warp votes; between
+// tests the hardware may park the warp for its own short limit and resumes it when the phase completes.  (With a
+// suspend-time hint a waiter was measured to come back about a hint late, and a chain of such waits - stage landed, slot
+// free, MMAs done - set the pace of the whole pipeline, so the latency-critical waits give no hint.)
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
-                                               unsigned hint_ns = 200) {
-    // fast path without divergence: every lane tests (one broadcast read), the warp votes
-    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
-    int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, code, hint_ns) ? 1 : 0;
-    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+                                               unsigned /*hint_ns*/ = 0, uint64_t limit_ns = 2000000000ull) {
+    if (mbar_try_wait_all(bar, parity)) return true;
+    uint64_t t0 = 0;
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_try_wait_all(bar, parity)) return true;
+        if ((spin & 255u) == 0) {
+            int give_up = 0;
+            if ((threadIdx.x & 31) == 0) {
+                if (*abort_flag) give_up = 1;
+                const uint64_t now = globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                if (now - t0 > limit_ns) {
+                    *abort_flag = code;
+                    give_up = 1;
+                }
+            }
+            if (__shfl_sync(0xffffffffu, give_up, 0)) return false;
+        }
+    }
 }
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -349,7 +378,7 @@ static inline PreparedLayout prepared_layout(int N, int K) {
     size_t off = 0;
     s.w8 = off; off += up256((size_t)N * K);
     s.wsf = off; off += up256((size_t)(K / 64) * s.Np128 * 2);
-    s.wsf2 = off; off += up256((size_t)(K / 64) * s.Np256 * 4);
+    s.wsf2 = off; off += up256((size_t)(K / 64) * s.Np128 * 4);
     s.total = off;
     return s;
 }
