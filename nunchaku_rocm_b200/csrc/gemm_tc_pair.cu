@@ -1,42 +1,34 @@
-// W4A4 int4 GEMM on the 5th-generation tensor cores, CTA-pair form: a cluster of two CTAs owns a 256 x 128 output tile
-// (tcgen05.mma.cta_group::2, M = 256, N = 128, kind::f8f6f4 on e4m3-encoded int4 values, exact integer-valued fp32 group
+// W4A4 int4 GEMM on the 5th-generation tensor cores, CTA-pair form: a cluster of two CTAs owns a 256 x 256 output tile
+// (tcgen05.mma.cta_group::2, M = 256, N = 256, kind::f8f6f4 on e4m3-encoded int4 values, exact integer-valued fp32 group
 // sums in tensor memory), with the low-rank branch and the fused epilogues.
 //
 // Arithmetic contract (reference: nunchaku/ops/triton/gemm_w4a4.py:446-488 and :155-209): for every 64-wide K group g one
 // EXACT int32 dot p_g[m,n]; acc += float(p_g) * as[g,m] * ws[g,n] in fp32; then + T(lora_act) . lora_up^T (16-bit
 // operands, fp32 accumulate), + bias, epilogue, one rounding to T.
 //
-// Why this shape.  Three things bound an int4 GEMM with exact per-group integer sums on this SM, per 128 x 128 x 64 group:
-//   * the drain: two fp32 operations per accumulator on 128 lanes = 256 cycles, and every accumulator has to come out of
-//     tensor memory first (about 250-350 B/clk/SM measured: 190-260 cycles);
-//   * the round trip of an accumulator slot: an MMA pair completes about 570 cycles after it was issued (measured), the
-//     drain needs a few hundred cycles to read a slot out, so about three slots must be in flight, and tensor memory
-//     holds four 128-column slots (a 256-column tile leaves two, which was measured: the tensor pipe then waits);
-//   * operand delivery: TMA from an L2-resident tensor tops out at 25 B/clk/SM (measured); a lone 128 x 128 tile pulls
-//     16 KB of e4m3 operands per group = 650 cycles.
-// A CTA pair takes the third wall down to 490 cycles: per group a CTA loads its own 128 activation rows (8 KB) and HALF of
-// the tile's 128 weight rows (4 KB); the tensor cores of both SMs read both halves of W from the two shared memories.
-// No load is multicast: every CTA issues plain TMA loads into its own shared memory; warp 1 of the second CTA relays "my
-// stage has landed" to the first CTA, whose warp 1 issues the MMAs for both; tcgen05.commit signals the barriers of both.
+// Why a pair.  Per 64-group a CTA computes 128 x 256 outputs from its own 128 activation rows (8 KB as e4m3 bytes) and HALF
+// of the tile's 256 weight rows (8 KB); the tensor cores of both SMs read both halves of W from the two shared memories.
+// That is 16 KB from L2 per 128 x 256 x 64 group -- half of what two independent 128 x 128 tiles pull -- and L2 -> SM operand
+// delivery is what bounds the single-CTA kernel right behind its drain.  No load is multicast: every CTA issues plain TMA
+// loads into its own shared memory; warp 1 of the second CTA relays "my stage has landed" to the first CTA, whose warp 1
+// issues the MMAs for both; tcgen05.commit signals the barriers of both CTAs.
 //
 // Roles (640 threads per CTA; warps 2 and 3 only exist to complete the control warp group):
-//   warp 0     TMA producer: per ring stage (two K groups) this CTA's A rows (128 x 128 B) and W rows (64 x 128 B), 128-byte
-//              swizzle, and the two groups' scale rows; low-rank chunks of 32 ranks travel through the same ring.
-//   warp 1     first CTA: MMA issuer, per ring stage four 256 x 128 x 32 MMAs into two of FOUR accumulator slots and ONE
-//              commit (the issuing thread pays for every commit, so the work between two of them has to be large); after
-//              the last group the low-rank product (kind::f16) goes into the next slot like one more group.
-//              Second CTA: relay.
-//   warps 4-19 drain: sixteen warps = four per scheduler, so that a warp's tensor-memory load (the longest latency of the
-//              loop; tcgen05.wait::ld waits for all of a thread's loads, so a thread cannot keep several in flight and wait
-//              for the oldest) hides behind the arithmetic of the other three.  A warp owns 32 rows x 32 columns = 32 fp32
-//              accumulators per thread and reads a group's sums in two chunks (tcgen05.ld.16x256b.x4: 16 lanes x 32
-//              columns, 16 registers), the next chunk in flight while the current one is scaled: t = p * as (packed
-//              multiply), acc = fma(t, ws, acc) (packed FMA).  Scales sit in shared memory in the order the threads read
-//              them: one 128-bit load gives a thread two row scales as duplicated pairs, two give it its eight fp32 column
-//              scales.  After a group's second chunk has landed the warp frees the slot (arrive on the first CTA's barrier).
-//   Epilogue (same warps, accumulators in registers): bias, optional per-head RMSNorm + RoPE (a tile is one head), or GELU /
-//              SwiGLU + next-layer int4 re-quantisation with the LoRA-down product on mma.sync straight from the accumulator
-//              registers; rounding and coalesced stores through a per-warp staging tile.
+//   warp 0     TMA producer: per ring stage (two K groups) this CTA's A rows and W rows (128 x 128 B each, 128-byte
+//              swizzle) and the two groups' scale rows; low-rank chunks of 32 ranks travel through the same ring.
+//   warp 1     first CTA: MMA issuer, per K group two 256 x 256 x 32 MMAs into one of TWO 256-column accumulator slots and
+//              one commit ("slot full", both CTAs); after the last group the low-rank product (kind::f16) goes into the next
+//              slot like one more group.  Second CTA: relay.
+//   warps 4-19 drain: sixteen warps = four per scheduler, so that the tensor-memory load of one warp (the longest latency
+//              in the loop) hides behind the arithmetic of the other three.  A warp owns 32 rows x 64 columns = 64 fp32
+//              accumulators per thread and reads a group's sums in four chunks (tcgen05.ld.16x256b.x4: 16 lanes x 32 columns,
+//              16 registers): t = p * as (packed multiply), acc = fma(t, ws, acc) (packed FMA).  Scales sit in shared
+//              memory in the order the threads read them: one 128-bit load gives a thread its two row scales as
+//              duplicated pairs, two give it its eight fp32 column scales.  After the last chunk's load the warp frees the
+//              slot (arrive on the first CTA's barrier) so the next group's MMAs overlap the arithmetic.
+//   Epilogue (same warps, accumulators in registers): bias, optional per-head RMSNorm + RoPE, or GELU + next-layer int4
+//              re-quantisation with the LoRA-down product on mma.sync straight from the accumulator registers; rounding and
+//              coalesced stores through a per-warp staging tile.
 //
 // Every wait on an mbarrier is bounded (~2 s); on expiry the CTA records a code in the status word, unwinds without
 // touching more data and frees its tensor memory after the pair has met at a cluster barrier.
@@ -49,26 +41,28 @@
 namespace nb {
 namespace tcp {
 
-constexpr int BM = 128;        // rows per CTA (256 per pair)
-constexpr int BN = 128;        // columns per pair tile
-constexpr int WROWS = BN / 2;  // W rows each CTA keeps in shared memory
-constexpr int STAGES = 5;
-constexpr int NSLOT = 4;       // tensor-memory accumulator slots of BN columns
+constexpr int BM = 128;   // rows per CTA (256 per pair)
+constexpr int BN = 256;   // columns per pair tile; each CTA keeps 128 of its W rows in shared memory
+constexpr int STAGES = 4;
+constexpr int NSLOT = 2;
 constexpr int DRAIN_WARPS = 16;
-constexpr int CTRL_WARPS = 4;  // TMA producer, MMA issuers / relay, idle (drain warp w reads TMEM lanes 32 (w % 4)..)
+constexpr int CTRL_WARPS = 4;   // one warp group: TMA producer, MMA issuer / relay, two idle warps
 constexpr int NTHREADS = (CTRL_WARPS + DRAIN_WARPS) * 32;
-constexpr int NCQ = DRAIN_WARPS / 4;  // column slices of the tile
-constexpr int COLS = BN / NCQ;        // 32 columns per drain warp
-constexpr int NJ = COLS / 8;          // 8-column blocks per warp
-constexpr int NV = 4 * NJ;            // registers of one 16-lane chunk of a warp's slice
+constexpr int LAUNCH_REGS = 96;   // what 640 threads per CTA leave per thread (the compiler's cap under the launch bound)
+constexpr int CTRL_REGS = 32, DRAIN_REGS = 112;
+// setmaxnreg.inc can only take what setmaxnreg.dec has put into the CTA's pool: it blocks until the pool has enough, for ever
+// if it never will.  The control warp group must give back at least what the four drain warp groups ask for.
+static_assert((LAUNCH_REGS - CTRL_REGS) * 128 >= (DRAIN_REGS - LAUNCH_REGS) * DRAIN_WARPS * 32, "register pool of the CTA");
+constexpr int COLS = 64;  // columns one drain warp owns
+constexpr int NJ = COLS / 8;
 
 struct Cfg {
-    static constexpr int ST_A = BM * 128, ST_W = WROWS * 128;  // two K groups of e4m3 bytes per row
-    static constexpr int ST_AS = 2 * BM * 8;                   // per group and row: (as, as), rows in drain order
-    static constexpr int ST_WS = 2 * BN * 4;                   // per group and column: ws as fp32, columns in drain order
+    static constexpr int ST_A = BM * 128, ST_W = 128 * 128;   // two K groups of e4m3 bytes per row
+    static constexpr int ST_AS = 2 * BM * 8;                  // per group and row: (as, as), rows in drain order
+    static constexpr int ST_WS = 2 * BN * 4;                  // per group and column: ws as fp32, columns in drain order
     static constexpr int ST_BYTES = ST_A + ST_W + ST_AS + ST_WS;
     static constexpr int STG_PITCH = COLS * 2 + 16;
-    static constexpr int STG_WARP = 32 * 32 * 4 + 512;         // a 32 x 32 fp32 LoRA-down partial (or 32 rows x STG_PITCH)
+    static constexpr int STG_WARP = 32 * STG_PITCH;           // 4608 B per warp
     static constexpr int STG_BYTES = DRAIN_WARPS * STG_WARP;
     static constexpr int XCH_BYTES = 2 * DRAIN_WARPS * 32 * 4;
     static constexpr int OFF_ST = 0;
@@ -76,21 +70,22 @@ struct Cfg {
     static constexpr int OFF_XCH = OFF_STG + STG_BYTES;
     static constexpr int OFF_BAR = OFF_XCH + XCH_BYTES;
     static constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;
-    static constexpr int TMEM_COLS = NSLOT * BN;               // 512
+    static constexpr int TMEM_COLS = NSLOT * BN;              // 512
 };
 static_assert(Cfg::ST_BYTES % 1024 == 0, "stage buffers must stay 1 KB aligned for the 128-byte swizzle");
 static_assert(Cfg::SMEM_BYTES <= 232448, "shared memory budget");
-static_assert(Cfg::STG_WARP >= 32 * Cfg::STG_PITCH, "staging tile");
+static_assert(Cfg::STG_WARP >= 32 * 32 * 4 + 0, "the staging tile also holds a warp's 32 x 32 fp32 LoRA-down partial");
 
 enum {  // barrier indices
     B_FULL = 0,                     // TMA: this CTA's half of the stage has landed
     B_PFULL = B_FULL + STAGES,      // (first CTA) the second CTA's half of the stage has landed
-    B_DONE = B_PFULL + STAGES,      // tcgen05.commit (both CTAs): the stage's MMAs have completed
-    B_SCDONE = B_DONE + STAGES,     // one arrival per drain warp: an int8 stage's scales have been read
-    B_ACC_EMPTY = B_SCDONE + STAGES,// (first CTA) one arrival per drain warp of the pair: the slot has been read out
-    B_XCH = B_ACC_EMPTY + NSLOT,    // 4: exchange between the four column slices of a lane quarter
-    B_LR = B_XCH + 4,               // 2, by tile parity; tcgen05.commit (both CTAs): the tile's low-rank accumulator is complete
-    B_COUNT = B_LR + 2
+    B_SCDONE = B_PFULL + STAGES,    // one arrival per drain warp: an int8 stage's MMAs are complete and its scales have been read
+    B_ACC_FULL = B_SCDONE + STAGES, // tcgen05.commit: the slot's group is complete (signalled in both CTAs)
+    B_ACC_EMPTY = B_ACC_FULL + NSLOT,// (first CTA) one arrival per drain warp of the pair: the slot has been read out
+    B_XCH = B_ACC_EMPTY + NSLOT,    // 8: exchange between the warps that share rows (lane quarter x head)
+    B_LX = B_XCH + 8,               // 4: the four column slices of a lane quarter (LoRA-down partial sums)
+    B_LRDONE = B_LX + 4,            // tcgen05.commit: the MMAs of a low-rank stage have read its operands (both CTAs)
+    B_COUNT = B_LRDONE + STAGES
 };
 enum { E_PROD = 0x310, E_MMA = 0x330, E_DRAIN = 0x340, E_RELAY = 0x350 };
 
@@ -108,12 +103,12 @@ struct Params {
     long long stride_rm;
     int rot_rows;
     float eps;
-    // GELU / SwiGLU + re-quantisation epilogue
+    // GELU + re-quantisation epilogue
     uint8_t* qout;
     void* oscales;
-    const float* inv_smooth;   // (Nq) fp32 reciprocals, or null
-    const void* lora_down_t;   // (R2, Nq) T: lora_down transposed, or null
-    float* lora_part;          // (N / 128, M, R2) fp32 partial sums, one slab per column tile
+    const float* inv_smooth;   // (N) fp32 reciprocals, or null
+    const void* lora_down_t;   // (R2, N) T: lora_down transposed, or null
+    float* lora_part;          // (N / 256, M, R2) fp32 partial sums, one slab per column tile
     int R2;
     float shift;
     long long stride_qm, stride_osg;
@@ -235,6 +230,10 @@ __device__ __forceinline__ void mma_sync_16816(float (&d)[4], const uint32_t (&a
                      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// Registers are handed out per warp group (128 threads): 640 threads start with 96 registers each, the control warp group
+// gives 72 of them back (setmaxnreg.dec to 24: 9216 registers into the CTA's pool) and the four drain warp groups grow to
+// 112 (setmaxnreg.inc: 8192 registers out of that pool).  (576 threads at 112 registers do not launch: the fifth warp
+// group is charged in full.)  The host refuses to launch if the compiled kernel does not start with exactly 96 registers.
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {  // shared-memory load by 32-bit address: no 64-bit pointer kept live
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -242,9 +241,10 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {  // shared-memory load 
 }
 
 // The control warps run their loops as whole warps, with everything but the issuing instruction itself warp-uniform (stage
-// and slot counters, barrier addresses, descriptors), and one elected lane issues: measured, a loop run by one lane inside a
-// divergent branch spent about 1700 cycles per ring stage on its own instructions (every descriptor and address moved
-// between the per-thread and the uniform register file), which made the MMA issuer the bottleneck of the whole kernel.
+// and slot counters, barrier addresses, descriptors), and one elected lane issues.  They share their schedulers and the
+// shared-memory pipe with drain warps that keep both busy (measured from the issuer warp inside the running kernel: about
+// 12 cycles per instruction issued, 70 per dependent shared-memory access), so what counts is the number of dependent
+// operations per K group: a loop run by one lane inside a divergent branch took about 1700 cycles per ring stage.
 template <int EPI, typename T, bool DEBUG_P>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
@@ -266,13 +266,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         for (int i = 0; i < STAGES; ++i) {
             mbar_init(bar(B_FULL + i), 1);
             mbar_init(bar(B_PFULL + i), 1);
-            mbar_init(bar(B_DONE + i), 1);
             mbar_init(bar(B_SCDONE + i), DRAIN_WARPS);
+            mbar_init(bar(B_LRDONE + i), 1);
         }
-        for (int i = 0; i < NSLOT; ++i) mbar_init(bar(B_ACC_EMPTY + i), 2 * DRAIN_WARPS);  // (used in the first CTA only)
-        for (int i = 0; i < 4; ++i) mbar_init(bar(B_XCH + i), NCQ);
-        mbar_init(bar(B_LR), 1);
-        mbar_init(bar(B_LR + 1), 1);
+        for (int i = 0; i < NSLOT; ++i) {
+            mbar_init(bar(B_ACC_FULL + i), 1);
+            mbar_init(bar(B_ACC_EMPTY + i), 2 * DRAIN_WARPS);  // (used in the first CTA only)
+        }
+        for (int i = 0; i < 8; ++i) mbar_init(bar(B_XCH + i), 2);
+        for (int i = 0; i < 4; ++i) mbar_init(bar(B_LX + i), 4);
         *abort_s = 0;
         fence_barrier_init();
     }
@@ -283,7 +285,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_s;
 
-    // static contiguous tile range of this pair; tile t = m_blk * NT + n_blk (256 x 128)
+    // static contiguous tile range of this pair; tile t = m_blk * NT + n_blk (256 x 256)
     const int MT = (p.M + 2 * BM - 1) / (2 * BM), NT = (p.N + BN - 1) / BN;
     const int total = MT * NT;
     const int pairs = gridDim.x / 2, pid = blockIdx.x / 2;
@@ -293,44 +295,49 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int GS = (G + 1) / 2;       // int8 stages per tile (two K groups each)
     const int LCH = (p.R + 31) / 32;  // low-rank stages per tile (32 ranks each)
 
+    if (warp < CTRL_WARPS) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(CTRL_REGS));
     if (warp == 0) {
         // ================================ TMA producer (both CTAs) ================================
         if (lane == 0) {
             tma_prefetch_desc(&tm_a); tma_prefetch_desc(&tm_w); tma_prefetch_desc(&tm_as); tma_prefetch_desc(&tm_ws);
             if (LCH) { tma_prefetch_desc(&tm_la); tma_prefetch_desc(&tm_lu); }
         }
-        // A stage is free again when its MMAs have completed (B_DONE, every fill) and, for an int8 fill, when the sixteen
-        // drain warps have read its scales (B_SCDONE).  One bit per stage: the parity of its int8 fills so far, and whether
-        // the last fill was one.
-        uint32_t it = 0, s = 0, ph = 0, n_sc = 0, last_sc = 0;
+        // per stage (one bit each): the parity of its int8 fills / low-rank fills so far, and what the last fill was.  An int8
+        // fill is released by the sixteen drain warps (they read its scales after its MMAs have completed), a low-rank
+        // fill by the MMAs' own completion: a rank above 128 needs more stages than the ring has, so those must come
+        // free before the drain has seen the low-rank product.
+        uint32_t it = 0, s = 0, n_sc = 0, n_lr = 0, last_lr = 0;
         bool ok = true;
         for (int t = t_begin; t < t_end && ok; ++t) {
             const int m0 = (t / NT) * (2 * BM) + (int)rank * BM, n0 = (t % NT) * BN;
             for (int j = 0; j < GS + LCH; ++j, ++it) {
-                if (!mbar_wait_warp(bar(B_DONE + s), ph ^ 1, abort_s, E_PROD | 1, 500)) { ok = false; break; }
-                if ((last_sc >> s) & 1u) {
-                    if (!mbar_wait_warp(bar(B_SCDONE + s), ((n_sc >> s) & 1u) ^ 1u, abort_s, E_PROD | 2, 500)) { ok = false; break; }
+                if (it >= (uint32_t)STAGES) {
+                    const bool was_lr = (last_lr >> s) & 1u;
+                    const uint32_t n = ((was_lr ? n_lr : n_sc) >> s) & 1u;  // parity of the fills of that kind so far (>= 1 fill)
+                    if (!mbar_wait_warp(bar(was_lr ? B_LRDONE : B_SCDONE) + 8u * s, n ^ 1u, abort_s, E_PROD | 1)) { ok = false; break; }
                 }
                 const uint32_t dst = s_base + C::OFF_ST + s * C::ST_BYTES;
+                const uint32_t fb = bar(B_FULL) + 8u * s;
                 if (j < GS) {
-                    n_sc ^= 1u << s; last_sc |= 1u << s;
+                    n_sc ^= 1u << s; last_lr &= ~(1u << s);
                     if (elect_one()) {
-                        mbar_expect_tx(bar(B_FULL + s), C::ST_BYTES);
-                        tma_load_2d(dst, &tm_a, bar(B_FULL + s), j * 128, m0);
-                        tma_load_2d(dst + C::ST_A, &tm_w, bar(B_FULL + s), j * 128, n0 + (int)rank * WROWS);
-                        tma_load_2d(dst + C::ST_A + C::ST_W, &tm_as, bar(B_FULL + s), m0 * 2, j * 2);
-                        tma_load_2d(dst + C::ST_A + C::ST_W + C::ST_AS, &tm_ws, bar(B_FULL + s), n0, j * 2);
+                        mbar_expect_tx(fb, C::ST_BYTES);
+                        tma_load_2d(dst, &tm_a, fb, j * 128, m0);
+                        tma_load_2d(dst + C::ST_A, &tm_w, fb, j * 128, n0 + (int)rank * 128);
+                        tma_load_2d(dst + C::ST_A + C::ST_W, &tm_as, fb, m0 * 2, j * 2);
+                        tma_load_2d(dst + C::ST_A + C::ST_W + C::ST_AS, &tm_ws, fb, n0, j * 2);
                     }
                 } else {
-                    last_sc &= ~(1u << s);
+                    n_lr ^= 1u << s; last_lr |= 1u << s;
                     if (elect_one()) {
-                        // 32 ranks of T(lora_act) rows m0.. and of this CTA's 64 lora_up rows: 64-byte rows, 64-byte swizzle
-                        mbar_expect_tx(bar(B_FULL + s), (BM + WROWS) * 64);
-                        tma_load_2d(dst, &tm_la, bar(B_FULL + s), (j - GS) * 32, m0);
-                        tma_load_2d(dst + C::ST_A, &tm_lu, bar(B_FULL + s), (j - GS) * 32, n0 + (int)rank * WROWS);
+                        // 32 ranks of T(lora_act) rows m0.. and of this CTA's 128 lora_up rows: 128 x 64 B each, 64-byte swizzle
+                        mbar_expect_tx(fb, 2 * 128 * 64);
+                        tma_load_2d(dst, &tm_la, fb, (j - GS) * 32, m0);
+                        tma_load_2d(dst + C::ST_A, &tm_lu, fb, (j - GS) * 32, n0 + (int)rank * 128);
                     }
                 }
-                if (++s == STAGES) { s = 0; ph ^= 1u; }
+                if (++s == STAGES) s = 0;
             }
         }
         if (!ok && lane == 0) {
@@ -349,15 +356,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         bool ok = true;
         for (int t = t_begin; t < t_end && ok; ++t)
             for (int j = 0; j < GS + LCH; ++j) {
-                if (!mbar_wait_warp(bar(B_FULL + s), ph, abort_s, E_RELAY | 1, 100)) { ok = false; break; }
-                if (lane == 0) mbar_arrive_cluster_release(bar(B_PFULL + s), 0);
+                if (!mbar_wait_warp(bar(B_FULL) + 8u * s, ph, abort_s, E_RELAY | 1)) { ok = false; break; }
+                if (lane == 0) mbar_arrive_cluster_release(bar(B_PFULL) + 8u * s, 0);
                 if (++s == STAGES) { s = 0; ph ^= 1u; }
             }
     } else if (warp == 1) {
         // ================================ MMA issuer (first CTA, for the pair) ================================
-        // A unit is one int8 ring stage (two K groups) or the tile's low-rank product; unit u owns the slot pair u & 1 (the
-        // low-rank product and a lone last group use the pair's first slot only).
-        // fp32 accumulators, e4m3 x e4m3, N = 128, M = 256 (pair)
+        // fp32 accumulators, e4m3 x e4m3, N = 256, M = 256 (pair)
         const uint32_t idesc_f8 = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((256u >> 4) << 24);
         const uint32_t f16fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
         const uint32_t idesc_lr = (1u << 4) | (f16fmt << 7) | (f16fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((256u >> 4) << 24);
@@ -366,38 +371,35 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         // An operand's address only changes the low word: stage s adds s * ST_BYTES / 16, a 32-byte K step adds 2.
         const uint32_t lo_a0 = (((s_base + C::OFF_ST) >> 4) & 0x3fffu) | (1u << 16), lo_w0 = lo_a0 + (C::ST_A >> 4);
         constexpr uint32_t HI128 = (1024u >> 4) | (1u << 14) | (2u << 29), HI64 = (512u >> 4) | (1u << 14) | (4u << 29);
-        uint32_t s = 0, ph = 0;       // ring stage and the parity of its fill
-        uint32_t unit = 0, aphase = 0;  // units so far; per slot, the parity of its uses so far
+        uint32_t s = 0, ph = 0;        // ring stage and the parity of its fill
+        uint32_t slot = 0, aph = 0;    // accumulator slot of the next group and the parity of its use
         bool ok = true;
         for (int t = t_begin; t < t_end && ok; ++t) {
-            for (int j = 0; j < GS && ok; ++j, ++unit) {
+            for (int j = 0; j < GS && ok; ++j) {
                 const int ng = min(2, G - 2 * j);
-                if (!mbar_wait_warp(bar(B_FULL) + 8u * s, ph, abort_s, E_MMA | 1, 100) ||
-                    !mbar_wait_warp(bar(B_PFULL) + 8u * s, ph, abort_s, E_MMA | 2, 100)) { ok = false; break; }
+                if (!mbar_wait_warp(bar(B_FULL) + 8u * s, ph, abort_s, E_MMA | 1) ||
+                    !mbar_wait_warp(bar(B_PFULL) + 8u * s, ph, abort_s, E_MMA | 2)) { ok = false; break; }
                 const uint32_t so = s * (C::ST_BYTES >> 4);
                 for (int i = 0; i < ng; ++i) {
-                    const uint32_t slot = 2u * (unit & 1u) + i;
-                    if (!mbar_wait_warp(bar(B_ACC_EMPTY) + 8u * slot, ((aphase >> slot) & 1u) ^ 1u, abort_s, E_MMA | 3, 100)) { ok = false; break; }
-                    aphase ^= 1u << slot;
+                    if (!mbar_wait_warp(bar(B_ACC_EMPTY) + 8u * slot, aph ^ 1u, abort_s, E_MMA | 3)) { ok = false; break; }
                     tc_fence_after();
                     if (elect_one()) {
                         const uint32_t d = tmem_base + slot * BN;
+                        // a 32-byte K step advances the descriptor's start address field by 2; a group is 64 bytes
                         mma2_f8<0>(d, desc64(lo_a0 + so + 4 * i, HI128), desc64(lo_w0 + so + 4 * i, HI128), idesc_f8);
                         mma2_f8<1>(d, desc64(lo_a0 + so + 4 * i + 2, HI128), desc64(lo_w0 + so + 4 * i + 2, HI128), idesc_f8);
+                        tc_commit2(bar(B_ACC_FULL) + 8u * slot);
                     }
+                    slot ^= 1u;
+                    if (slot == 0) aph ^= 1u;
                 }
-                // one commit per stage: both slots full, operands read
-                if (ok && elect_one()) tc_commit2(bar(B_DONE) + 8u * s);
                 if (++s == STAGES) { s = 0; ph ^= 1u; }
             }
             if (ok && LCH > 0) {
-                const uint32_t slot = 2u * (unit & 1u);
-                ++unit;
-                if (!mbar_wait_warp(bar(B_ACC_EMPTY) + 8u * slot, ((aphase >> slot) & 1u) ^ 1u, abort_s, E_MMA | 4, 100)) { ok = false; break; }
-                aphase ^= 1u << slot;
+                if (!mbar_wait_warp(bar(B_ACC_EMPTY) + 8u * slot, aph ^ 1u, abort_s, E_MMA | 4)) { ok = false; break; }
                 for (int c = 0; c < LCH; ++c) {
-                    if (!mbar_wait_warp(bar(B_FULL) + 8u * s, ph, abort_s, E_MMA | 5, 100) ||
-                        !mbar_wait_warp(bar(B_PFULL) + 8u * s, ph, abort_s, E_MMA | 6, 100)) { ok = false; break; }
+                    if (!mbar_wait_warp(bar(B_FULL) + 8u * s, ph, abort_s, E_MMA | 5) ||
+                        !mbar_wait_warp(bar(B_PFULL) + 8u * s, ph, abort_s, E_MMA | 6)) { ok = false; break; }
                     tc_fence_after();
                     if (elect_one()) {
                         const uint32_t so = s * (C::ST_BYTES >> 4);
@@ -405,117 +407,137 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         if (c == 0) mma2_f16<0>(d, desc64(lo_a0 + so, HI64), desc64(lo_w0 + so, HI64), idesc_lr);
                         else mma2_f16<1>(d, desc64(lo_a0 + so, HI64), desc64(lo_w0 + so, HI64), idesc_lr);
                         mma2_f16<1>(d, desc64(lo_a0 + so + 2, HI64), desc64(lo_w0 + so + 2, HI64), idesc_lr);
-                        tc_commit2(bar(B_DONE) + 8u * s);
+                        tc_commit2(bar(B_LRDONE) + 8u * s);
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
-                if (elect_one()) tc_commit2(bar(B_LR + ((t - t_begin) & 1)));
+                if (elect_one()) tc_commit2(bar(B_ACC_FULL) + 8u * slot);
+                slot ^= 1u;
+                if (slot == 0) aph ^= 1u;
             }
         }
-    } else if (warp >= CTRL_WARPS) {
+    }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(DRAIN_REGS));
         // ================================ drain + epilogue (both CTAs, own 128 rows) ================================
         // tcgen05.ld.16x256b.x4 hands a thread, for one 16-lane block and 32 columns, rows {gid, gid + 8} and the column
         // pairs 8 j + 2 tig + {0, 1}, j = 0..3: register 4 j + 2 rs + e.
-        // (Everything the K loop does not need is computed after it: a spill inside the loop costs more than that arithmetic.)
+        // (Everything the K loop does not need is computed after it: the loop runs with 64 accumulators, one 16-register
+        // chunk and 12 scale registers out of 112, and a spill inside it costs more than any of this arithmetic.)
         const int q = warp & 3;                    // TMEM lane quarter this warp may read (warp id mod 4)
-        const int cq = (warp - CTRL_WARPS) >> 2;   // 32-column slice of the tile
+        const int cq = (warp - CTRL_WARPS) >> 2;   // 64-column slice of the tile
         const int gid = lane >> 2, tig = lane & 3;
         const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16) + cq * COLS;
         // byte offsets of this thread's scales inside a stage's scale block: row-scale entry (quarter, lane block 0, gid),
-        // column-scale entry (slice, tig); both blocks keep 1 KB / 512 B per group
+        // column-scale entry (slice, half 0, tig)
         const uint32_t sc_off = s_base + C::OFF_ST + C::ST_A + C::ST_W;
-        const uint32_t as_off = (q * 16 + gid) * 16, ws_off = C::ST_AS + (cq * 4 + tig) * 32;
+        const uint32_t as_off = (q * 16 + gid) * 16, ws_off = C::ST_AS + (cq * 8 + tig) * 32;
         // The loop is bound by instruction issue (four drain warps per scheduler), so everything a K group does not strictly
-        // need is kept out of it: ring stage, parity and addresses are carried in registers and advanced by additions, the
+        // need is kept out of it: slot, ring stage and addresses are carried in registers and advanced by additions, the
         // remote barrier address is mapped once, the slot is freed by one predicated instruction.
         const uint32_t is_lane0 = lane == 0 ? 1u : 0u;
         const uint32_t rem_empty = mapa_cluster(bar(B_ACC_EMPTY), 0);  // the first CTA's slot barriers
-        const uint32_t as_base = sc_off + as_off, ws_base = sc_off + ws_off;
-        uint32_t ds = 0, dph = 0;   // ring stage of the next int8 unit and the parity of its fill
-        uint32_t unit = 0;          // units drained so far: unit u owns the slot pair u & 1
-        uint32_t xph = 0;
+        uint32_t ds = 0;               // ring stage of the next int8 stage
+        uint32_t slot = 0, fph = 0;    // accumulator slot of the next group and the parity of its use
+        uint32_t xph = 0, lxph = 0;
         bool ok = true;
-        // acc[(lb * NJ + j) * 2 + rs]: rows q*32 + lb*16 + rs*8 + gid, columns cq*32 + 8 j + 2 tig + {0, 1}
+        // acc[(lb * NJ + jx) * 2 + rs]: rows q*32 + lb*16 + rs*8 + gid, columns cq*64 + 8 jx + 2 tig + {0, 1}
         uint64_t acc[2 * NJ * 2];
 
         for (int t = t_begin; t < t_end && ok; ++t) {
 #pragma unroll
             for (int i = 0; i < 2 * NJ * 2; ++i) acc[i] = 0ull;
-            // One K group: both 16-lane chunks of the warp's slice are requested, the scales are fetched while they are on
-            // their way, the slot is freed as soon as they have landed, then 32 packed operations.  The other three warps of
-            // the scheduler fill the time this warp waits for tensor memory.
-            auto drain_group = [&](uint32_t tm, uint32_t sa, uint32_t sw, uint32_t rem_bar, int g) {
-                uint32_t v[2][NV];
-                tmem_ld_16x256b_x4(tm, v[0]);
-                tmem_ld_16x256b_x4(tm + (16u << 16), v[1]);
-                const uint4 a0 = lds128(sa), a1 = lds128(sa + 128);
-                const uint4 w0 = lds128(sw), w1 = lds128(sw + 16);
-                const uint64_t ap[4] = {pack_u32x2(a0.x, a0.y), pack_u32x2(a0.z, a0.w), pack_u32x2(a1.x, a1.y), pack_u32x2(a1.z, a1.w)};
-                const uint64_t wp[4] = {pack_u32x2(w0.x, w0.y), pack_u32x2(w0.z, w0.w), pack_u32x2(w1.x, w1.y), pack_u32x2(w1.z, w1.w)};
-                tmem_wait_ld();  // (warp-wide: every lane's values have landed)
-                tc_fence_before();
-                mbar_arrive_remote_if(rem_bar, is_lane0);
+            // One K group: four chunks of 16 lanes x 32 columns; the slot is freed when the last chunk has landed.  One load is
+            // in flight per warp (the registers hold 64 accumulators, one chunk and its scales); what hides the tensor-memory
+            // latency is the arithmetic of the other three warps of the scheduler.  (Two loads of 64 columns per group were
+            // measured: 8 % faster with the drain alone, slower inside the whole kernel on long K loops.)
+            auto drain_group = [&](uint32_t taddr, uint32_t st, uint32_t rem_bar, int g) {
 #pragma unroll
-                for (int lb = 0; lb < 2; ++lb) {
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint64_t wp[4];
 #pragma unroll
-                    for (int j = 0; j < NJ; ++j)
-#pragma unroll
-                        for (int rs = 0; rs < 2; ++rs) {
-                            const uint64_t tt = mul_f32x2(pack_u32x2(v[lb][4 * j + 2 * rs], v[lb][4 * j + 2 * rs + 1]), ap[lb * 2 + rs]);
-                            uint64_t& a = acc[(lb * NJ + j) * 2 + rs];
-                            a = fma_f32x2(tt, wp[j], a);
+                    for (int lb = 0; lb < 2; ++lb) {
+                        uint32_t v[16];
+                        tmem_ld_16x256b_x4(taddr + ((uint32_t)(lb * 16) << 16) + ch * 32, v);
+                        // the scales are fetched while the chunk is on its way: shared memory answers slowly while the tensor
+                        // cores read their operands from it
+                        const uint4 a4 = lds128(st + as_off + lb * 128);
+                        const uint64_t ap[2] = {pack_u32x2(a4.x, a4.y), pack_u32x2(a4.z, a4.w)};
+                        if (lb == 0) {
+                            const uint4 w0 = lds128(st + ws_off + ch * 128), w1 = lds128(st + ws_off + ch * 128 + 16);
+                            wp[0] = pack_u32x2(w0.x, w0.y); wp[1] = pack_u32x2(w0.z, w0.w);
+                            wp[2] = pack_u32x2(w1.x, w1.y); wp[3] = pack_u32x2(w1.z, w1.w);
                         }
-                    if (DEBUG_P) {
+                        tmem_wait_ld();  // (warp-wide: every lane's values have landed)
+                        if (ch == 1 && lb == 1) {
+                            // the slot is read out: the next group's MMAs may overwrite it while this warp does its arithmetic
+                            tc_fence_before();
+                            mbar_arrive_remote_if(rem_bar, is_lane0);
+                        }
 #pragma unroll
-                        for (int e = 0; e < NV; ++e) {
-                            const int m = (t / NT) * (2 * BM) + (int)rank * BM + q * 32 + lb * 16 + ((e >> 1) & 1) * 8 + gid;
-                            const int n = (t % NT) * BN + cq * COLS + (e >> 2) * 8 + 2 * tig + (e & 1);
-                            if (m < p.M && n < p.N)
-                                p.p_out[((long long)g * p.M + m) * p.N + n] = (int)__uint_as_float(v[lb][e]);
+                        for (int j = 0; j < 4; ++j)
+#pragma unroll
+                            for (int rs = 0; rs < 2; ++rs) {
+                                const uint64_t tt = mul_f32x2(pack_u32x2(v[4 * j + 2 * rs], v[4 * j + 2 * rs + 1]), ap[rs]);
+                                uint64_t& a = acc[(lb * NJ + ch * 4 + j) * 2 + rs];
+                                a = fma_f32x2(tt, wp[j], a);
+                            }
+                        if (DEBUG_P) {
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) {
+                                const int m = (t / NT) * (2 * BM) + (int)rank * BM + q * 32 + lb * 16 + ((e >> 1) & 1) * 8 + gid;
+                                const int n = (t % NT) * BN + cq * COLS + ch * 32 + (e >> 2) * 8 + 2 * tig + (e & 1);
+                                if (m < p.M && n < p.N)
+                                    p.p_out[((long long)g * p.M + m) * p.N + n] = (int)__uint_as_float(v[e]);
+                            }
                         }
                     }
                 }
             };
             for (int j = 0; j < GS; ++j) {
-                if (!mbar_wait_warp(bar(B_DONE) + 8u * ds, dph, abort_s, E_DRAIN | 1, 100)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t pair = unit & 1u;
-                const uint32_t tm = lane_base + pair * (2 * BN);
-                const uint32_t sa = as_base + ds * C::ST_BYTES, sw = ws_base + ds * C::ST_BYTES;
-                drain_group(tm, sa, sw, rem_empty + 16u * pair, 2 * j);
-                if (2 * j + 1 < G) drain_group(tm + BN, sa + BM * 8, sw + BN * 4, rem_empty + 16u * pair + 8u, 2 * j + 1);
+                const uint32_t st = sc_off + ds * C::ST_BYTES;  // both scale blocks keep 1 KB per group
+                const int ng = min(2, G - 2 * j);
+                for (int i = 0; i < ng; ++i) {
+                    if (!mbar_wait_warp(bar(B_ACC_FULL) + 8u * slot, fph, abort_s, E_DRAIN | 1)) { ok = false; break; }
+                    tc_fence_after();
+                    drain_group(lane_base + slot * BN, st + i * 1024, rem_empty + 8u * slot, 2 * j + i);
+                    slot ^= 1u;
+                    if (slot == 0) fph ^= 1u;
+                }
+                if (!ok) break;
                 // the stage's scales are in registers and have been used (the arithmetic above depends on them)
                 if (lane == 0) mbar_arrive(bar(B_SCDONE) + 8u * ds);
-                ++unit;
-                if (++ds == STAGES) { ds = 0; dph ^= 1u; }
+                if (++ds == STAGES) ds = 0;
             }
             if (!ok) break;
             if (LCH > 0) {
-                // the low-rank product arrives like one more group, with unit scales, in the first slot of the next pair
-                const uint32_t tl = (uint32_t)(t - t_begin);
-                if (!mbar_wait_warp(bar(B_LR + (tl & 1)), (tl >> 1) & 1, abort_s, E_DRAIN | 2, 100)) { ok = false; break; }
+                // the low-rank product arrives like one more group, with unit scales
+                if (!mbar_wait_warp(bar(B_ACC_FULL) + 8u * slot, fph, abort_s, E_DRAIN | 2)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t pair = unit & 1u;
-                const uint32_t tm = lane_base + pair * (2 * BN);
-                uint32_t v[2][NV];
-                tmem_ld_16x256b_x4(tm, v[0]);
-                tmem_ld_16x256b_x4(tm + (16u << 16), v[1]);
-                tmem_wait_ld();
-                tc_fence_before();
-                mbar_arrive_remote_if(rem_empty + 16u * pair, is_lane0);
+                const uint32_t taddr = lane_base + slot * BN;
 #pragma unroll
-                for (int lb = 0; lb < 2; ++lb)
+                for (int ch = 0; ch < 2; ++ch)
 #pragma unroll
-                    for (int j = 0; j < NJ; ++j)
-#pragma unroll
-                        for (int rs = 0; rs < 2; ++rs) {
-                            uint64_t& a = acc[(lb * NJ + j) * 2 + rs];
-                            a = add_f32x2(a, pack_u32x2(v[lb][4 * j + 2 * rs], v[lb][4 * j + 2 * rs + 1]));
+                    for (int lb = 0; lb < 2; ++lb) {
+                        uint32_t v[16];
+                        tmem_ld_16x256b_x4(taddr + ((uint32_t)(lb * 16) << 16) + ch * 32, v);
+                        tmem_wait_ld();
+                        if (ch == 1 && lb == 1) {
+                            tc_fence_before();
+                            mbar_arrive_remote_if(rem_empty + 8u * slot, is_lane0);
                         }
-                ++unit;
-                for (int c = 0; c < LCH; ++c)  // the low-rank stages carry nothing for the drain
-                    if (++ds == STAGES) { ds = 0; dph ^= 1u; }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+#pragma unroll
+                            for (int rs = 0; rs < 2; ++rs) {
+                                uint64_t& a = acc[(lb * NJ + ch * 4 + j) * 2 + rs];
+                                a = add_f32x2(a, pack_u32x2(v[4 * j + 2 * rs], v[4 * j + 2 * rs + 1]));
+                            }
+                    }
+                slot ^= 1u;
+                if (slot == 0) fph ^= 1u;
+                ds = (ds + LCH) % STAGES;  // the low-rank stages carry nothing for the drain
             }
 
             // ---------------- epilogue ----------------
@@ -525,22 +547,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             const int pw = cq * 4 + q;                        // index of this warp's staging / exchange buffers
             uint8_t* stg = smem + C::OFF_STG + pw * C::STG_WARP;
             float* xch = reinterpret_cast<float*>(smem + C::OFF_XCH);
-            const int qk_part = EPI == NB_EPI_QK_NORM_ROPE ? n0 / (p.N / 3) : 2;
-            // one exchange among the four slices of this lane quarter: publish `val[r]` of the thread's four rows, wait, and
-            // leave the buffer of this round in `xb` (double-buffered: a buffer is rewritten two rounds later, by when every
-            // warp of the quarter has passed the round in between, i.e. has read this one)
-            float* xb = nullptr;
-            auto exchange = [&](const float (&val)[4], int code) -> bool {
-                xb = xch + (xph & 1) * (DRAIN_WARPS * 32);
-#pragma unroll
-                for (int r = 0; r < 4; ++r)
-                    if (tig == 0) xb[pw * 32 + r * 8 + gid] = val[r];
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(B_XCH + q));
-                const bool done = mbar_wait_warp(bar(B_XCH + q), xph & 1, abort_s, E_DRAIN | code, 100);
-                ++xph;
-                return done;
-            };
+            const int head = cq >> 1;                         // 128-column half of the tile
+            const int hc0 = (cq & 1) * COLS;                  // this warp's first column inside its head
+            const int qk_part = EPI == NB_EPI_QK_NORM_ROPE ? (n0 + head * 128) / (p.N / 3) : 2;
             float sumsq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int j = 0; j < NJ; ++j) {
@@ -559,49 +568,49 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     }
             }
             if (EPI == NB_EPI_QK_NORM_ROPE && qk_part < 2) {
-                // The 128-column tile is one head; its row sums come from the four slices of this lane quarter.  The rotary
-                // values of all four rows are requested before the exchange: their L2 latency hides behind it.
-                float2 sc[4][NJ];
+                // A 128-column half of the tile is one head; its row sums come from this warp and the neighbouring slice.
+                float* xb = xch + (xph & 1) * (DRAIN_WARPS * 32);
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
+                    float s = sumsq[r];
+                    s += __shfl_xor_sync(0xffffffffu, s, 1);
+                    s += __shfl_xor_sync(0xffffffffu, s, 2);
+                    if (tig == 0) xb[pw * 32 + r * 8 + gid] = s;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(B_XCH + q * 2 + head));
+                if (!mbar_wait_warp(bar(B_XCH + q * 2 + head), xph & 1, abort_s, E_DRAIN | 4, 100)) { ok = false; break; }
+                // (the buffer of this parity is written again two exchanges later, and no warp gets there before both warps
+                // of the pair have arrived at the exchange in between, i.e. after they have read this one)
+                const T* nw = static_cast<const T*>(qk_part == 0 ? p.norm_q : p.norm_k) + hc0 + 2 * tig;
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    // both slices add the two partial sums in the same order
+                    const float tot = xb[((head * 2) * 4 + q) * 32 + r * 8 + gid] + xb[((head * 2 + 1) * 4 + q) * 32 + r * 8 + gid];
+                    const float rstd = rsqrtf(tot / 128.0f + p.eps);
+                    const int lb = r >> 1, rs = r & 1;
                     const int m = m0 + q * 32 + r * 8 + gid;
                     int mr = m < p.actual_m ? m : 0;
                     if (mr >= p.rot_rows) mr %= p.rot_rows;
-                    const float2* rp = reinterpret_cast<const float2*>(p.rot + (long long)mr * p.stride_rm + cq * COLS + 2 * tig);
+                    const float2* rp = reinterpret_cast<const float2*>(p.rot + (long long)mr * p.stride_rm + hc0 + 2 * tig);
+                    float2 sc[NJ];
 #pragma unroll
-                    for (int j = 0; j < NJ; ++j) sc[r][j] = __ldg(rp + 4 * j);
-                }
-                float2 nw[NJ];
-                {
-                    const T* nwp = static_cast<const T*>(qk_part == 0 ? p.norm_q : p.norm_k) + cq * COLS + 2 * tig;
-#pragma unroll
-                    for (int j = 0; j < NJ; ++j) nw[j] = unpack2<T>(__ldg(reinterpret_cast<const uint32_t*>(nwp + 8 * j)));
-                }
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    sumsq[r] += __shfl_xor_sync(0xffffffffu, sumsq[r], 1);
-                    sumsq[r] += __shfl_xor_sync(0xffffffffu, sumsq[r], 2);
-                }
-                if (!exchange(sumsq, 4)) { ok = false; break; }
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    float tot = 0.f;  // every slice adds the partial sums in the same order
-#pragma unroll
-                    for (int c = 0; c < NCQ; ++c) tot += xb[(c * 4 + q) * 32 + r * 8 + gid];
-                    const float rstd = rsqrtf(tot / 128.0f + p.eps);
-                    const int lb = r >> 1, rs = r & 1;
+                    for (int j = 0; j < NJ; ++j) sc[j] = __ldg(rp + 4 * j);
 #pragma unroll
                     for (int j = 0; j < NJ; ++j) {
+                        const float2 w = unpack2<T>(__ldg(reinterpret_cast<const uint32_t*>(nw + 8 * j)));
                         const float2 a = unpack_f32x2(acc[(lb * NJ + j) * 2 + rs]);
-                        const float xe = a.x * rstd * nw[j].x, xo = a.y * rstd * nw[j].y;
-                        acc[(lb * NJ + j) * 2 + rs] = pack_f32x2(xe * sc[r][j].y - xo * sc[r][j].x, xe * sc[r][j].x + xo * sc[r][j].y);
+                        const float xe = a.x * rstd * w.x, xo = a.y * rstd * w.y;
+                        acc[(lb * NJ + j) * 2 + rs] = pack_f32x2(xe * sc[j].y - xo * sc[j].x, xe * sc[j].x + xo * sc[j].y);
                     }
                 }
+                ++xph;
+            } else if (EPI == NB_EPI_QK_NORM_ROPE) {
+                // V tiles take no part in the exchange; nothing to do
             }
 
-            constexpr bool REQUANT = EPI == NB_EPI_GELU_QUANT || EPI == NB_EPI_SWIGLU_QUANT;
-            if (!REQUANT || (EPI == NB_EPI_GELU_QUANT && p.out)) {
-                // round, transpose through the per-warp staging tile, store whole 64-byte row segments
+            if (EPI == NB_EPI_STORE || EPI == NB_EPI_QK_NORM_ROPE || (EPI == NB_EPI_GELU_QUANT && p.out)) {
+                // round, transpose through the per-warp staging tile, store whole 128-byte row segments
                 __syncwarp();
 #pragma unroll
                 for (int lb = 0; lb < 2; ++lb)
@@ -613,9 +622,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                             *reinterpret_cast<uint32_t*>(stg + (lb * 16 + rs * 8 + gid) * C::STG_PITCH + (8 * j + 2 * tig) * 2) = pack2<T>(a.x, a.y);
                         }
                 __syncwarp();
-                const int ur = lane >> 2, uc = lane & 3;  // four 16-byte units per row, 8 rows per pass
+                const int ur = lane >> 3, uc = lane & 7;  // 8 16-byte units per row, 4 rows per pass
 #pragma unroll
-                for (int r = 0; r < 32; r += 8) {
+                for (int r = 0; r < 32; r += 4) {
                     const int rr = r + ur;
                     const int mm = m0 + q * 32 + rr, nn = nc0 + uc * 8;
                     const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * C::STG_PITCH + uc * 16);
@@ -625,30 +634,31 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 __syncwarp();
             }
 
-            if (REQUANT) {
-                // GELU:   x = gelu(acc) on all N columns; unsigned codes; a 64-column group spans this slice and its neighbour.
-                // SwiGLU: columns come in blocks of 32 = 16 gate + 16 up (the layer's rows were interleaved at load time), one
-                //         block per slice; y = silu(gate) * up gives N / 2 output columns, 16 per warp; signed codes; a
-                //         64-column output group spans the four slices.
+            if (EPI == NB_EPI_GELU_QUANT || EPI == NB_EPI_SWIGLU_QUANT) {
+                // GELU:   x = gelu(acc) on all N columns; unsigned codes, the 64-column group is this warp's slice.
+                // SwiGLU: columns come in blocks of 32 = 16 gate + 16 up (the layer's rows were interleaved at load time);
+                //         y = silu(gate) * up gives N / 2 output columns, 32 per warp; signed codes, a 64-column output
+                //         group spans this warp and its neighbour slice.
                 // Both: LoRA-down from T(x) before shift and smoothing; v = (x + shift) / smooth; scale = max / qmax from the
                 // unrounded maximum, stored rounded; code = clamp(rint(v * (1 / scale))).
                 constexpr bool SWI = EPI == NB_EPI_SWIGLU_QUANT;
-                constexpr int KSTEPS = SWI ? 1 : 2;      // 16 output columns per mma k step
-                constexpr int NH = SWI ? 2 : 4;          // output 8-column blocks per warp
+                constexpr int KSTEPS = SWI ? 2 : 4;      // 16 output columns per mma k step
                 const int Nq = SWI ? p.N / 2 : p.N;
                 const int oc0 = SWI ? nc0 / 2 : nc0;     // this warp's first output column
                 if (SWI) {
-                    // gate block j (j < 2) and up block j + 2 hold the same (tig, e) positions: thread-local
+                    // gate block j = 4 b + jj (jj < 2) and up block j + 2 hold the same (tig, e) positions: thread-local
 #pragma unroll
                     for (int lb = 0; lb < 2; ++lb)
 #pragma unroll
-                        for (int jj = 0; jj < 2; ++jj)
+                        for (int b = 0; b < 2; ++b)
 #pragma unroll
-                            for (int rs = 0; rs < 2; ++rs) {
-                                const float2 g2 = unpack_f32x2(acc[(lb * NJ + jj) * 2 + rs]);
-                                const float2 u2 = unpack_f32x2(acc[(lb * NJ + jj + 2) * 2 + rs]);
-                                acc[(lb * NJ + jj) * 2 + rs] = pack_f32x2(silu(g2.x) * u2.x, silu(g2.y) * u2.y);
-                            }
+                            for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+                                for (int rs = 0; rs < 2; ++rs) {
+                                    const float2 g2 = unpack_f32x2(acc[(lb * NJ + 4 * b + jj) * 2 + rs]);
+                                    const float2 u2 = unpack_f32x2(acc[(lb * NJ + 4 * b + jj + 2) * 2 + rs]);
+                                    acc[(lb * NJ + 4 * b + jj) * 2 + rs] = pack_f32x2(silu(g2.x) * u2.x, silu(g2.y) * u2.y);
+                                }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 2 * NJ * 2; ++i) {
@@ -656,8 +666,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         acc[i] = pack_f32x2(gelu_tanh(a.x), gelu_tanh(a.y));
                     }
                 }
-                // accumulator index of output 8-column block h (columns oc0 + 8 h + 2 tig + {0, 1})
-                auto xi = [](int lb, int h, int rs) { return (lb * NJ + h) * 2 + rs; };
+                // accumulator index of output k-step kk, half h (columns 16 kk + 8 h + 2 tig + {0, 1} of this warp's outputs)
+                auto xi = [](int lb, int kk, int h, int rs) { return SWI ? (lb * NJ + 4 * kk + h) * 2 + rs : (lb * NJ + 2 * kk + h) * 2 + rs; };
                 const bool have_lora = p.lora_down_t != nullptr && p.R2 > 0;
                 if (have_lora) {
                     // Two adjacent 8-column blocks of the accumulator fragment ARE the A fragment of mma.m16n8k16 (rows gid,
@@ -668,7 +678,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     // and stores the tile's partial sum (the column tiles are added up in tile order by a second kernel).
                     const T* ldt = static_cast<const T*>(p.lora_down_t);
                     float* part = p.lora_part + ((long long)(n0 / BN) * p.M) * p.R2;
-                    const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
                     for (int r0 = 0; r0 < p.R2; r0 += 32) {
                         float c[2][4][4];
 #pragma unroll
@@ -682,8 +691,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                             uint32_t a[2][4];
 #pragma unroll
                             for (int lb = 0; lb < 2; ++lb) {
-                                const float2 x00 = unpack_f32x2(acc[xi(lb, 2 * kk, 0)]), x10 = unpack_f32x2(acc[xi(lb, 2 * kk, 1)]);
-                                const float2 x01 = unpack_f32x2(acc[xi(lb, 2 * kk + 1, 0)]), x11 = unpack_f32x2(acc[xi(lb, 2 * kk + 1, 1)]);
+                                const float2 x00 = unpack_f32x2(acc[xi(lb, kk, 0, 0)]), x10 = unpack_f32x2(acc[xi(lb, kk, 0, 1)]);
+                                const float2 x01 = unpack_f32x2(acc[xi(lb, kk, 1, 0)]), x11 = unpack_f32x2(acc[xi(lb, kk, 1, 1)]);
                                 a[lb][0] = pack2<T>(x00.x, x00.y); a[lb][1] = pack2<T>(x10.x, x10.y);
                                 a[lb][2] = pack2<T>(x01.x, x01.y); a[lb][3] = pack2<T>(x11.x, x11.y);
                             }
@@ -711,7 +720,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                                 *reinterpret_cast<float2*>(cs + (lb * 16 + gid) * 32 + nb * 8 + 2 * tig) = make_float2(c[lb][nb][0], c[lb][nb][1]);
                                 *reinterpret_cast<float2*>(cs + (lb * 16 + 8 + gid) * 32 + nb * 8 + 2 * tig) = make_float2(c[lb][nb][2], c[lb][nb][3]);
                             }
-                        if (!exchange(zero4, 5)) { ok = false; break; }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar(B_LX + q));
+                        if (!mbar_wait_warp(bar(B_LX + q), lxph & 1, abort_s, E_DRAIN | 5, 100)) { ok = false; break; }
+                        ++lxph;
                         if (cq == 0) {
                             // row `lane`: 32 ranks; slices added in slice order
                             const int m = m0 + q * 32 + lane;
@@ -719,7 +731,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                             for (int u = 0; u < 8; ++u) {
                                 float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                                for (int sl = 0; sl < NCQ; ++sl) {
+                                for (int sl = 0; sl < 4; ++sl) {
                                     const float4 x = *reinterpret_cast<const float4*>(smem + C::OFF_STG + (sl * 4 + q) * C::STG_WARP + (lane * 32 + ((u + lane) & 7) * 4) * 4);
                                     sum.x += x.x; sum.y += x.y; sum.z += x.z; sum.w += x.w;
                                 }
@@ -728,11 +740,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                             }
                         }
                         // the staging tiles are rewritten (next slab, or the codes below) only after the first slice's warp has read them
-                        if (!exchange(zero4, 6)) { ok = false; break; }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar(B_LX + q));
+                        if (!mbar_wait_warp(bar(B_LX + q), lxph & 1, abort_s, E_DRAIN | 6, 100)) { ok = false; break; }
+                        ++lxph;
                     }
                     if (!ok) break;
                 }
-                // ---- quantise
+                // ---- quantise: NH output 8-column blocks per (16-lane block, row select)
+                constexpr int NH = SWI ? 4 : 8;
                 float isw[NH][2];
 #pragma unroll
                 for (int h = 0; h < NH; ++h) {
@@ -748,7 +764,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     mx[r] = 0.f;
 #pragma unroll
                     for (int h = 0; h < NH; ++h) {
-                        const float2 a = unpack_f32x2(acc[xi(lb, h, rs)]);
+                        const float2 a = unpack_f32x2(acc[SWI ? (lb * NJ + 4 * (h >> 1) + (h & 1)) * 2 + rs : (lb * NJ + h) * 2 + rs]);
                         vv[r][h][0] = __fmul_rn(__fadd_rn(a.x, p.shift), isw[h][0]);
                         vv[r][h][1] = __fmul_rn(__fadd_rn(a.y, p.shift), isw[h][1]);
                         mx[r] = SWI ? fmaxf(mx[r], fmaxf(fabsf(vv[r][h][0]), fabsf(vv[r][h][1])))
@@ -757,30 +773,31 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
                 }
-                // the 64-column output group: this slice and its neighbour (GELU), all four slices (SwiGLU)
-                if (!exchange(mx, 7)) { ok = false; break; }
+                if (SWI) {
+                    // the 64-column output group is shared with the neighbour slice: exchange the row maxima
+                    float* xb = xch + (xph & 1) * (DRAIN_WARPS * 32);
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    if (SWI) {
-                        float m4 = 0.f;
+                    for (int r = 0; r < 4; ++r)
+                        if (tig == 0) xb[pw * 32 + r * 8 + gid] = mx[r];
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(B_XCH + q * 2 + head));
+                    if (!mbar_wait_warp(bar(B_XCH + q * 2 + head), xph & 1, abort_s, E_DRAIN | 7, 100)) { ok = false; break; }
 #pragma unroll
-                        for (int c = 0; c < NCQ; ++c) m4 = fmaxf(m4, xb[(c * 4 + q) * 32 + r * 8 + gid]);
-                        mx[r] = m4;
-                    } else {
-                        mx[r] = fmaxf(xb[(((cq & ~1)) * 4 + q) * 32 + r * 8 + gid], xb[(((cq | 1)) * 4 + q) * 32 + r * 8 + gid]);
-                    }
+                    for (int r = 0; r < 4; ++r)
+                        mx[r] = fmaxf(xb[((head * 2) * 4 + q) * 32 + r * 8 + gid], xb[((head * 2 + 1) * 4 + q) * 32 + r * 8 + gid]);
+                    ++xph;
                 }
                 const float qmax = SWI ? 7.0f : 15.0f, qlo = SWI ? -8.0f : 0.0f;
                 const int grp = oc0 / 64;
-                constexpr int RP = 16 + 16;        // staging pitch
-                const bool scale_writer = SWI ? cq == 0 : (cq & 1) == 0;
+                constexpr int RB = SWI ? 16 : 32;   // code bytes per row of this warp
+                constexpr int RP = RB + 16;         // staging pitch
                 __syncwarp();
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     const float scale = __fdiv_rn(mx[r], qmax);
                     const float inv = __fdiv_rn(1.0f, scale == 0.f ? 1.0f : scale);
                     const int m = m0 + q * 32 + r * 8 + gid;
-                    if (tig == 0 && m < p.M && oc0 < Nq && scale_writer)
+                    if (tig == 0 && m < p.M && oc0 < Nq && (!SWI || (cq & 1) == 0))
                         static_cast<T*>(p.oscales)[(long long)grp * p.stride_osg + m] = from_f32<T>(scale);
 #pragma unroll
                     for (int h = 0; h < NH; ++h) {
@@ -791,12 +808,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 }
                 __syncwarp();
                 {
-                    // 32 rows x RB bytes: one row per lane
-                    const int mm = m0 + q * 32 + lane;
-                    if (mm < p.M && oc0 < Nq) {
-                        uint8_t* dst = p.qout + (long long)mm * p.stride_qm + oc0 / 2;
-                        if (SWI) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(stg + lane * RP);
-                        else *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(stg + lane * RP);
+                    // 32 rows x RB bytes in 16-byte units
+                    constexpr int UPR = RB / 16;
+#pragma unroll
+                    for (int u0 = 0; u0 < 32 * UPR; u0 += 32) {
+                        const int idx = u0 + lane, rr = idx / UPR, u = idx % UPR;
+                        const int mm = m0 + q * 32 + rr;
+                        const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * RP + u * 16);
+                        if (mm < p.M && oc0 + u * 32 < Nq)
+                            *reinterpret_cast<uint4*>(p.qout + (long long)mm * p.stride_qm + oc0 / 2 + u * 16) = o;
                     }
                 }
                 __syncwarp();
@@ -822,7 +842,7 @@ struct PrepackParams {
     const uint8_t* act; const uint8_t* wgt;
     const void* ascales; const void* wscales; const float* lora_act;
     uint8_t* a8; uint8_t* w8; float* asf; float* wsf; void* la16;
-    int M, N, K, R, Np, Mp;  // Np: N rounded up to 128, Mp: M rounded up to 256
+    int M, N, K, R, Np, Mp;  // Np, Mp: N, M rounded up to 256
     int act_unsigned;
     int do_act, do_w8, do_wsf;
     long long stride_am, stride_wn, stride_asg, stride_wsg, stride_lam;
@@ -869,12 +889,12 @@ __global__ void __launch_bounds__(256) prepack_pair_kernel(const PrepackParams p
     }
     u -= as_units;
     if (u < ws_units) {
-        // column c of its 128-wide tile -> (slice * 4 + tig) * 8 + j * 2 + e
+        // column c of its 256-wide tile -> ((slice * 2 + half) * 4 + tig) * 8 + j * 2 + e
         const int g = (int)(u / p.Np), n = (int)(u % p.Np);
         const float w = n < p.N ? to_f32<T>(static_cast<const T*>(p.wscales)[(long long)g * p.stride_wsg + n]) : 0.f;
-        const int c = n & 127;
-        const int pos = ((c >> 5) * 4 + ((c >> 1) & 3)) * 8 + ((c >> 3) & 3) * 2 + (c & 1);
-        p.wsf[(long long)g * p.Np + (n & ~127) + pos] = w;
+        const int c = n & 255;
+        const int pos = (((c >> 6) * 2 + ((c >> 5) & 1)) * 4 + ((c >> 1) & 3)) * 8 + ((c >> 3) & 3) * 2 + (c & 1);
+        p.wsf[(long long)g * p.Np + (n & ~255) + pos] = w;
         return;
     }
     u -= ws_units;
@@ -1060,14 +1080,14 @@ static int launch_t(const nb_gemm_args* a, const void* epi, Params p, cudaStream
     const CUtensorMapDataType t16 = std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     bool ok = make_map(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, pp.a8, a->K, a->M, a->K, 128, BM, CU_TENSOR_MAP_SWIZZLE_128B) &&
-              make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, pp.w8, a->K, a->N, a->K, 128, WROWS, CU_TENSOR_MAP_SWIZZLE_128B) &&
+              make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, pp.w8, a->K, a->N, a->K, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B) &&
               make_map(&tm_as, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, pp.asf, (uint64_t)sc.Mp * 2, G, (uint64_t)sc.Mp * 8, BM * 2, 2,
                        CU_TENSOR_MAP_SWIZZLE_NONE) &&
               make_map(&tm_ws, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, pp.wsf, sc.Np, G, (uint64_t)sc.Np * 4, BN, 2,
                        CU_TENSOR_MAP_SWIZZLE_NONE);
     if (ok && a->R > 0)
         ok = make_map(&tm_la, t16, pp.la16, a->R, a->M, (uint64_t)a->R * 2, 32, BM, CU_TENSOR_MAP_SWIZZLE_64B) &&
-             make_map(&tm_lu, t16, a->lora_up, a->R, a->N, (uint64_t)a->stride_lun * 2, 32, WROWS, CU_TENSOR_MAP_SWIZZLE_64B);
+             make_map(&tm_lu, t16, a->lora_up, a->R, a->N, (uint64_t)a->stride_lun * 2, 32, 128, CU_TENSOR_MAP_SWIZZLE_64B);
     else if (ok) { tm_la = tm_a; tm_lu = tm_w; }
     if (!ok) return fail_with(NB_ERR_UNSUPPORTED, "pair kernel: a tensor map could not be encoded");
 
@@ -1078,6 +1098,18 @@ static int launch_t(const nb_gemm_args* a, const void* epi, Params p, cudaStream
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
         NB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    {
+        // the register hand-over inside the kernel is balanced for a launch allocation of LAUNCH_REGS per thread
+        static int regs[64] = {};
+        if (dev < 0 || dev >= 64 || !regs[dev]) {
+            cudaFuncAttributes fa;
+            NB_CUDA_CHECK(cudaFuncGetAttributes(&fa, kern));
+            if (dev >= 0 && dev < 64) regs[dev] = fa.numRegs;
+            if (fa.numRegs != LAUNCH_REGS) return fail_with(NB_ERR_UNSUPPORTED, "pair kernel: unexpected register allocation");
+        } else if (regs[dev] != LAUNCH_REGS) {
+            return fail_with(NB_ERR_UNSUPPORTED, "pair kernel: unexpected register allocation");
+        }
     }
     const int limit = max_pairs(kern, dev);
     if (limit < 1) return fail_with(NB_ERR_UNSUPPORTED, "pair kernel: no CTA pair fits on this device");

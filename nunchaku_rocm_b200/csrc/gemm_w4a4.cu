@@ -53,8 +53,8 @@ static Kernel choose_kernel(const nb_gemm_args* a, const void* epi, int epi_kind
     const char* pair = tcp_unsupported_reason(a, epi, epi_kind);
     if (a->impl == NB_IMPL_TCGEN05_PAIR) { *why = pair; return pair ? K_GENERIC : K_TC_PAIR; }
     if (a->impl == NB_IMPL_TCGEN05_SINGLE) { *why = single; return single ? K_GENERIC : K_TC_SINGLE; }
-    const long long pair_tiles = (long long)((a->M + 255) / 256) * ((a->N + 127) / 128);
-    if (!pair && (single || pair_tiles >= 96)) return K_TC_PAIR;
+    const long long pair_tiles = (long long)((a->M + 255) / 256) * ((a->N + 255) / 256);
+    if (!pair && (single || pair_tiles >= 48)) return K_TC_PAIR;
     if (!single) return K_TC_SINGLE;
     *why = single;
     return K_GENERIC;

@@ -378,7 +378,7 @@ static inline PreparedLayout prepared_layout(int N, int K) {
     size_t off = 0;
     s.w8 = off; off += up256((size_t)N * K);
     s.wsf = off; off += up256((size_t)(K / 64) * s.Np128 * 2);
-    s.wsf2 = off; off += up256((size_t)(K / 64) * s.Np128 * 4);
+    s.wsf2 = off; off += up256((size_t)(K / 64) * s.Np256 * 4);
     s.total = off;
     return s;
 }
