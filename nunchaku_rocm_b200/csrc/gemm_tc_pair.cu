@@ -442,6 +442,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         uint32_t slot = 0, fph = 0;    // accumulator slot of the next group and the parity of its use
         uint32_t xph = 0, lxph = 0;
         bool ok = true;
+        bool ready = false;  // the next group's barrier has already been seen complete
         // acc[(lb * NJ + jx) * 2 + rs]: rows q*32 + lb*16 + rs*8 + gid, columns cq*64 + 8 jx + 2 tig + {0, 1}
         uint64_t acc[2 * NJ * 2];
 
@@ -452,7 +453,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             // in flight per warp (the registers hold 64 accumulators, one chunk and its scales); what hides the tensor-memory
             // latency is the arithmetic of the other three warps of the scheduler.  (Two loads of 64 columns per group were
             // measured: 8 % faster with the drain alone, slower inside the whole kernel on long K loops.)
-            auto drain_group = [&](uint32_t taddr, uint32_t st, uint32_t rem_bar, int g) {
+            auto drain_group = [&](uint32_t taddr, uint32_t st, uint32_t rem_bar, int g, uint32_t next_bar, uint32_t next_par) {
 #pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
                     uint64_t wp[4];
@@ -474,6 +475,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                             // the slot is read out: the next group's MMAs may overwrite it while this warp does its arithmetic
                             tc_fence_before();
                             mbar_arrive_remote_if(rem_bar, is_lane0);
+                            // look at the next group's barrier now: the answer comes back while the last chunk is scaled
+                            // (asked after that arithmetic, a test that passes at once still cost this warp some 300 cycles)
+                            ready = mbar_test_all(next_bar, next_par);
                         }
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
@@ -499,11 +503,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 const uint32_t st = sc_off + ds * C::ST_BYTES;  // both scale blocks keep 1 KB per group
                 const int ng = min(2, G - 2 * j);
                 for (int i = 0; i < ng; ++i) {
-                    if (!mbar_wait_warp(bar(B_ACC_FULL) + 8u * slot, fph, abort_s, E_DRAIN | 1)) { ok = false; break; }
+                    if (!ready && !mbar_wait_warp(bar(B_ACC_FULL) + 8u * slot, fph, abort_s, E_DRAIN | 1)) { ok = false; break; }
                     tc_fence_after();
-                    drain_group(lane_base + slot * BN, st + i * 1024, rem_empty + 8u * slot, 2 * j + i);
-                    slot ^= 1u;
-                    if (slot == 0) fph ^= 1u;
+                    const uint32_t nslot = slot ^ 1u, nph = fph ^ slot;  // (the parity flips when the slot index wraps to 0)
+                    drain_group(lane_base + slot * BN, st + i * 1024, rem_empty + 8u * slot, 2 * j + i, bar(B_ACC_FULL) + 8u * nslot, nph);
+                    slot = nslot;
+                    fph = nph;
                 }
                 if (!ok) break;
                 // the stage's scales are in registers and have been used (the arithmetic above depends on them)
@@ -513,7 +518,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             if (!ok) break;
             if (LCH > 0) {
                 // the low-rank product arrives like one more group, with unit scales
-                if (!mbar_wait_warp(bar(B_ACC_FULL) + 8u * slot, fph, abort_s, E_DRAIN | 2)) { ok = false; break; }
+                if (!ready && !mbar_wait_warp(bar(B_ACC_FULL) + 8u * slot, fph, abort_s, E_DRAIN | 2)) { ok = false; break; }
+                ready = false;
                 tc_fence_after();
                 const uint32_t taddr = lane_base + slot * BN;
 #pragma unroll

@@ -160,6 +160,19 @@ __device__ __forceinline__ bool mbar_try_wait_all(uint32_t bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
+// the same as a non-blocking probe (test_wait never parks the warp): for looking at a barrier ahead of time
+__device__ __forceinline__ bool mbar_test_all(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "vote.sync.all.pred q, p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // try_wait that lets the hardware park the thread for up to `hint_ns` before it reports "not yet"
 __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
     uint32_t ok;
