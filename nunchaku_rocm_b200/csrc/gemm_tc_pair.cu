@@ -9,7 +9,7 @@
 // Why a pair.  Per 64-group a CTA computes 128 x 256 outputs from its own 128 activation rows (8 KB as e4m3 bytes) and HALF
 // of the tile's 256 weight rows (8 KB); the tensor cores of both SMs read both halves of W from the two shared memories.
 // That is 16 KB from L2 per 128 x 256 x 64 group -- half of what two independent 128 x 128 tiles pull -- and L2 -> SM operand
-// delivery is what bounds the single-CTA kernel right behind its drain.  No load is multicast: every CTA issues plain TMA
+// delivery is what bounds the single-CTA kernel right behind its drain (TMA from L2: 25 B/clk/SM measured).  No load is multicast: every CTA issues plain TMA
 // loads into its own shared memory; warp 1 of the second CTA relays "my stage has landed" to the first CTA, whose warp 1
 // issues the MMAs for both; tcgen05.commit signals the barriers of both CTAs.
 //
@@ -231,7 +231,7 @@ __device__ __forceinline__ void mma_sync_16816(float (&d)[4], const uint32_t (&a
 }
 
 // Registers are handed out per warp group (128 threads): 640 threads start with 96 registers each, the control warp group
-// gives 72 of them back (setmaxnreg.dec to 24: 9216 registers into the CTA's pool) and the four drain warp groups grow to
+// gives 64 of them back (setmaxnreg.dec to 32: 8192 registers into the CTA's pool) and the four drain warp groups grow to
 // 112 (setmaxnreg.inc: 8192 registers out of that pool).  (576 threads at 112 registers do not launch: the fifth warp
 // group is charged in full.)  The host refuses to launch if the compiled kernel does not start with exactly 96 registers.
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {  // shared-memory load by 32-bit address: no 64-bit pointer kept live
@@ -575,6 +575,24 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
             if (EPI == NB_EPI_QK_NORM_ROPE && qk_part < 2) {
                 // A 128-column half of the tile is one head; its row sums come from this warp and the neighbouring slice.
+                // The rotary values of a row are requested one row ahead (the first row before the exchange), so that their
+                // trip to L2 hides behind the exchange and the arithmetic of the row before.
+                float2 sc[2][NJ];
+                auto load_rot = [&](int r, float2 (&dst)[NJ]) {
+                    const int m = m0 + q * 32 + r * 8 + gid;
+                    int mr = m < p.actual_m ? m : 0;
+                    if (mr >= p.rot_rows) mr %= p.rot_rows;
+                    const float2* rp = reinterpret_cast<const float2*>(p.rot + (long long)mr * p.stride_rm + hc0 + 2 * tig);
+#pragma unroll
+                    for (int j = 0; j < NJ; ++j) dst[j] = __ldg(rp + 4 * j);
+                };
+                load_rot(0, sc[0]);
+                uint32_t nwv[NJ];
+                {
+                    const T* nw = static_cast<const T*>(qk_part == 0 ? p.norm_q : p.norm_k) + hc0 + 2 * tig;
+#pragma unroll
+                    for (int j = 0; j < NJ; ++j) nwv[j] = __ldg(reinterpret_cast<const uint32_t*>(nw + 8 * j));
+                }
                 float* xb = xch + (xph & 1) * (DRAIN_WARPS * 32);
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
@@ -588,26 +606,20 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 if (!mbar_wait_warp(bar(B_XCH + q * 2 + head), xph & 1, abort_s, E_DRAIN | 4, 100)) { ok = false; break; }
                 // (the buffer of this parity is written again two exchanges later, and no warp gets there before both warps
                 // of the pair have arrived at the exchange in between, i.e. after they have read this one)
-                const T* nw = static_cast<const T*>(qk_part == 0 ? p.norm_q : p.norm_k) + hc0 + 2 * tig;
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
+                    if (r + 1 < 4) load_rot(r + 1, sc[(r + 1) & 1]);
                     // both slices add the two partial sums in the same order
                     const float tot = xb[((head * 2) * 4 + q) * 32 + r * 8 + gid] + xb[((head * 2 + 1) * 4 + q) * 32 + r * 8 + gid];
                     const float rstd = rsqrtf(tot / 128.0f + p.eps);
                     const int lb = r >> 1, rs = r & 1;
-                    const int m = m0 + q * 32 + r * 8 + gid;
-                    int mr = m < p.actual_m ? m : 0;
-                    if (mr >= p.rot_rows) mr %= p.rot_rows;
-                    const float2* rp = reinterpret_cast<const float2*>(p.rot + (long long)mr * p.stride_rm + hc0 + 2 * tig);
-                    float2 sc[NJ];
-#pragma unroll
-                    for (int j = 0; j < NJ; ++j) sc[j] = __ldg(rp + 4 * j);
 #pragma unroll
                     for (int j = 0; j < NJ; ++j) {
-                        const float2 w = unpack2<T>(__ldg(reinterpret_cast<const uint32_t*>(nw + 8 * j)));
+                        const float2 w = unpack2<T>(nwv[j]);
                         const float2 a = unpack_f32x2(acc[(lb * NJ + j) * 2 + rs]);
+                        const float2 c = sc[r & 1][j];
                         const float xe = a.x * rstd * w.x, xo = a.y * rstd * w.y;
-                        acc[(lb * NJ + j) * 2 + rs] = pack_f32x2(xe * sc[j].y - xo * sc[j].x, xe * sc[j].x + xo * sc[j].y);
+                        acc[(lb * NJ + j) * 2 + rs] = pack_f32x2(xe * c.y - xo * c.x, xe * c.x + xo * c.y);
                     }
                 }
                 ++xph;
