@@ -197,8 +197,10 @@ int nb_qk_norm_rope(void* out, int32_t M, int32_t N, int64_t stride_om, int32_t 
 
 /*
  * AWQ W4A16.  `nb_awq_gemv` replaces `awq_gemv_w4a16` (nunchaku/ops/triton/awq.py:186-229) for
- * group 64; `nb_awq_dequant` replaces `awq_dequantize` (awq.py:83-118).  `kernel` is the TinyChat
- * int16 (n/4, k) packing (awq.py:8-18).
+ * group 64; `nb_awq_dequant` replaces `awq_dequantize` (awq.py:83-118); `nb_awq_gemm` replaces
+ * `awq_gemm_w4a16` (awq.py:232-251: dequantise, then a dense matmul) with one kernel that widens the
+ * weight tile in shared memory (k % 64 == 0, group % 32 == 0, rows of x 16-byte aligned).  `kernel` is
+ * the TinyChat int16 (n/4, k) packing (awq.py:8-18).
  */
 int nb_awq_gemv(const void* x, const void* kernel, const void* scales, const void* zeros, void* out, int32_t m,
                 int32_t n, int32_t k, int64_t stride_xm, int64_t stride_kn, int64_t stride_sg, int64_t stride_om,
@@ -206,6 +208,18 @@ int nb_awq_gemv(const void* x, const void* kernel, const void* scales, const voi
 int nb_awq_dequant(const void* kernel, const void* scales, const void* zeros, void* out, int32_t n, int32_t k,
                    int32_t group, int64_t stride_kn, int64_t stride_sg, int64_t stride_on, int32_t dtype,
                    void* stream);
+int nb_awq_gemm(const void* x, const void* kernel, const void* scales, const void* zeros, void* out, int32_t m,
+                int32_t n, int32_t k, int32_t group, int64_t stride_xm, int64_t stride_kn, int64_t stride_sg,
+                int64_t stride_om, int32_t dtype, void* stream);
+
+/*
+ * Checkpoint layout converter for the 4-bit weight: the stored fragment order of a SVDQuant checkpoint
+ * ((n, k/2) bytes viewed as int32 words) -> natural packed nibbles (n, k/2), even k in the low nibble.
+ * Replaces `unpack_weight_packed_nibbles` (nunchaku/ops/triton/layout.py:36-118; inverse of
+ * NunchakuWeightPacker.pack_weight, nunchaku/lora/flux/packer.py:187-239).  n, k multiples of 128;
+ * `stride_on` = bytes between output rows.
+ */
+int nb_layout_unpack_weight(const void* stored, void* out, int32_t n, int32_t k, int64_t stride_on, void* stream);
 
 /*
  * Unmasked flash attention, (B,H,T,D) strided inputs with unit last stride -> (B,Tq,H*D).

@@ -6,7 +6,7 @@ rotated over several buffer sets so that HBM-bound kernels do not run out of L2,
 that bounds the kernel and the fraction of the measured peak (``MEASURED_PEAKS.json`` beside the repository root, else
 the stated fallback).
 
-    python -m nunchaku_rocm_b200.bench_kernels [--iters 50] [--warmup 10] [--only quantize,gemm,mlp,fp4,awq,attention]
+    python -m nunchaku_rocm_b200.bench_kernels [--iters 50] [--warmup 10] [--only quantize,gemm,mlp,fp4,awq,layout,attention]
 
 Prints one JSON object per kernel and shape.  Synthetic seeded inputs with the benchmark configurations' shapes.
 """
@@ -74,7 +74,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--only", default="quantize,gemm,mlp,fp4,awq,attention")
+    ap.add_argument("--only", default="quantize,gemm,mlp,fp4,awq,layout,attention")
     args = ap.parse_args()
     only = set(args.only.split(","))
     dev = torch.device("cuda", 0)
@@ -201,6 +201,22 @@ def main():
             ms, best = time_ms(lambda p: awq_gemv_w4a16(x, p["w"], p["s"], p["z"], m, n, k, 64), sets, args.iters, args.warmup)
             work = n * k // 2 + 2 * 2 * (k // 64) * n + 2 * m * k + 2 * m * n
             emit("awq_gemv_kernel", f"m={m} n={n} k={k} g=64", ms, best, work, "GB/s", "hbm", hbm, src)
+        # the one-kernel W4A16 GEMM for larger batches (legacy mma.sync tensor path: about a third of the bf16 peak at best)
+        from nunchaku_rocm_b200.ops.triton.awq import awq_gemm_w4a16
+        for m in (512, 4608):
+            x = torch.randn(m, k, generator=g).to(T).to(dev)
+            ms, best = time_ms(lambda p: awq_gemm_w4a16(x, p["w"], p["s"], p["z"], 64), sets, max(5, args.iters // 5), 3)
+            emit("awq_gemm_kernel", f"m={m} n={n} k={k} g=64", ms, best, 2.0 * m * n * k, "TFLOP/s", "tensor", bf16, src)
+        del sets
+
+    # ---------------------------------------------------------------- checkpoint layout converter (HBM)
+    if "layout" in only:
+        from nunchaku_rocm_b200.ops.triton.layout import unpack_weight_packed_nibbles
+        n, k = 12288, 3072
+        g = torch.Generator().manual_seed(3)
+        sets = [dict(w=torch.randint(-128, 128, (n, k // 2), dtype=torch.int8, generator=g).to(dev)) for _ in range(12)]  # 12 x 18.9 MB > L2 with the outputs
+        ms, best = time_ms(lambda p: unpack_weight_packed_nibbles(p["w"], n, k), sets, args.iters, args.warmup)
+        emit("layout_unpack_weight_kernel", f"n={n} k={k} (stored fragment order -> natural nibbles)", ms, best, n * k, "GB/s", "hbm", hbm, src)
         del sets
 
     # ---------------------------------------------------------------- attention (tensor pipe, bf16)

@@ -347,6 +347,143 @@ int launch_gemv(const void* x, const void* kernel, const void* scales, const voi
 }
 
 }  // namespace
+
+// ------------------------------------------------------------------------------------------------
+// W4A16 GEMM for larger batches (reference: awq_gemm_w4a16, nunchaku/ops/triton/awq.py:232-251 = dequantise, then a
+// dense matmul): one kernel, the weight never exists in dense form outside shared memory.
+//
+// A CTA owns 128 rows x 128 output channels and walks K in steps of 64.  Per step its 256 threads copy the activations
+// (128 x 64 T) to shared memory and each thread widens ONE 16-byte packed unit (32 nibbles of one channel: k = 64 c + 32 h
+// + 8 m4 + j) to q * s + z rounded to T, exactly as awq_dequant_kernel does, into the channel-major weight tile.  Eight
+// warps (4 along the rows x 2 along the channels, 32 x 64 each) multiply with mma.sync.m16n8k16 (fp32 accumulators) from
+// ldmatrix fragments; rows of both tiles are padded by 16 bytes so that the eight rows of an 8 x 8 matrix fall into
+// different bank groups.  The next step's global loads are issued before the current step's MMAs.
+// ------------------------------------------------------------------------------------------------
+constexpr int GM_BM = 128, GM_BN = 128, GM_BK = 64, GM_PITCH = GM_BK + 8;  // pitch in T elements (144 bytes)
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+template <typename T>
+__device__ __forceinline__ void mma16816_acc(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if (std::is_same<T, __nv_bfloat16>::value)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    else
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) awq_gemm_kernel(const T* __restrict__ x, const uint16_t* __restrict__ kernel,
+                                                       const T* __restrict__ scales, const T* __restrict__ zeros,
+                                                       T* __restrict__ out, int m, int n, int k, int group,
+                                                       long long stride_xm, long long stride_kn, long long stride_sg,
+                                                       long long stride_om) {
+    __shared__ __align__(16) T xs[GM_BM * GM_PITCH];
+    __shared__ __align__(16) T ws[GM_BN * GM_PITCH];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.y * GM_BM, n0 = blockIdx.x * GM_BN;
+    const int wm = (warp & 3) * 32, wn = (warp >> 2) * 64;  // this warp's 32 x 64 corner of the tile
+
+    // this thread's packed unit of a step: packed row a (4 channels), channel b of it, 32-wide half h
+    const int ua = tid >> 3, ub = (tid >> 1) & 3, uh = tid & 1;
+    const int ch = 4 * ua + ub;                      // channel inside the tile
+    const bool ch_ok = n0 + ch < n;
+    const uint16_t* wsrc = kernel + (long long)(n0 / 4 + ua) * stride_kn + 16 * ub + 8 * uh;
+    // this thread's activation units of a step: row tid / 2, 32-element half tid % 2 (four 16-byte units)
+    const int xr = tid >> 1, xh = tid & 1;
+    const bool x_ok = m0 + xr < m;
+    const T* xsrc = x + (long long)(m0 + xr) * stride_xm + 32 * xh;
+
+    float acc[2][8][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+
+    uint4 wreg = make_uint4(0, 0, 0, 0), xreg[4];
+    float sc = 0.f, zp = 0.f;
+    auto fetch = [&](int c) {
+        wreg = ch_ok ? __ldg(reinterpret_cast<const uint4*>(wsrc + 64 * c)) : make_uint4(0, 0, 0, 0);
+        const int g = (64 * c + 32 * uh) / group;
+        sc = ch_ok ? to_f32<T>(__ldg(scales + (long long)g * stride_sg + n0 + ch)) : 0.f;
+        zp = ch_ok ? to_f32<T>(__ldg(zeros + (long long)g * stride_sg + n0 + ch)) : 0.f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            xreg[u] = x_ok ? __ldg(reinterpret_cast<const uint4*>(xsrc + 64 * c) + u) : make_uint4(0, 0, 0, 0);
+    };
+    const int steps = k / GM_BK;
+    fetch(0);
+    for (int c = 0; c < steps; ++c) {
+        __syncthreads();  // the previous step's fragments have been read
+        {
+            const uint32_t w[4] = {wreg.x, wreg.y, wreg.z, wreg.w};
+#pragma unroll
+            for (int m4 = 0; m4 < 4; ++m4) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = (float)((w[j >> 1] >> (16 * (j & 1) + 4 * m4)) & 0xF) * sc + zp;
+                uint4 o;
+                o.x = pack2<T>(v[0], v[1]); o.y = pack2<T>(v[2], v[3]); o.z = pack2<T>(v[4], v[5]); o.w = pack2<T>(v[6], v[7]);
+                *reinterpret_cast<uint4*>(ws + ch * GM_PITCH + 32 * uh + 8 * m4) = o;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) *reinterpret_cast<uint4*>(xs + xr * GM_PITCH + 32 * xh + 8 * u) = xreg[u];
+        }
+        __syncthreads();
+        if (c + 1 < steps) fetch(c + 1);  // in flight during the MMAs
+#pragma unroll
+        for (int kk = 0; kk < GM_BK; kk += 16) {
+            uint32_t a[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                ldmatrix_x4(a[i], smem_u32(xs + (wm + 16 * i + (lane & 15)) * GM_PITCH + kk + 8 * (lane >> 4)));
+#pragma unroll
+            for (int jp = 0; jp < 4; ++jp) {
+                // two 8-channel blocks per load: matrices (channels 0-7, k 0-7), (0-7, k 8-15), (8-15, k 0-7), (8-15, k 8-15)
+                uint32_t b[4];
+                ldmatrix_x4(b, smem_u32(ws + (wn + 16 * jp + (lane & 7) + 8 * (lane >> 4)) * GM_PITCH + kk + 8 * ((lane >> 3) & 1)));
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    mma16816_acc<T>(acc[i][2 * jp], a[i], b[0], b[1]);
+                    mma16816_acc<T>(acc[i][2 * jp + 1], a[i], b[2], b[3]);
+                }
+            }
+        }
+    }
+    // C fragment: rows gid, gid + 8 of a 16-row block, columns 2 tig + {0, 1} of an 8-column block
+    const int gid = lane >> 2, tig = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int col = n0 + wn + 8 * j + 2 * tig;
+            if (col >= n) continue;  // (n is a multiple of 4 and col is even: col + 1 < n as well)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = m0 + wm + 16 * i + gid + 8 * h;
+                if (row < m)
+                    *reinterpret_cast<uint32_t*>(out + (long long)row * stride_om + col) = pack2<T>(acc[i][j][2 * h], acc[i][j][2 * h + 1]);
+            }
+        }
+}
+
+template <typename T>
+static int launch_gemm(const void* x, const void* kernel, const void* scales, const void* zeros, void* out, int m, int n, int k,
+                       int group, long long sxm, long long skn, long long ssg, long long som, cudaStream_t s) {
+    dim3 grid((n + GM_BN - 1) / GM_BN, (m + GM_BM - 1) / GM_BM);
+    awq_gemm_kernel<T><<<grid, 256, 0, s>>>(static_cast<const T*>(x), static_cast<const uint16_t*>(kernel),
+                                            static_cast<const T*>(scales), static_cast<const T*>(zeros), static_cast<T*>(out), m, n,
+                                            k, group, sxm, skn, ssg, som);
+    NB_CUDA_CHECK(cudaGetLastError());
+    return NB_OK;
+}
+
 }  // namespace nb
 
 extern "C" int nb_awq_gemv(const void* x, const void* kernel, const void* scales, const void* zeros, void* out,
@@ -388,4 +525,20 @@ extern "C" int nb_awq_dequant(const void* kernel, const void* scales, const void
             stride_on);
     NB_CUDA_CHECK(cudaGetLastError());
     return NB_OK;
+}
+
+extern "C" int nb_awq_gemm(const void* x, const void* kernel, const void* scales, const void* zeros, void* out, int32_t m,
+                           int32_t n, int32_t k, int32_t group, int64_t stride_xm, int64_t stride_kn, int64_t stride_sg,
+                           int64_t stride_om, int32_t dtype, void* stream) {
+    using namespace nb;
+    NB_REQUIRE(x && kernel && scales && zeros && out);
+    NB_REQUIRE(m >= 0 && n > 0 && k > 0 && n % 4 == 0 && k % 64 == 0 && group >= 32 && group % 32 == 0 && k % group == 0);
+    NB_REQUIRE(dtype == NB_DTYPE_BF16 || dtype == NB_DTYPE_FP16);
+    NB_REQUIRE(aligned16(kernel) && stride_kn % 8 == 0 && aligned16(x) && stride_xm % 8 == 0);
+    NB_REQUIRE((reinterpret_cast<uintptr_t>(out) & 3) == 0 && stride_om % 2 == 0);
+    if (m == 0) return NB_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return dtype == NB_DTYPE_BF16
+               ? launch_gemm<__nv_bfloat16>(x, kernel, scales, zeros, out, m, n, k, group, stride_xm, stride_kn, stride_sg, stride_om, s)
+               : launch_gemm<__half>(x, kernel, scales, zeros, out, m, n, k, group, stride_xm, stride_kn, stride_sg, stride_om, s);
 }

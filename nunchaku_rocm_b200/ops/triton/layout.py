@@ -97,7 +97,27 @@ def unpack_weight(packed: torch.Tensor, n: int, k: int, bits: int = 4) -> torch.
 
 
 def unpack_weight_packed_nibbles(packed: torch.Tensor, n: int, k: int, bits: int = 4) -> torch.Tensor:
-    """As :func:`unpack_weight`, returned in the natural packed form ``(n, k // 2)`` uint8, even ``k`` in the low nibble."""
+    """
+    As :func:`unpack_weight`, returned in the natural packed form ``(n, k // 2)`` uint8, even ``k`` in the low nibble.
+    A tensor that sits on a CUDA device is converted there by ``layout_unpack_weight_kernel`` (a permutation of 32-bit
+    words at HBM speed); on the host the index formula runs in torch.
+    """
+    assert bits == 4, "SVDQuant checkpoints are 4-bit"
+    if packed.is_cuda:
+        import ctypes as C
+
+        from ... import _lib as L
+
+        lib = L.lib()
+        lib.nb_layout_unpack_weight.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_void_p]
+        assert n % 128 == 0 and k % 128 == 0, f"n ({n}) and k ({k}) must be multiples of 128"
+        src = packed.contiguous()
+        assert src.numel() * src.element_size() == n * k // 2
+        out = torch.empty(n, k // 2, dtype=torch.uint8, device=packed.device)
+        with torch.cuda.device(packed.device):
+            L.check(lib.nb_layout_unpack_weight(L.ptr(src), L.ptr(out), n, k, out.stride(0), L.stream_of(out)),
+                    "unpack_weight_packed_nibbles")
+        return out
     codes = unpack_weight(packed, n, k, bits)
     return (codes[:, 0::2] | (codes[:, 1::2] << 4)).to(torch.uint8)
 

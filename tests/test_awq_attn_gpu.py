@@ -54,6 +54,33 @@ def test_awq_gemv(cuda_dev, dtype, m, n, k):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k,group", [(40, 384, 256, 128), (300, 1000, 512, 64), (129, 132, 64, 64), (1024, 4096, 1024, 128)])
+def test_awq_gemm_kernel(cuda_dev, dtype, m, n, k, group):
+    """The one-kernel W4A16 GEMM against ``x @ T(q * s + z)^T`` in fp32 (reference: awq.py:232-251), tails included."""
+    from nunchaku_rocm_b200.ops.triton.awq import awq_gemm_w4a16
+
+    g = torch.Generator().manual_seed(m + n + k)
+    q = torch.randint(0, 16, (n, k), dtype=torch.int32, generator=g)
+    s = (torch.rand(k // group, n, generator=g) * 0.1 + 0.01).to(dtype)
+    z = (torch.randn(k // group, n, generator=g) * 0.1).to(dtype)
+    x = torch.randn(m, k, generator=g).to(dtype)
+    packed = awq_attn.awq_pack(q)
+    canvas = torch.full((m + 2, n), 7.0, dtype=dtype, device=cuda_dev)  # (the op allocates its own output; canary for the view below)
+    out = awq_gemm_w4a16(x.to(cuda_dev), packed.to(cuda_dev), s.to(cuda_dev), z.to(cuda_dev), group)
+    assert out.shape == (m, n) and (canvas == 7.0).all()
+    w = awq_attn.awq_dequant(packed, s, z, n, k, group).to(dtype).float()  # the weight as the kernel rounds it
+    ref = x.float() @ w.T
+    eps = 2.0**-8 if dtype == torch.bfloat16 else 2.0**-11
+    # one rounding of the fp32 sum to the 16-bit dtype, plus the order of the fp32 additions
+    assert ((out.float().cpu() - ref).abs() <= eps * ref.abs() + 1e-3 * ref.abs().max()).all()
+    # a strided activation view (rows 16-byte aligned) goes through the same kernel
+    xx = torch.zeros(m, k + 8, dtype=dtype, device=cuda_dev)
+    xx[:, :k] = x.to(cuda_dev)
+    out2 = awq_gemm_w4a16(xx[:, :k], packed.to(cuda_dev), s.to(cuda_dev), z.to(cuda_dev), group)
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_awq_gemm_and_linear(cuda_dev, dtype):
     from nunchaku_rocm_b200.models.linear import AWQW4A16Linear
     from nunchaku_rocm_b200.ops.dispatch import gemm_awq

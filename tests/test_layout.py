@@ -1,6 +1,7 @@
 """The checkpoint-layout converter against fixtures produced by the reference's packer and its inverse
 (tests/golden/make_golden.py; reference tests: tests/triton/test_layout.py:20-66)."""
 
+import pytest
 import torch
 
 from nunchaku_rocm_b200.ops.triton import layout
@@ -73,3 +74,21 @@ def test_convert_linear_round_trip():
         assert _eq(lin.proj_down.data, down) and _eq(lin.proj_up.data, up)
         if precision == "nvfp4":
             assert _eq(lin.wcscales.data, wcs)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,k", [(128, 128), (384, 256), (3072, 3072)])
+def test_weight_layout_kernel_matches_index_formula(n, k):
+    """The device kernel (one word permutation per 128 x 64 block) against the index formula run by torch on the host."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    g = torch.Generator().manual_seed(n + k)
+    stored = torch.randint(-128, 128, (n, k // 2), dtype=torch.int8, generator=g)
+    want = layout.unpack_weight_packed_nibbles(stored, n, k)  # host: gather by formula
+    got = layout.unpack_weight_packed_nibbles(stored.cuda(), n, k)
+    assert got.is_cuda and got.dtype == torch.uint8 and got.shape == (n, k // 2)
+    assert torch.equal(got.cpu(), want)
+    # and it inverts the forward direction (pack_weight)
+    codes = torch.randint(0, 16, (n, k), dtype=torch.int32, generator=g)
+    nat = layout.unpack_weight_packed_nibbles(layout.pack_weight(codes).cuda(), n, k).cpu().to(torch.int32)
+    assert torch.equal(nat & 0xF, codes[:, 0::2]) and torch.equal(nat >> 4, codes[:, 1::2])
