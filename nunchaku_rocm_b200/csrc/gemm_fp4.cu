@@ -164,7 +164,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     const int total = MT * NT;
     const int per = (total + gridDim.x - 1) / gridDim.x;
     const int t_begin = min(total, (int)blockIdx.x * per), t_end = min(total, t_begin + per);
-    const int KS = p.K / KSTAGE;      // ring stages of the main loop per tile
+    const int KS = (p.K + KSTAGE - 1) / KSTAGE;  // ring stages of the main loop per tile (the last one may hold fewer than four 64-k steps)
     const int KS4 = p.K / 64;         // 64-k steps (scale chunks) per row block
     const int LCH = (p.R + 31) / 32;  // low-rank stages per tile (32 ranks each)
 
@@ -186,14 +186,16 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     // position in the old order (K loop first): j < KS is a K-loop stage, else low-rank stage j - KS
                     const int j = NH == 1 ? jj : (jj < LCH ? KS + jj : (jj < LCH + KS ? jj - LCH : jj));
                     if (j < KS) {
-                        mbar_expect_tx(bar(B_FULL + s), ST_BYTES);
+                        // codes beyond K are zero-filled by TMA (and never multiplied); scale chunks exist for whole 64-k steps only
+                        const uint32_t nst = (uint32_t)min(4, KS4 - 4 * j);
+                        mbar_expect_tx(bar(B_FULL + s), ST_A + ST_W + nst * 512u * (1 + NH));
                         tma_load_2d(dst, &tm_a, bar(B_FULL + s), j * 128, mt * BM);
                         tma_load_2d(dst + ST_A, &tm_w, bar(B_FULL + s), j * 128, nt * BN);
-                        bulk_load_1d(dst + ST_A + ST_W, p.sfa + ((size_t)mt * KS4 + j * 4) * 512, C::ST_SFA, bar(B_FULL + s));
+                        bulk_load_1d(dst + ST_A + ST_W, p.sfa + ((size_t)mt * KS4 + j * 4) * 512, nst * 512u, bar(B_FULL + s));
 #pragma unroll
                         for (int hh = 0; hh < NH; ++hh)
                             bulk_load_1d(dst + ST_A + ST_W + C::ST_SFA + hh * 2048,
-                                         p.sfb + ((size_t)(nt * NH + hh) * KS4 + j * 4) * 512, 2048, bar(B_FULL + s));
+                                         p.sfb + ((size_t)(nt * NH + hh) * KS4 + j * 4) * 512, nst * 512u, bar(B_FULL + s));
                     } else {
                         const int h = (j - KS) / LCH, c = (j - KS) % LCH;
                         mbar_expect_tx(bar(B_FULL + s), 2 * 128 * 64);
@@ -252,8 +254,10 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     const uint32_t a_addr = s_base + s * ST_BYTES;
                     const uint64_t da = desc_sw128(a_addr), dw = desc_sw128(a_addr + ST_A);
                     const uint32_t sfa_s = a_addr + ST_A + ST_W, sfb_s = sfa_s + C::ST_SFA;
+                    const int nst = min(4, KS4 - 4 * j);
 #pragma unroll
                     for (int st = 0; st < 4; ++st) {
+                        if (st >= nst) break;
                         // this step's scale chunks -> tensor memory, then the MMA that reads them (issue order is kept):
                         // four columns for the 128 rows of A, four per 128 rows of W
                         const uint32_t tsf = tmem_base + TM_SF + (it % C::SF_BUFS) * (4 * C::SF_STEP) + st * C::SF_STEP;
@@ -504,7 +508,7 @@ const char* tc_fp4_unsupported_reason(const nb_gemm_args* a, const void* epi, in
     (void)epi;
     if (!a->fp4) return "not NVFP4";
     if (epi_kind != NB_EPI_STORE || a->fuse_silu) return "epilogue";
-    if (a->K % fp4::KSTAGE || a->N % 8 || a->M < 1) return "K % 256, N % 8";
+    if (a->K % 64 || a->N % 8 || a->M < 1) return "K % 64, N % 8";
     if (!aligned16(a->act) || !aligned16(a->wgt) || a->stride_am % 16 || a->stride_wn % 16) return "act / wgt alignment";
     if (!a->out || !aligned16(a->out) || a->stride_om % 8) return "out alignment";
     if (a->bias && (reinterpret_cast<uintptr_t>(a->bias) & 1)) return "bias alignment";

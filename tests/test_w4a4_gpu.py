@@ -401,6 +401,8 @@ def test_gemm_fp4_wcscales_alpha(cuda_dev, dtype):
     (128, 128, 256, 0), (200, 264, 512, 32), (384, 640, 1024, 16), (130, 136, 768, 48),
     # N % 256 == 0 or N >= 2048: the 128 x 256 tile (low-rank slot served per 128-column half, ragged last tile)
     (128, 256, 256, 0), (300, 512, 512, 32), (257, 768, 1024, 80), (130, 2056, 512, 16),
+    # K % 256 != 0: the last ring stage holds one, two or three 64-k steps
+    (200, 264, 64, 16), (130, 512, 320, 32), (384, 640, 448, 0), (129, 256, 1216, 16),
 ])
 def test_gemm_fp4_shapes_lora_bias(cuda_dev, dtype, impl, M, N, K, R):
     Kn = _ops()
@@ -434,20 +436,20 @@ def test_library_selftest(cuda_dev):
 
 
 def test_gemm_fp4_tensor_core_kernel_is_selected(cuda_dev):
-    # the shapes above with K % 256 == 0 must run on the block-scaled kernel, not silently on the generic one
+    # the shapes above (K % 64 == 0) must run on the block-scaled kernel, not silently on the generic one
     import ctypes as C
 
     from nunchaku_rocm_b200 import _lib as L
     from nunchaku_rocm_b200.ops.triton.gemm_w4a4 import _gemm_args
 
-    M, N, K = 256, 256, 512
-    act = torch.zeros(M, K // 2, dtype=torch.uint8, device=cuda_dev)
-    wgt = torch.zeros(N, K // 2, dtype=torch.uint8, device=cuda_dev)
-    asc = torch.zeros(K // 16, M, dtype=torch.float8_e4m3fn, device=cuda_dev)
-    wsc = torch.zeros(K // 16, N, dtype=torch.float8_e4m3fn, device=cuda_dev)
-    out = torch.empty(M, N, dtype=torch.bfloat16, device=cuda_dev)
-    a = _gemm_args(act, wgt, out, asc, wsc, None, None, None, None, False, False, True, 1.0, torch.bfloat16, L.IMPL_AUTO)
-    assert L.lib().nb_gemm_w4a4_uses_tcgen05(C.byref(a), None, L.EPI_STORE) == 1
+    for M, N, K in [(256, 256, 512), (130, 512, 320)]:
+        act = torch.zeros(M, K // 2, dtype=torch.uint8, device=cuda_dev)
+        wgt = torch.zeros(N, K // 2, dtype=torch.uint8, device=cuda_dev)
+        asc = torch.zeros(K // 16, M, dtype=torch.float8_e4m3fn, device=cuda_dev)
+        wsc = torch.zeros(K // 16, N, dtype=torch.float8_e4m3fn, device=cuda_dev)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=cuda_dev)
+        a = _gemm_args(act, wgt, out, asc, wsc, None, None, None, None, False, False, True, 1.0, torch.bfloat16, L.IMPL_AUTO)
+        assert L.lib().nb_gemm_w4a4_uses_tcgen05(C.byref(a), None, L.EPI_STORE) == 1
 
 
 # ------------------------------------------------------------------------------------------------
