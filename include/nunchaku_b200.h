@@ -213,6 +213,24 @@ int nb_awq_gemm(const void* x, const void* kernel, const void* scales, const voi
                 int64_t stride_om, int32_t dtype, void* stream);
 
 /*
+ * The element-wise steps around the quantised linears of a DiT block, one pass over HBM each, rounded to the 16-bit
+ * dtype at the points where the reference's operator sequence rounds.  The reference runs them as torch operators (LayerNorm, broadcast multiply, broadcast add):
+ * AdaLayerNormZero (nunchaku/models/normalization.py:60-159) and the gated residuals of the blocks
+ * (nunchaku/models/transformers/transformer_flux_v2.py:174-343).
+ *   nb_layernorm_modulate: out[r] = LayerNorm(x[r]) * (scale[b] + scale_add) + shift[b], b = r / rows_per_batch;
+ *                          dim in {1024, 2048, 3072, 4096} (else NB_ERR_UNSUPPORTED)
+ *   nb_gated_residual:     out[r] = x[r] + gate[b] * (y[r] + y2[r])   (y2 may be null)
+ * Row strides in elements; scale / shift / gate are (batch, dim) views: `stride_*b` elements between batches,
+ * `stride_*d` between channels (they are columns of the modulation linear's interleaved output).
+ */
+int nb_layernorm_modulate(const void* x, const void* scale, const void* shift, void* out, int32_t rows,
+                          int32_t rows_per_batch, int32_t dim, int64_t stride_xr, int64_t stride_or, int64_t stride_sb,
+                          int64_t stride_sd, float scale_add, float eps, int32_t dtype, void* stream);
+int nb_gated_residual(const void* x, const void* gate, const void* y, const void* y2, void* out, int32_t rows,
+                      int32_t rows_per_batch, int32_t dim, int64_t stride_xr, int64_t stride_yr, int64_t stride_y2r,
+                      int64_t stride_or, int64_t stride_gb, int64_t stride_gd, int32_t dtype, void* stream);
+
+/*
  * Checkpoint layout converter for the 4-bit weight: the stored fragment order of a SVDQuant checkpoint
  * ((n, k/2) bytes viewed as int32 words) -> natural packed nibbles (n, k/2), even k in the low nibble.
  * Replaces `unpack_weight_packed_nibbles` (nunchaku/ops/triton/layout.py:36-118; inverse of

@@ -59,7 +59,10 @@ static Kernel choose_kernel(const nb_gemm_args* a, const void* epi, int epi_kind
     *why = nullptr;
     if (a->impl == NB_IMPL_GENERIC) return K_GENERIC;
     if (a->fp4) {
-        *why = tc_fp4_unsupported_reason(a, epi, epi_kind);
+        // The block-scaled kernel stores 16-bit tiles only.  A Q/K epilogue on an NVFP4 call runs as that kernel plus the
+        // row kernel in place on the stored tile: the reference's unfused form (gemm_w4a4.py:834-866), i.e. with the
+        // tile rounded to the 16-bit dtype before RMSNorm + RoPE.
+        *why = tc_fp4_unsupported_reason(a, epi, epi_kind == NB_EPI_QK_NORM_ROPE ? NB_EPI_STORE : epi_kind);
         return *why ? K_GENERIC : K_TC_FP4;
     }
     const char* single = tc_unsupported_reason(a, epi, epi_kind);
@@ -150,7 +153,12 @@ extern "C" int nb_gemm_w4a4(const nb_gemm_args* a, const void* epi, int epi_kind
     const char* reason;
     const Kernel k = choose_kernel(a, epi, epi_kind, &reason);
     if (k == K_GENERIC && a->impl != NB_IMPL_AUTO && a->impl != NB_IMPL_GENERIC) return NB_ERR_UNSUPPORTED;
-    if (k == K_TC_FP4) return launch_tc_fp4(a, s);
+    if (k == K_TC_FP4) {
+        st = launch_tc_fp4(a, s);
+        if (st == NB_OK && epi_kind == NB_EPI_QK_NORM_ROPE)
+            st = launch_qk_rows(nullptr, a->out, a->stride_om, a->actual_m, a->N, a->dtype, static_cast<const nb_qk_args*>(epi), s);
+        return st;
+    }
     if (k == K_TC_SINGLE) return launch_tc(a, epi, epi_kind, nullptr, s);
     if (k == K_TC_PAIR) return launch_tc_pair(a, epi, epi_kind, nullptr, s);
 

@@ -31,6 +31,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops.dispatch import scaled_dot_product_attention
+from ..ops.elementwise import gated_residual, layernorm_modulate
 from ..ops.fused import fused_gelu_mlp, fused_qkv_norm_rottary
 from .embeddings import flux_image_ids, flux_pos_embed
 from .linear import AWQW4A16Linear, SVDQW4A4Linear
@@ -76,11 +77,12 @@ class _AdaLayerNormZero(nn.Module):
     def forward(self, x: torch.Tensor, emb: torch.Tensor):
         e = self.linear(F.silu(emb))
         parts = e.view(e.shape[0], -1, self.n).permute(2, 0, 1)  # (n, B, dim)
-        shift_msa, scale_msa = parts[0], parts[1] + self.scale_shift
-        norm = F.layer_norm(x, (self.dim,), eps=1e-6) * scale_msa[:, None] + shift_msa[:, None]
+        # LayerNorm (no affine) * (scale + scale_shift) + shift in one pass; the second modulation's scale comes back without
+        # its scale_shift, which the block's own layernorm_modulate call adds
+        norm = layernorm_modulate(x, parts[1], parts[0], scale_add=self.scale_shift)
         if self.n == 3:
             return norm, parts[2]
-        return norm, parts[2], parts[3], parts[4] + self.scale_shift, parts[5]
+        return norm, parts[2], parts[3], parts[4], parts[5]
 
 
 class _FeedForward(nn.Module):
@@ -132,13 +134,14 @@ class FluxDoubleBlock(nn.Module):
         attn = self.to_out(attn)
         context_attn = self.to_add_out(context_attn)
 
-        hidden_states = hidden_states + gate_msa[:, None] * attn
-        norm_h = F.layer_norm(hidden_states, (cfg.hidden,), eps=1e-6) * scale_mlp[:, None] + shift_mlp[:, None]
-        hidden_states = hidden_states + gate_mlp[:, None] * self.ff(norm_h)
+        ss = self.norm1.scale_shift
+        hidden_states = gated_residual(hidden_states, gate_msa, attn)
+        norm_h = layernorm_modulate(hidden_states, scale_mlp, shift_mlp, scale_add=ss)
+        hidden_states = gated_residual(hidden_states, gate_mlp, self.ff(norm_h))
 
-        encoder_hidden_states = encoder_hidden_states + c_gate_msa[:, None] * context_attn
-        norm_e = F.layer_norm(encoder_hidden_states, (cfg.hidden,), eps=1e-6) * c_scale_mlp[:, None] + c_shift_mlp[:, None]
-        encoder_hidden_states = encoder_hidden_states + c_gate_mlp[:, None] * self.ff_context(norm_e)
+        encoder_hidden_states = gated_residual(encoder_hidden_states, c_gate_msa, context_attn)
+        norm_e = layernorm_modulate(encoder_hidden_states, c_scale_mlp, c_shift_mlp, scale_add=ss)
+        encoder_hidden_states = gated_residual(encoder_hidden_states, c_gate_mlp, self.ff_context(norm_e))
         return encoder_hidden_states, hidden_states
 
 
@@ -160,7 +163,7 @@ class FluxSingleBlock(nn.Module):
         mlp = fused_gelu_mlp(norm_h, self.mlp_fc1, self.mlp_fc2)
         qkv = fused_qkv_norm_rottary(norm_h, self.to_qkv, self.norm_q, self.norm_k, rotary)
         attn = self.to_out(_attention(qkv, self.cfg))
-        return residual + gate[:, None] * (attn + mlp)
+        return gated_residual(residual, gate, attn, mlp)
 
 
 def _attention(qkv: torch.Tensor, cfg: FluxDiTConfig) -> torch.Tensor:
@@ -257,7 +260,7 @@ class FluxDiT(nn.Module):
             hidden_states = block(hidden_states, temb, rot_all)
         hidden_states = hidden_states[:, n_txt:]
         scale, shift = self.norm_out_linear(F.silu(temb)).chunk(2, dim=1)
-        hidden_states = F.layer_norm(hidden_states, (cfg.hidden,), eps=1e-6) * (1 + scale)[:, None] + shift[:, None]
+        hidden_states = layernorm_modulate(hidden_states, scale, shift, scale_add=1.0)
         return self.proj_out(hidden_states)
 
 

@@ -19,13 +19,15 @@ random tensors of the benchmark configuration's format; there are no checkpoints
 from __future__ import annotations
 
 from dataclasses import dataclass
+from types import SimpleNamespace
 
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops.dispatch import scaled_dot_product_attention
-from ..ops.fused import fused_gelu_mlp
+from ..ops.elementwise import gated_residual, layernorm_modulate
+from ..ops.fused import fused_gelu_mlp, fused_qkv_norm_rottary
 from .linear import AWQW4A16Linear, SVDQW4A4Linear
 
 
@@ -51,6 +53,14 @@ def _rotate(x: torch.Tensor, freqs: torch.Tensor) -> torch.Tensor:
     """``apply_rotary_emb_qwen(..., use_real=False)``: channel pairs as complex numbers times ``freqs (S, D/2)`` complex."""
     xc = torch.view_as_complex(x.float().reshape(*x.shape[:-1], -1, 2))
     return torch.view_as_real(xc * freqs[None, :, None, :]).flatten(3).to(x.dtype)
+
+
+def rotary_table(freqs: torch.Tensor) -> torch.Tensor:
+    """Complex unit rotations ``(S, D / 2)`` as the fp32 ``(S, D / 2, 1, 2)`` table of (sin, cos) pairs that the fused
+    Q/K epilogue reads (a table already in that form passes through)."""
+    if not freqs.is_complex():
+        return freqs
+    return torch.stack([freqs.imag, freqs.real], dim=-1)[:, :, None, :].float().contiguous()
 
 
 class _Modulation(nn.Module):
@@ -90,33 +100,40 @@ class QwenBlock(nn.Module):
 
     @staticmethod
     def _modulate(x, mod):
+        """LayerNorm (no affine) of ``x``, ``* (1 + scale) + shift`` in one pass; returns it and the gate ``(B, dim)``."""
         shift, scale, gate = mod.chunk(3, dim=-1)
-        return x * (scale + 1.0)[:, None] + shift[:, None], gate[:, None]
+        return layernorm_modulate(x, scale, shift, scale_add=1.0), gate
 
     def forward(self, hidden_states, encoder_hidden_states, temb, img_freqs, txt_freqs):
         cfg = self.cfg
         B, S_img, C = hidden_states.shape
         S_txt = encoder_hidden_states.shape[1]
+        img_freqs, txt_freqs = rotary_table(img_freqs), rotary_table(txt_freqs)  # (no-op when the model already did it)
         img_mod1, img_mod2 = self.img_mod(temb)
         txt_mod1, txt_mod2 = self.txt_mod(temb)
-        img_m, img_gate1 = self._modulate(F.layer_norm(hidden_states, (C,), eps=1e-6), img_mod1)
-        txt_m, txt_gate1 = self._modulate(F.layer_norm(encoder_hidden_states, (C,), eps=1e-6), txt_mod1)
+        img_m, img_gate1 = self._modulate(hidden_states, img_mod1)
+        txt_m, txt_gate1 = self._modulate(encoder_hidden_states, txt_mod1)
 
-        iq, ik, iv = (t.unflatten(-1, (cfg.heads, -1)) for t in self.to_qkv(img_m).chunk(3, dim=-1))
-        tq, tk, tv = (t.unflatten(-1, (cfg.heads, -1)) for t in self.add_qkv_proj(txt_m).chunk(3, dim=-1))
-        iq, ik = _rotate(_rms(iq, self.norm_q), img_freqs), _rotate(_rms(ik, self.norm_k), img_freqs)
-        tq, tk = _rotate(_rms(tq, self.norm_added_q), txt_freqs), _rotate(_rms(tk, self.norm_added_k), txt_freqs)
-        q, k, v = torch.cat([tq, iq], dim=1), torch.cat([tk, ik], dim=1), torch.cat([tv, iv], dim=1)  # (B, S, H, D)
-        attn = scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2)
-        attn = attn.flatten(2, 3)
-        txt_attn, img_attn = self.to_add_out(attn[:, :S_txt].contiguous()), self.to_out(attn[:, S_txt:].contiguous())
+        # joint attention over [text; image]: both projections write their rows of one buffer, per-head RMSNorm + RoPE of
+        # Q and K run in the projection's epilogue
+        nq, nk, naq, nak = (SimpleNamespace(weight=w) for w in (self.norm_q, self.norm_k, self.norm_added_q, self.norm_added_k))
+        if B == 1:
+            qkv = torch.empty(1, S_txt + S_img, 3 * C, dtype=hidden_states.dtype, device=hidden_states.device)
+            fused_qkv_norm_rottary(txt_m, self.add_qkv_proj, naq, nak, txt_freqs, output=qkv[0, :S_txt])
+            fused_qkv_norm_rottary(img_m, self.to_qkv, nq, nk, img_freqs, output=qkv[0, S_txt:])
+        else:
+            qkv = torch.cat([fused_qkv_norm_rottary(txt_m, self.add_qkv_proj, naq, nak, txt_freqs),
+                             fused_qkv_norm_rottary(img_m, self.to_qkv, nq, nk, img_freqs)], dim=1)
+        q, k, v = (t.view(B, S_txt + S_img, cfg.heads, cfg.head_dim).transpose(1, 2) for t in qkv.chunk(3, dim=-1))
+        attn = scaled_dot_product_attention(q, k, v).transpose(1, 2).flatten(2, 3)  # (B, S, H D)
+        txt_attn, img_attn = self.to_add_out(attn[:, :S_txt]), self.to_out(attn[:, S_txt:])
 
-        hidden_states = hidden_states + img_gate1 * img_attn
-        encoder_hidden_states = encoder_hidden_states + txt_gate1 * txt_attn
-        img_m2, img_gate2 = self._modulate(F.layer_norm(hidden_states, (C,), eps=1e-6), img_mod2)
-        hidden_states = hidden_states + img_gate2 * self.img_mlp(img_m2)
-        txt_m2, txt_gate2 = self._modulate(F.layer_norm(encoder_hidden_states, (C,), eps=1e-6), txt_mod2)
-        encoder_hidden_states = encoder_hidden_states + txt_gate2 * self.txt_mlp(txt_m2)
+        hidden_states = gated_residual(hidden_states, img_gate1, img_attn)
+        encoder_hidden_states = gated_residual(encoder_hidden_states, txt_gate1, txt_attn)
+        img_m2, img_gate2 = self._modulate(hidden_states, img_mod2)
+        hidden_states = gated_residual(hidden_states, img_gate2, self.img_mlp(img_m2))
+        txt_m2, txt_gate2 = self._modulate(encoder_hidden_states, txt_mod2)
+        encoder_hidden_states = gated_residual(encoder_hidden_states, txt_gate2, self.txt_mlp(txt_m2))
         return encoder_hidden_states, hidden_states
 
 
@@ -181,10 +198,11 @@ class QwenDiT(nn.Module):
         h = self.img_in(hidden_states)
         e = self.txt_in(encoder_hidden_states)
         temb = self.time_in(_timestep_embedding(timestep * 1000.0).to(cfg.dtype))
+        img_freqs, txt_freqs = rotary_table(img_freqs), rotary_table(txt_freqs)
         for blk in self.blocks:
             e, h = blk(h, e, temb, img_freqs, txt_freqs)
         scale, shift = self.norm_out_linear(F.silu(temb)).chunk(2, dim=1)
-        h = F.layer_norm(h, (cfg.hidden,), eps=1e-6) * (1 + scale)[:, None] + shift[:, None]
+        h = layernorm_modulate(h, scale, shift, scale_add=1.0)
         return self.proj_out(h)
 
 
