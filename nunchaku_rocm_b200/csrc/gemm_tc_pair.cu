@@ -234,6 +234,10 @@ __device__ __forceinline__ void mma_sync_16816(float (&d)[4], const uint32_t (&a
 // gives 64 of them back (setmaxnreg.dec to 32: 8192 registers into the CTA's pool) and the four drain warp groups grow to
 // 112 (setmaxnreg.inc: 8192 registers out of that pool).  (576 threads at 112 registers do not launch: the fifth warp
 // group is charged in full.)  The host refuses to launch if the compiled kernel does not start with exactly 96 registers.
+// 128-bit shared-memory load as two 64-bit registers (pairs of fp32 for the packed operations)
+__device__ __forceinline__ void lds2x64(uint32_t addr, uint64_t& a, uint64_t& b) {
+    asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "r"(addr));
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {  // shared-memory load by 32-bit address: no 64-bit pointer kept live
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -461,14 +465,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     for (int lb = 0; lb < 2; ++lb) {
                         uint32_t v[16];
                         tmem_ld_16x256b_x4(taddr + ((uint32_t)(lb * 16) << 16) + ch * 32, v);
-                        // the scales are fetched while the chunk is on its way: shared memory answers slowly while the tensor
-                        // cores read their operands from it
-                        const uint4 a4 = lds128(st + as_off + lb * 128);
-                        const uint64_t ap[2] = {pack_u32x2(a4.x, a4.y), pack_u32x2(a4.z, a4.w)};
+                        // the scales are fetched while the chunk is on its way (shared memory answers slowly while the tensor
+                        // cores read their operands from it), as 64-bit pairs: the form the packed arithmetic takes
+                        uint64_t ap[2];
+                        lds2x64(st + as_off + lb * 128, ap[0], ap[1]);
                         if (lb == 0) {
-                            const uint4 w0 = lds128(st + ws_off + ch * 128), w1 = lds128(st + ws_off + ch * 128 + 16);
-                            wp[0] = pack_u32x2(w0.x, w0.y); wp[1] = pack_u32x2(w0.z, w0.w);
-                            wp[2] = pack_u32x2(w1.x, w1.y); wp[3] = pack_u32x2(w1.z, w1.w);
+                            lds2x64(st + ws_off + ch * 128, wp[0], wp[1]);
+                            lds2x64(st + ws_off + ch * 128 + 16, wp[2], wp[3]);
                         }
                         tmem_wait_ld();  // (warp-wide: every lane's values have landed)
                         if (ch == 1 && lb == 1) {
