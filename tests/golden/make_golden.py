@@ -198,4 +198,6 @@ def main(root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <checkout of the reference repository>")
+    main(sys.argv[1])

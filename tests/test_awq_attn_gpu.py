@@ -94,7 +94,7 @@ def test_awq_gemm_and_linear(cuda_dev, dtype):
     packed = awq_attn.awq_pack(q)
     out = gemm_awq(x.to(cuda_dev), packed.to(cuda_dev), s128.to(cuda_dev), z128.to(cuda_dev))
     ref = x.float() @ awq_attn.awq_dequant(packed, s128, z128, n, k, 128).float().T
-    # 16-bit weights and a 16-bit output of magnitude ~10: judge the tile as a whole
+    # 16-bit weights and a 16-bit output of magnitude ~10: assess the tile as a whole
     err = (out.float().cpu() - ref).norm() / ref.norm()
     assert err <= 1e-2, err
 
