@@ -156,7 +156,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 const int s = j & 1;
                 const uint32_t par = ((j >> 1) & 1) ^ 1;  // parity of the stage's previous use, tile j - 2
                 // stage s is free once the MMAs of its previous use have completed: the scores' / the product's own barrier
-                if (j >= 2 && !mbar_wait(bar(B_SF + s), par, abort_s, E_PROD | 1, 500)) { ok = false; break; }
+                if (j >= 2 && !mbar_wait(bar(B_SF + s), par, abort_s, E_PROD | 1, 50)) { ok = false; break; }
                 mbar_expect_tx(bar(B_KF + s), TILE);
                 {
                     // coordinates (d, key, head, batch) in the order the tensor map sorted the outer dimensions by stride
@@ -166,7 +166,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     tma_load_4d(s_base + OFF_K + s * TILE, &tm_k, bar(B_KF + s), 0, c[1], c[2], c[3]);
                     tma_load_4d(s_base + OFF_K + s * TILE + TILE / 2, &tm_k, bar(B_KF + s), 64, c[1], c[2], c[3]);
                 }
-                if (j >= 2 && !mbar_wait(bar(B_PV + s), par, abort_s, E_PROD | 2, 500)) { ok = false; break; }
+                if (j >= 2 && !mbar_wait(bar(B_PV + s), par, abort_s, E_PROD | 2, 50)) { ok = false; break; }
                 mbar_expect_tx(bar(B_VF + s), TILE);
                 tma_load_2d(s_base + OFF_V + s * TILE, &tm_v, bar(B_VF + s), j * BN, bh * HD);
                 tma_load_2d(s_base + OFF_V + s * TILE + TILE / 2, &tm_v, bar(B_VF + s), j * BN + 64, bh * HD);
@@ -182,31 +182,35 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         // The issuing thread pays ~100 cycles per tcgen05.mma and more per commit and wait, and a 128 x 128 x 16 MMA is only
         // 64 cycles of tensor work, so the two products have an issuing warp each and every descriptor is one add away
         // from a precomputed base.  A commit doubles as the "stage consumed" signal for the producer.
-        if (lane == 0) {
+        // (the loop runs as a whole warp with warp-uniform state and one elected lane issues: a loop run by one lane inside a
+        // divergent branch, and waits with a suspend-time hint, cost the issuing warps of the int4 GEMM most of their time)
+        {
             const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             const uint32_t idesc = umma_idesc(1u, fmt, fmt, 128);
-            bool ok = mbar_wait(bar(B_Q), 0, abort_s, E_MMA | 1, 100);
+            bool ok = mbar_wait_warp(bar(B_Q), 0, abort_s, E_MMA | 1);
             const uint64_t dq = desc_sw128(s_base + OFF_Q), dk0 = desc_sw128(s_base + OFF_K);
             for (int j = 0; j < NT && ok; ++j) {
                 const int b = j & 1;
                 const uint32_t par = (j >> 1) & 1;
-                if (!mbar_wait(bar(B_KF + b), par, abort_s, E_MMA | 2, 100)) { ok = false; break; }
-                if (!mbar_wait(bar(B_SE + b), par ^ 1, abort_s, E_MMA | 3, 100)) { ok = false; break; }
+                if (!mbar_wait_warp(bar(B_KF + b), par, abort_s, E_MMA | 2)) { ok = false; break; }
+                if (!mbar_wait_warp(bar(B_SE + b), par ^ 1, abort_s, E_MMA | 3)) { ok = false; break; }
                 tc_fence_after();
-                const uint64_t dk = dk0 + (uint64_t)(b * (TILE >> 4));
-                const uint32_t d = tmem_base + TM_S + b * 128;
-                // the descriptor's start-address field counts 16-byte units: +2 per 32-byte K step, +1024 per 64-wide half
+                if (elect_one()) {
+                    const uint64_t dk = dk0 + (uint64_t)(b * (TILE >> 4));
+                    const uint32_t d = tmem_base + TM_S + b * 128;
+                    // the descriptor's start-address field counts 16-byte units: +2 per 32-byte K step, +1024 per 64-wide half
 #pragma unroll
-                for (int dh = 0; dh < 2; ++dh)
+                    for (int dh = 0; dh < 2; ++dh)
 #pragma unroll
-                    for (int st = 0; st < 4; ++st)
-                        mma_f16(d, dq + dh * 1024 + st * 2, dk + dh * 1024 + st * 2, idesc, (dh || st) ? 1u : 0u);
-                tc_commit(bar(B_SF + b));
+                        for (int st = 0; st < 4; ++st)
+                            mma_f16(d, dq + dh * 1024 + st * 2, dk + dh * 1024 + st * 2, idesc, (dh || st) ? 1u : 0u);
+                    tc_commit(bar(B_SF + b));
+                }
             }
         }
     } else if (warp == 2 + SM_WARPS) {
         // ================================ MMA issuer: P V ================================
-        if (lane == 0) {
+        {
             const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             const uint32_t idesc = umma_idesc(1u, fmt, fmt, 128);
             const uint64_t dv0 = desc_sw128(s_base + OFF_V);
@@ -214,18 +218,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             for (int i = 0; i < NT && ok; ++i) {
                 const int b = i & 1;
                 const uint32_t par = (i >> 1) & 1;
-                if (!mbar_wait(bar(B_PF + b), par, abort_s, E_MMA | 4, 100)) { ok = false; break; }
-                if (!mbar_wait(bar(B_VF + b), par, abort_s, E_MMA | 5, 100)) { ok = false; break; }
+                if (!mbar_wait_warp(bar(B_PF + b), par, abort_s, E_MMA | 4)) { ok = false; break; }
+                if (!mbar_wait_warp(bar(B_VF + b), par, abort_s, E_MMA | 5)) { ok = false; break; }
                 tc_fence_after();
-                const uint64_t dv = dv0 + (uint64_t)(b * (TILE >> 4));
-                const uint32_t pa = tmem_base + TM_P + b * 64;
+                if (elect_one()) {
+                    const uint64_t dv = dv0 + (uint64_t)(b * (TILE >> 4));
+                    const uint32_t pa = tmem_base + TM_P + b * 64;
 #pragma unroll
-                for (int kh = 0; kh < 2; ++kh)
+                    for (int kh = 0; kh < 2; ++kh)
 #pragma unroll
-                    for (int st = 0; st < 4; ++st)
-                        mma_f16_ts(tmem_base + TM_O, pa + (kh * 4 + st) * 8, dv + kh * 1024 + st * 2, idesc,
-                                   (i > 0 || kh || st) ? 1u : 0u);
-                tc_commit(bar(B_PV + b));
+                        for (int st = 0; st < 4; ++st)
+                            mma_f16_ts(tmem_base + TM_O, pa + (kh * 4 + st) * 8, dv + kh * 1024 + st * 2, idesc,
+                                       (i > 0 || kh || st) ? 1u : 0u);
+                    tc_commit(bar(B_PV + b));
+                }
             }
         }
     } else {

@@ -132,62 +132,6 @@ __device__ __forceinline__ uint64_t desc_sw64(uint32_t smem_addr) {
     d |= (uint64_t)4 << 61;
     return d;
 }
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// Arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster.  What the arrival publishes is
-// "this warp's tcgen05.ld of the slot have completed", which tcgen05.wait::ld + tcgen05.fence::before_thread_sync order;
-// no generic-memory write is handed over, so the arrival carries no cluster-scope release (that form compiles to a
-// memory barrier which, once per warp and K group, was the largest stall of the kernel).
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t local_bar, uint32_t rank) {
-    asm volatile(
-        "{\n\t.reg .b32 ra;\n\tmapa.shared::cluster.u32 ra, %0, %1;\n\t"
-        "mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [ra];\n\t}"
-        ::"r"(local_bar), "r"(rank)
-        : "memory");
-}
-__device__ __forceinline__ uint32_t mapa_cluster(uint32_t local_addr, uint32_t rank) {
-    uint32_t ra;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(rank));
-    return ra;
-}
-// the same arrival on an address mapa_cluster() gave, by the threads whose `pred` is non-zero
-__device__ __forceinline__ void mbar_arrive_remote_if(uint32_t remote_bar, uint32_t pred) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %1, 0;\n\t"
-        "@p mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];\n\t}"
-        ::"r"(remote_bar), "r"(pred)
-        : "memory");
-}
-// The same with release semantics at cluster scope: the relay's "my half of the stage has landed" precedes reads of this
-// CTA's shared memory by the other SM's tensor core (one thread, once per ring stage).
-__device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t local_bar, uint32_t rank) {
-    asm volatile(
-        "{\n\t.reg .b32 ra;\n\tmapa.shared::cluster.u32 ra, %0, %1;\n\t"
-        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
-        ::"r"(local_bar), "r"(rank)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t ncols) {  // warp 1 of both CTAs
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-// completion of every MMA issued so far -> one arrival on the barrier at this offset in both CTAs
-__device__ __forceinline__ void tc_commit2(uint32_t bar) {
-    asm volatile(
-        "{\n\t.reg .b16 m;\n\tmov.b16 m, 3;\n\t"
-        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}"
-        ::"r"(bar)
-        : "memory");
-}
 // ACC = 0 overwrites the accumulator, 1 adds to it
 template <int ACC>
 __device__ __forceinline__ void mma2_f8(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
@@ -209,12 +153,6 @@ __device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) {
     uint64_t d;
     asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
     return d;
-}
-// one lane of the (converged) warp
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
-    return pred != 0;
 }
 // D (16 x 8, fp32) += A (16 x 16, row) * B (16 x 8, col), 16-bit operands: the legacy warp-level MMA, used for the small
 // LoRA-down product whose A operand is already in the accumulator registers in exactly this fragment layout
