@@ -181,7 +181,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 // half, the K loop, then the low-rank K loop of the second half (the issuer consumes them in this order)
                 for (int jj = 0; jj < KS + NH * LCH; ++jj, ++it) {
                     const int s = it % STAGES;
-                    if (!mbar_wait(bar(B_EMPTY + s), ((it / STAGES) & 1) ^ 1, abort_s, E_PROD | 1, 500)) { ok = false; break; }
+                    if (!mbar_wait(bar(B_EMPTY + s), ((it / STAGES) & 1) ^ 1, abort_s, E_PROD | 1, 50)) { ok = false; break; }
                     const uint32_t dst = s_base + s * ST_BYTES;
                     // position in the old order (K loop first): j < KS is a K-loop stage, else low-rank stage j - KS
                     const int j = NH == 1 ? jj : (jj < LCH ? KS + jj : (jj < LCH + KS ? jj - LCH : jj));
@@ -217,7 +217,8 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         }
     } else if (warp == 1) {
         // ================================ MMA issuer ================================
-        if (lane == 0) {
+        // (the loop runs as a whole warp with warp-uniform state and one elected lane issues; waits carry no suspend-time hint)
+        {
             const uint32_t idesc = idesc_mxf4nvf4(BN);
             const uint32_t f16fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             const uint32_t idesc_lr = umma_idesc(1u, f16fmt, f16fmt, 128);
@@ -228,48 +229,52 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 const uint32_t d = tmem_base + TM_ACC + slot * BN;
                 // low-rank product of one 128-column half into the single low-rank slot
                 auto low_rank_half = [&]() {
-                    if (!mbar_wait(bar(B_LR_EMPTY), (lrn & 1) ^ 1, abort_s, E_MMA | 3, 100)) return false;  // previous contents read
+                    if (!mbar_wait_warp(bar(B_LR_EMPTY), (lrn & 1) ^ 1, abort_s, E_MMA | 3)) return false;  // previous contents read
                     for (int c = 0; c < LCH; ++c, ++it) {
                         const int s = it % STAGES;
-                        if (!mbar_wait(bar(B_FULL + s), (it / STAGES) & 1, abort_s, E_MMA | 4, 100)) return false;
+                        if (!mbar_wait_warp(bar(B_FULL + s), (it / STAGES) & 1, abort_s, E_MMA | 4)) return false;
                         tc_fence_after();
-                        const uint32_t a_addr = s_base + s * ST_BYTES, w_addr = a_addr + ST_A;
+                        if (elect_one()) {
+                            const uint32_t a_addr = s_base + s * ST_BYTES, w_addr = a_addr + ST_A;
 #pragma unroll
-                        for (int kk = 0; kk < 2; ++kk)
-                            mma_f16(tmem_base + TM_LORA, desc_sw64(a_addr + kk * 32), desc_sw64(w_addr + kk * 32), idesc_lr,
-                                    (c | kk) ? 1u : 0u);
-                        tc_commit(bar(B_EMPTY + s));
+                            for (int kk = 0; kk < 2; ++kk)
+                                mma_f16(tmem_base + TM_LORA, desc_sw64(a_addr + kk * 32), desc_sw64(w_addr + kk * 32), idesc_lr,
+                                        (c | kk) ? 1u : 0u);
+                            tc_commit(bar(B_EMPTY + s));
+                        }
                     }
-                    tc_commit(bar(B_LR_FULL));
+                    if (elect_one()) tc_commit(bar(B_LR_FULL));
                     ++lrn;
                     return true;
                 };
                 // wide tile: the first half's product goes first; its slot and the accumulator were released together
                 if (LCH > 0 && NH == 2 && !low_rank_half()) { ok = false; break; }
-                if (!mbar_wait(bar(B_ACC_EMPTY + slot), ((tl / ACC_SLOTS) & 1) ^ 1, abort_s, E_MMA | 2, 100)) { ok = false; break; }
+                if (!mbar_wait_warp(bar(B_ACC_EMPTY + slot), ((tl / ACC_SLOTS) & 1) ^ 1, abort_s, E_MMA | 2)) { ok = false; break; }
                 for (int j = 0; j < KS && ok; ++j, ++it) {
                     const int s = it % STAGES;
-                    if (!mbar_wait(bar(B_FULL + s), (it / STAGES) & 1, abort_s, E_MMA | 1, 100)) { ok = false; break; }
+                    if (!mbar_wait_warp(bar(B_FULL + s), (it / STAGES) & 1, abort_s, E_MMA | 1)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = s_base + s * ST_BYTES;
-                    const uint64_t da = desc_sw128(a_addr), dw = desc_sw128(a_addr + ST_A);
-                    const uint32_t sfa_s = a_addr + ST_A + ST_W, sfb_s = sfa_s + C::ST_SFA;
-                    const int nst = min(4, KS4 - 4 * j);
+                    if (elect_one()) {
+                        const uint32_t a_addr = s_base + s * ST_BYTES;
+                        const uint64_t da = desc_sw128(a_addr), dw = desc_sw128(a_addr + ST_A);
+                        const uint32_t sfa_s = a_addr + ST_A + ST_W, sfb_s = sfa_s + C::ST_SFA;
+                        const int nst = min(4, KS4 - 4 * j);
 #pragma unroll
-                    for (int st = 0; st < 4; ++st) {
-                        if (st >= nst) break;
-                        // this step's scale chunks -> tensor memory, then the MMA that reads them (issue order is kept):
-                        // four columns for the 128 rows of A, four per 128 rows of W
-                        const uint32_t tsf = tmem_base + TM_SF + (it % C::SF_BUFS) * (4 * C::SF_STEP) + st * C::SF_STEP;
-                        tmem_cp_32x128b_warpx4(tsf, umma_desc_kmajor(sfa_s + st * 512, 16, 128));
+                        for (int st = 0; st < 4; ++st) {
+                            if (st >= nst) break;
+                            // this step's scale chunks -> tensor memory, then the MMA that reads them (issue order is kept):
+                            // four columns for the 128 rows of A, four per 128 rows of W
+                            const uint32_t tsf = tmem_base + TM_SF + (it % C::SF_BUFS) * (4 * C::SF_STEP) + st * C::SF_STEP;
+                            tmem_cp_32x128b_warpx4(tsf, umma_desc_kmajor(sfa_s + st * 512, 16, 128));
 #pragma unroll
-                        for (int hh = 0; hh < NH; ++hh)
-                            tmem_cp_32x128b_warpx4(tsf + 4 + 4 * hh, umma_desc_kmajor(sfb_s + (hh * 4 + st) * 512, 16, 128));
-                        mma_mxf4nvf4(d, da + 2 * st, dw + 2 * st, idesc, tsf, tsf + 4, (j | st) ? 1u : 0u);
+                            for (int hh = 0; hh < NH; ++hh)
+                                tmem_cp_32x128b_warpx4(tsf + 4 + 4 * hh, umma_desc_kmajor(sfb_s + (hh * 4 + st) * 512, 16, 128));
+                            mma_mxf4nvf4(d, da + 2 * st, dw + 2 * st, idesc, tsf, tsf + 4, (j | st) ? 1u : 0u);
+                        }
+                        tc_commit(bar(B_EMPTY + s));
                     }
-                    tc_commit(bar(B_EMPTY + s));
                 }
-                if (ok) tc_commit(bar(B_ACC_FULL + slot));
+                if (ok && elect_one()) tc_commit(bar(B_ACC_FULL + slot));
                 if (ok && LCH > 0 && !low_rank_half()) { ok = false; break; }
             }
         }
