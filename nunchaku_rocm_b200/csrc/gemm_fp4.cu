@@ -170,48 +170,50 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
 
     if (warp == 0) {
         // ================================ producer ================================
+        // (a whole-warp loop with warp-uniform state; one elected lane issues the copies)
         if (lane == 0) {
             tma_prefetch_desc(&tm_a); tma_prefetch_desc(&tm_w);
             if (LCH) { tma_prefetch_desc(&tm_la); tma_prefetch_desc(&tm_lu); }
-            uint32_t it = 0;
-            bool ok = true;
-            for (int t = t_begin; t < t_end && ok; ++t) {
-                const int mt = t / NT, nt = t % NT;
-                // 128 x 128: the K loop, then the low-rank K loop.  128 x 256: the low-rank K loop of the first 128-column
-                // half, the K loop, then the low-rank K loop of the second half (the issuer consumes them in this order)
-                for (int jj = 0; jj < KS + NH * LCH; ++jj, ++it) {
-                    const int s = it % STAGES;
-                    if (!mbar_wait(bar(B_EMPTY + s), ((it / STAGES) & 1) ^ 1, abort_s, E_PROD | 1, 50)) { ok = false; break; }
-                    const uint32_t dst = s_base + s * ST_BYTES;
-                    // position in the old order (K loop first): j < KS is a K-loop stage, else low-rank stage j - KS
-                    const int j = NH == 1 ? jj : (jj < LCH ? KS + jj : (jj < LCH + KS ? jj - LCH : jj));
-                    if (j < KS) {
-                        // codes beyond K are zero-filled by TMA (and never multiplied); scale chunks exist for whole 64-k steps only
-                        const uint32_t nst = (uint32_t)min(4, KS4 - 4 * j);
-                        mbar_expect_tx(bar(B_FULL + s), ST_A + ST_W + nst * 512u * (1 + NH));
-                        tma_load_2d(dst, &tm_a, bar(B_FULL + s), j * 128, mt * BM);
-                        tma_load_2d(dst + ST_A, &tm_w, bar(B_FULL + s), j * 128, nt * BN);
-                        bulk_load_1d(dst + ST_A + ST_W, p.sfa + ((size_t)mt * KS4 + j * 4) * 512, nst * 512u, bar(B_FULL + s));
+        }
+        uint32_t it = 0;
+        bool ok = true;
+        for (int t = t_begin; t < t_end && ok; ++t) {
+            const int mt = t / NT, nt = t % NT;
+            // 128 x 128: the K loop, then the low-rank K loop.  128 x 256: the low-rank K loop of the first 128-column
+            // half, the K loop, then the low-rank K loop of the second half (the issuer consumes them in this order)
+            for (int jj = 0; jj < KS + NH * LCH; ++jj, ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait_warp(bar(B_EMPTY + s), ((it / STAGES) & 1) ^ 1, abort_s, E_PROD | 1)) { ok = false; break; }
+                if (!elect_one()) continue;
+                const uint32_t dst = s_base + s * ST_BYTES;
+                // position in the old order (K loop first): j < KS is a K-loop stage, else low-rank stage j - KS
+                const int j = NH == 1 ? jj : (jj < LCH ? KS + jj : (jj < LCH + KS ? jj - LCH : jj));
+                if (j < KS) {
+                    // codes beyond K are zero-filled by TMA (and never multiplied); scale chunks exist for whole 64-k steps only
+                    const uint32_t nst = (uint32_t)min(4, KS4 - 4 * j);
+                    mbar_expect_tx(bar(B_FULL + s), ST_A + ST_W + nst * 512u * (1 + NH));
+                    tma_load_2d(dst, &tm_a, bar(B_FULL + s), j * 128, mt * BM);
+                    tma_load_2d(dst + ST_A, &tm_w, bar(B_FULL + s), j * 128, nt * BN);
+                    bulk_load_1d(dst + ST_A + ST_W, p.sfa + ((size_t)mt * KS4 + j * 4) * 512, nst * 512u, bar(B_FULL + s));
 #pragma unroll
-                        for (int hh = 0; hh < NH; ++hh)
-                            bulk_load_1d(dst + ST_A + ST_W + C::ST_SFA + hh * 2048,
-                                         p.sfb + ((size_t)(nt * NH + hh) * KS4 + j * 4) * 512, nst * 512u, bar(B_FULL + s));
-                    } else {
-                        const int h = (j - KS) / LCH, c = (j - KS) % LCH;
-                        mbar_expect_tx(bar(B_FULL + s), 2 * 128 * 64);
-                        tma_load_2d(dst, &tm_la, bar(B_FULL + s), c * 32, mt * BM);
-                        tma_load_2d(dst + ST_A, &tm_lu, bar(B_FULL + s), c * 32, nt * BN + h * 128);
-                    }
+                    for (int hh = 0; hh < NH; ++hh)
+                        bulk_load_1d(dst + ST_A + ST_W + C::ST_SFA + hh * 2048,
+                                     p.sfb + ((size_t)(nt * NH + hh) * KS4 + j * 4) * 512, nst * 512u, bar(B_FULL + s));
+                } else {
+                    const int h = (j - KS) / LCH, c = (j - KS) % LCH;
+                    mbar_expect_tx(bar(B_FULL + s), 2 * 128 * 64);
+                    tma_load_2d(dst, &tm_la, bar(B_FULL + s), c * 32, mt * BM);
+                    tma_load_2d(dst + ST_A, &tm_lu, bar(B_FULL + s), c * 32, nt * BN + h * 128);
                 }
             }
-            if (!ok) {
-                // let copies already in flight land before the CTA goes away (bounded)
-                for (int s = 0; s < STAGES; ++s) {
-                    const uint32_t issued = it > (uint32_t)s ? (it - 1 - s) / STAGES + 1 : 0;
-                    if (issued) {
-                        uint64_t t0 = globaltimer_ns();
-                        while (!mbar_try_wait(bar(B_FULL + s), (issued - 1) & 1) && globaltimer_ns() - t0 < 200000000ull) {}
-                    }
+        }
+        if (!ok && lane == 0) {
+            // let copies already in flight land before the CTA goes away (bounded)
+            for (int s = 0; s < STAGES; ++s) {
+                const uint32_t issued = it > (uint32_t)s ? (it - 1 - s) / STAGES + 1 : 0;
+                if (issued) {
+                    uint64_t t0 = globaltimer_ns();
+                    while (!mbar_try_wait(bar(B_FULL + s), (issued - 1) & 1) && globaltimer_ns() - t0 < 200000000ull) {}
                 }
             }
         }
