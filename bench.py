@@ -592,6 +592,27 @@ def flux_profile_step() -> None:
           flush=True)
 
 
+def qwen_profile_step() -> None:
+    """One eager forward of the Qwen-Image-architecture transformer (batch 1) inside a cudaProfilerStart/Stop range."""
+    from nunchaku_rocm_b200.models.qwen_dit import GraphedQwenStep, QwenDiT, QwenDiTConfig
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    with torch.no_grad():
+        model = QwenDiT(QwenDiTConfig(), device=dev).random_init(seed=100)
+        step = GraphedQwenStep(model, batch=1)  # (runs the forward eagerly twice first)
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.cudart().cudaProfilerStart()
+        e0.record()
+        out = step._forward()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        torch.cuda.cudart().cudaProfilerStop()
+    print(json.dumps({"qwen_profile_step": {"eager_forward_ms": e0.elapsed_time(e1), "finite": bool(torch.isfinite(out.float()).all())}}),
+          flush=True)
+
+
 def run_qwen(args, dev, world: int, barrier) -> dict:
     """
     Qwen-Image-architecture MMDiT with NVFP4 W4A4 layers: 60 blocks, hidden 3072, 24 x 128 heads, MLP 12288, 6889 image +
@@ -643,10 +664,15 @@ def main() -> None:
     ap.add_argument("--no-qwen", action="store_true", help="skip the Qwen-Image-architecture (NVFP4) forward measurement")
     ap.add_argument("--flux-batches", default="1,4", help="per-GPU image batches to measure")
     ap.add_argument("--flux-images", type=int, default=4, help="image batches per timed region")
+    ap.add_argument("--qwen-profile-step", action="store_true",
+                    help="the same for the Qwen-Image-architecture (NVFP4) transformer")
     ap.add_argument("--flux-profile-step", action="store_true",
                     help="run ONE eager FLUX-architecture transformer forward between cudaProfilerStart/Stop and exit "
                          "(for a profiler's launch list; prints the forward's wall time, which is not a bench value)")
     args = ap.parse_args()
+    if args.qwen_profile_step:
+        qwen_profile_step()
+        return
     if args.flux_profile_step:
         flux_profile_step()
     elif args.impl == "reference":
