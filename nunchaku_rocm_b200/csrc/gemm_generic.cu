@@ -177,20 +177,30 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(const GenericParams p
 }
 
 // ---- per-head RMSNorm + RoPE on the Q and K thirds (gemm_w4a4.py:498-521, 781-831) -----------------
-// One warp per (row, head); SRC is float (fused path, unrounded tile) or T (in place on a stored tile).
-template <typename T, typename SRC>
-__global__ void qk_rows_kernel(const SRC* src, long long stride_sm, T* out, long long stride_om, int M, int N,
+// One warp per (row, head); SRC is float (fused path, unrounded tile) or T (in place on a stored tile).  In place, the V
+// third is not touched at all (`heads` then counts the Q and K heads only).  VEC: rows and pointers are 16-byte aligned,
+// so a lane's four values, weights and rotary entries move as one access each.
+template <typename T, typename SRC, bool VEC>
+__global__ void qk_rows_kernel(const SRC* src, long long stride_sm, T* out, long long stride_om, int M, int N, int heads,
                                const T* norm_q, const T* norm_k, const float* rot, long long stride_rm, int rot_rows,
                                float eps) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    const int heads = N / 128;  // over Q, K and V
     if (warp >= M * heads) return;
     const int m = warp / heads, h = warp % heads;
     const int part = (h * 128) / (N / 3);
     const SRC* s = src + (long long)m * stride_sm + h * 128 + lane * 4;
     float x[4];
+    if (VEC && sizeof(SRC) == 2) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(s);
+        const float2 a = unpack2<T>(raw.x), b = unpack2<T>(raw.y);
+        x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+    } else if (VEC) {
+        const float4 raw = *reinterpret_cast<const float4*>(s);
+        x[0] = raw.x; x[1] = raw.y; x[2] = raw.z; x[3] = raw.w;
+    } else {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) x[i] = (float)s[i];
+        for (int i = 0; i < 4; ++i) x[i] = (float)s[i];
+    }
     if (part < 2) {
         float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
 #pragma unroll
@@ -198,18 +208,33 @@ __global__ void qk_rows_kernel(const SRC* src, long long stride_sm, T* out, long
         const float rstd = rsqrtf(ss / 128.0f + eps);
         const T* w = (part == 0 ? norm_q : norm_k) + lane * 4;
         const float* rr = rot + (long long)(m % rot_rows) * stride_rm + lane * 4;
+        float wf[4], rf[4];
+        if (VEC) {
+            const uint2 wr = __ldg(reinterpret_cast<const uint2*>(w));
+            const float2 a = unpack2<T>(wr.x), b = unpack2<T>(wr.y);
+            wf[0] = a.x; wf[1] = a.y; wf[2] = b.x; wf[3] = b.y;
+            const float4 r4 = __ldg(reinterpret_cast<const float4*>(rr));
+            rf[0] = r4.x; rf[1] = r4.y; rf[2] = r4.z; rf[3] = r4.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { wf[i] = to_f32<T>(w[i]); rf[i] = rr[i]; }
+        }
 #pragma unroll
         for (int pr = 0; pr < 2; ++pr) {
-            const float xe = x[2 * pr] * rstd * to_f32<T>(w[2 * pr]);
-            const float xo = x[2 * pr + 1] * rstd * to_f32<T>(w[2 * pr + 1]);
-            const float sn = rr[2 * pr], cs = rr[2 * pr + 1];
+            const float xe = x[2 * pr] * rstd * wf[2 * pr];
+            const float xo = x[2 * pr + 1] * rstd * wf[2 * pr + 1];
+            const float sn = rf[2 * pr], cs = rf[2 * pr + 1];
             x[2 * pr] = xe * cs - xo * sn;
             x[2 * pr + 1] = xe * sn + xo * cs;
         }
     }
     T* o = out + (long long)m * stride_om + h * 128 + lane * 4;
+    if (VEC) {
+        *reinterpret_cast<uint2*>(o) = make_uint2(pack2<T>(x[0], x[1]), pack2<T>(x[2], x[3]));
+    } else {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) o[i] = from_f32<T>(x[i]);
+        for (int i = 0; i < 4; ++i) o[i] = from_f32<T>(x[i]);
+    }
 }
 
 // ---- GELU / SwiGLU + LoRA-down + int4 re-quantisation of an fp32 tile (gemm_w4a4.py:723-778) --------
@@ -283,18 +308,23 @@ int launch_generic(const GenericParams& p, int dtype, cudaStream_t s) {
 template <typename T>
 static int launch_qk_rows_t(const float* src_f, void* out, long long stride_om, int M, int N, const nb_qk_args* qk,
                             cudaStream_t s) {
-    const int warps = M * (N / 128);
-    const int blocks = (warps + 7) / 8;
-    if (src_f)
-        qk_rows_kernel<T, float><<<blocks, 256, 0, s>>>(src_f, N, static_cast<T*>(out), stride_om, M, N,
-                                                         static_cast<const T*>(qk->norm_q),
-                                                         static_cast<const T*>(qk->norm_k), qk->rot, qk->stride_rm,
-                                                         qk->rot_rows, qk->eps);
-    else
-        qk_rows_kernel<T, T><<<blocks, 256, 0, s>>>(static_cast<const T*>(out), stride_om, static_cast<T*>(out),
-                                                     stride_om, M, N, static_cast<const T*>(qk->norm_q),
-                                                     static_cast<const T*>(qk->norm_k), qk->rot, qk->stride_rm,
-                                                     qk->rot_rows, qk->eps);
+    const int heads = src_f ? N / 128 : 2 * (N / 3) / 128;  // in place: Q and K only
+    const long long warps = (long long)M * heads;
+    const int blocks = (int)((warps + 7) / 8);
+    const bool vec = aligned16(out) && stride_om % 8 == 0 && aligned16(qk->norm_q) && aligned16(qk->norm_k) &&
+                     aligned16(qk->rot) && qk->stride_rm % 4 == 0 && (!src_f || (aligned16(src_f) && N % 4 == 0));
+    auto go = [&](auto kern, auto* src, long long stride_sm) {
+        kern<<<blocks, 256, 0, s>>>(src, stride_sm, static_cast<T*>(out), stride_om, M, N, heads,
+                                    static_cast<const T*>(qk->norm_q), static_cast<const T*>(qk->norm_k), qk->rot,
+                                    qk->stride_rm, qk->rot_rows, qk->eps);
+    };
+    if (src_f) {
+        if (vec) go(qk_rows_kernel<T, float, true>, src_f, (long long)N);
+        else go(qk_rows_kernel<T, float, false>, src_f, (long long)N);
+    } else {
+        if (vec) go(qk_rows_kernel<T, T, true>, static_cast<const T*>(out), stride_om);
+        else go(qk_rows_kernel<T, T, false>, static_cast<const T*>(out), stride_om);
+    }
     NB_CUDA_CHECK(cudaGetLastError());
     return NB_OK;
 }
