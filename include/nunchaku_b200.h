@@ -123,12 +123,13 @@ int nb_gemm_w4a4(const nb_gemm_args* args, const void* epi, int epi_kind, void* 
 int64_t nb_gemm_w4a4_scratch_bytes(const nb_gemm_args* args, const void* epi, int epi_kind);
 
 /*
- * Load-time half of the int4 tensor-core path.  The weights of a layer do not change between calls, so the form the
- * kernel's TMA loads read (one e4m3 byte per int4 value, column scales in the drain's order) can be written once instead
- * of by every call's pre-pass: the role of the reference's load-time weight packing (`NunchakuWeightPacker`,
- * nunchaku/lora/flux/packer.py:165-517) for its MMA layout.  `args` needs wgt, wscales, N, K, dtype and the two strides.
- * nb_gemm_w4a4_prepared_bytes returns the size of the buffer (0: this weight cannot use the tensor-core kernel, e.g.
- * NVFP4 or K % 64 != 0); nb_gemm_w4a4_prepare_weights fills it (256-byte aligned) on `stream`.  A later nb_gemm_w4a4 call
+ * Load-time half of the tensor-core paths.  The weights of a layer do not change between calls, so the form the
+ * kernel reads (int4: one e4m3 byte per value and the column scales in the drain's order; NVFP4, `fp4` set: the block
+ * scales in the chunk layout of the block-scaled MMA, the codes are used as they are) can be written once instead of by
+ * every call's pre-pass: the role of the reference's load-time weight packing (`NunchakuWeightPacker`,
+ * nunchaku/lora/flux/packer.py:165-517) for its MMA layout.  `args` needs wgt, wscales, N, K, dtype, fp4 and the two
+ * strides.  nb_gemm_w4a4_prepared_bytes returns the size of the buffer (0: this weight cannot use a tensor-core kernel,
+ * e.g. K % 64 != 0); nb_gemm_w4a4_prepare_weights fills it (256-byte aligned) on `stream`.  A later nb_gemm_w4a4 call
  * with the same wgt / wscales / N / K / dtype may pass it as `wgt_prepared`; it then needs less scratch (ask
  * nb_gemm_w4a4_scratch_bytes with the field set) and skips that part of the pre-pass.  The generic kernel ignores it.
  * The caller must drop the buffer when it changes the weights.

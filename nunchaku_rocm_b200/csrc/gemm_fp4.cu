@@ -372,33 +372,59 @@ struct PrepackParams {
     uint8_t* sfa; uint8_t* sfb; void* la16;
     int M, N, K, R;
     long long stride_asg, stride_wsg, stride_lam;
+    int do_a, do_w;  // which of the two scale sides this launch writes (the weight side may have been prepared before)
 };
 
-template <typename T>
+// VEC: both scale arrays have 4-byte-aligned rows of a multiple of four scales, so a thread takes four consecutive rows of
+// a 64-k step with four 32-bit loads and turns the 4 x 4 bytes round in registers.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) prepack_fp4_kernel(const PrepackParams p) {
     const long long tid = (long long)blockIdx.x * 256 + threadIdx.x;
     const int KS4 = p.K / 64;
     const int Mp = (p.M + 127) / 128 * 128, Np = (p.N + 255) / 256 * 256;  // whole 128-row chunks; W: whole wide tiles
-    const long long a_units = (long long)KS4 * Mp, w_units = (long long)KS4 * Np;
+    constexpr int RPT = VEC ? 4 : 1;                                        // rows per thread
+    const long long a_units = p.do_a ? (long long)KS4 * (Mp / RPT) : 0, w_units = p.do_w ? (long long)KS4 * (Np / RPT) : 0;
     if (tid < a_units + w_units) {
-        // one thread per (64-k step, row): four scales -> one 32-bit word of the chunk
+        // one thread per (64-k step, row or four rows): four scales per row -> one 32-bit word of the chunk
         const bool is_w = tid >= a_units;
         const long long u = is_w ? tid - a_units : tid;
-        const int rows_p = is_w ? Np : Mp, rows = is_w ? p.N : p.M;
-        const int ks = (int)(u / rows_p), r = (int)(u % rows_p);
+        const int rows_p = (is_w ? Np : Mp) / RPT, rows = is_w ? p.N : p.M;
+        const int ks = (int)(u / rows_p), r = (int)(u % rows_p) * RPT;
         const uint8_t* src = is_w ? p.wscales : p.ascales;
         const long long sg = is_w ? p.stride_wsg : p.stride_asg;
-        uint32_t w = 0;
-        if (r < rows) {
-#pragma unroll
-            for (int kb = 0; kb < 4; ++kb) w |= (uint32_t)__ldg(src + (long long)(ks * 4 + kb) * sg + r) << (8 * kb);
-        }
         uint8_t* dst = (is_w ? p.sfb : p.sfa) + ((size_t)(r / 128) * KS4 + ks) * 512 + (r % 32) * 16 + ((r % 128) / 32) * 4;
-        *reinterpret_cast<uint32_t*>(dst) = w;
+        if (VEC) {
+            uint32_t k4[4] = {0, 0, 0, 0};  // k4[kb]: rows r .. r + 3 of 16-group kb
+            if (r + 3 < rows) {
+#pragma unroll
+                for (int kb = 0; kb < 4; ++kb)
+                    k4[kb] = __ldg(reinterpret_cast<const uint32_t*>(src + (long long)(ks * 4 + kb) * sg + r));
+            } else {
+#pragma unroll
+                for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (r + i < rows) k4[kb] |= (uint32_t)__ldg(src + (long long)(ks * 4 + kb) * sg + r + i) << (8 * i);
+            }
+            // byte i of k4[kb] -> byte kb of row r + i
+            const uint32_t lo01 = __byte_perm(k4[0], k4[1], 0x5140), hi01 = __byte_perm(k4[0], k4[1], 0x7362);
+            const uint32_t lo23 = __byte_perm(k4[2], k4[3], 0x5140), hi23 = __byte_perm(k4[2], k4[3], 0x7362);
+            *reinterpret_cast<uint32_t*>(dst) = __byte_perm(lo01, lo23, 0x5410);
+            *reinterpret_cast<uint32_t*>(dst + 16) = __byte_perm(lo01, lo23, 0x7632);
+            *reinterpret_cast<uint32_t*>(dst + 32) = __byte_perm(hi01, hi23, 0x5410);
+            *reinterpret_cast<uint32_t*>(dst + 48) = __byte_perm(hi01, hi23, 0x7632);
+        } else {
+            uint32_t w = 0;
+            if (r < rows) {
+#pragma unroll
+                for (int kb = 0; kb < 4; ++kb) w |= (uint32_t)__ldg(src + (long long)(ks * 4 + kb) * sg + r) << (8 * kb);
+            }
+            *reinterpret_cast<uint32_t*>(dst) = w;
+        }
         return;
     }
     const long long u = tid - (a_units + w_units);
-    const long long la_units = p.R ? (long long)p.M * (p.R / 8) : 0;
+    const long long la_units = p.do_a && p.R ? (long long)p.M * (p.R / 8) : 0;
     if (u < la_units) {
         const int rpr = p.R / 8;
         const long long m = u / rpr;
@@ -479,6 +505,26 @@ static int launch_kernel(const nb_gemm_args* a, const Params& p, const void* la1
     return NB_OK;
 }
 
+static int64_t prepared_bytes(const nb_gemm_args* a) {
+    return (int64_t)((a->N + 255) / 256 * 2) * (a->K / 64) * 512;
+}
+
+template <typename T>
+static int launch_prepack(const PrepackParams& pp, cudaStream_t s) {
+    const long long KS4 = pp.K / 64;
+    const bool vec = pp.stride_asg % 4 == 0 && pp.stride_wsg % 4 == 0 && (reinterpret_cast<uintptr_t>(pp.ascales) & 3) == 0 &&
+                     (reinterpret_cast<uintptr_t>(pp.wscales) & 3) == 0;
+    const int rpt = vec ? 4 : 1;
+    const long long units = (pp.do_a ? KS4 * ((pp.M + 127) / 128 * 128 / rpt) : 0) +
+                            (pp.do_w ? KS4 * ((pp.N + 255) / 256 * 256 / rpt) : 0) +
+                            (pp.do_a && pp.R ? (long long)pp.M * (pp.R / 8) : 0);
+    if (units == 0) return NB_OK;
+    if (vec) prepack_fp4_kernel<T, true><<<(unsigned)((units + 255) / 256), 256, 0, s>>>(pp);
+    else prepack_fp4_kernel<T, false><<<(unsigned)((units + 255) / 256), 256, 0, s>>>(pp);
+    NB_CUDA_CHECK(cudaGetLastError());
+    return NB_OK;
+}
+
 template <typename T>
 static int launch_t(const nb_gemm_args* a, cudaStream_t s) {
     const Scratch sc = scratch_layout(a);
@@ -491,11 +537,13 @@ static int launch_t(const nb_gemm_args* a, cudaStream_t s) {
     pp.sfa = base + sc.sfa; pp.sfb = base + sc.sfb; pp.la16 = base + sc.la16;
     pp.M = a->M; pp.N = a->N; pp.K = a->K; pp.R = a->R;
     pp.stride_asg = a->stride_asg; pp.stride_wsg = a->stride_wsg; pp.stride_lam = a->stride_lam;
-    const long long KS4 = a->K / 64;
-    const long long units = KS4 * ((a->M + 127) / 128 * 128) + KS4 * ((a->N + 255) / 256 * 256) +
-                            (a->R ? (long long)a->M * (a->R / 8) : 0);
-    prepack_fp4_kernel<T><<<(unsigned)((units + 255) / 256), 256, 0, s>>>(pp);
-    NB_CUDA_CHECK(cudaGetLastError());
+    // the weight side is static: a caller that prepared it once (nb_gemm_w4a4_prepare_weights) passes it in
+    const bool prepared = a->wgt_prepared && a->wgt_prepared_bytes >= prepared_bytes(a) &&
+                          (reinterpret_cast<uintptr_t>(a->wgt_prepared) & 255) == 0;
+    if (prepared) pp.sfb = const_cast<uint8_t*>(static_cast<const uint8_t*>(a->wgt_prepared));
+    pp.do_a = 1; pp.do_w = prepared ? 0 : 1;
+    const int st = launch_prepack<T>(pp, s);
+    if (st != NB_OK) return st;
 
     Params p = {};
     p.out = a->out; p.bias = a->bias; p.wcscales = a->wcscales;
@@ -527,6 +575,25 @@ const char* tc_fp4_unsupported_reason(const nb_gemm_args* a, const void* epi, in
 }
 
 int64_t tc_fp4_scratch_bytes(const nb_gemm_args* a) { return (int64_t)fp4::scratch_layout(a).total; }
+
+// Load-time form of an NVFP4 weight: its block scales in the chunk layout of the block-scaled MMA (the codes are consumed
+// as they are).
+static bool tc_fp4_weight_ok(const nb_gemm_args* a) {
+    return a && a->fp4 && a->wscales && a->N > 0 && a->K > 0 && a->K % 64 == 0 &&
+           (a->dtype == NB_DTYPE_BF16 || a->dtype == NB_DTYPE_FP16);
+}
+int64_t tc_fp4_prepared_bytes(const nb_gemm_args* a) { return tc_fp4_weight_ok(a) ? fp4::prepared_bytes(a) : 0; }
+int tc_fp4_prepare_weights(const nb_gemm_args* a, void* dst, int64_t dst_bytes, cudaStream_t s) {
+    if (!tc_fp4_weight_ok(a)) return NB_ERR_UNSUPPORTED;
+    if (!dst || dst_bytes < fp4::prepared_bytes(a) || (reinterpret_cast<uintptr_t>(dst) & 255)) return NB_ERR_INVALID;
+    fp4::PrepackParams pp = {};
+    pp.wscales = static_cast<const uint8_t*>(a->wscales); pp.ascales = pp.wscales;
+    pp.sfb = static_cast<uint8_t*>(dst);
+    pp.M = 0; pp.N = a->N; pp.K = a->K; pp.R = 0;
+    pp.stride_wsg = a->stride_wsg; pp.stride_asg = a->stride_wsg;
+    pp.do_a = 0; pp.do_w = 1;
+    return a->dtype == NB_DTYPE_BF16 ? fp4::launch_prepack<__nv_bfloat16>(pp, s) : fp4::launch_prepack<__half>(pp, s);
+}
 
 int launch_tc_fp4(const nb_gemm_args* a, cudaStream_t s) {
     return a->dtype == NB_DTYPE_BF16 ? fp4::launch_t<__nv_bfloat16>(a, s) : fp4::launch_t<__half>(a, s);

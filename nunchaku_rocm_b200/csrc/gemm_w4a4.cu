@@ -29,6 +29,8 @@ const char* tc_unsupported_reason(const nb_gemm_args* a, const void* epi, int ep
 int launch_tc(const nb_gemm_args* a, const void* epi, int epi_kind, int32_t* p_out, cudaStream_t s);
 int64_t tc_scratch_bytes(const nb_gemm_args* a);
 int64_t tc_prepared_bytes(const nb_gemm_args* a);
+int64_t tc_fp4_prepared_bytes(const nb_gemm_args* a);
+int tc_fp4_prepare_weights(const nb_gemm_args* a, void* dst, int64_t dst_bytes, cudaStream_t s);
 int tc_prepare_weights(const nb_gemm_args* a, void* dst, int64_t dst_bytes, cudaStream_t s);
 const char* tcp_unsupported_reason(const nb_gemm_args* a, const void* epi, int epi_kind);
 int launch_tc_pair(const nb_gemm_args* a, const void* epi, int epi_kind, int32_t* p_out, cudaStream_t s);
@@ -183,9 +185,12 @@ namespace nb { int tcp_kernel_info(int* out); }
 // Diagnostics: how the CTA-pair kernel fits the current device (registers, threads, shared memory, resident pairs).
 extern "C" int nb_debug_pair_kernel_info(int* out10) { return out10 ? nb::tcp_kernel_info(out10) : NB_ERR_INVALID; }
 
-extern "C" int64_t nb_gemm_w4a4_prepared_bytes(const nb_gemm_args* a) { return nb::tc_prepared_bytes(a); }
+extern "C" int64_t nb_gemm_w4a4_prepared_bytes(const nb_gemm_args* a) {
+    return a && a->fp4 ? nb::tc_fp4_prepared_bytes(a) : nb::tc_prepared_bytes(a);
+}
 
 extern "C" int nb_gemm_w4a4_prepare_weights(const nb_gemm_args* a, void* dst, int64_t dst_bytes, void* stream) {
+    if (a && a->fp4) return nb::tc_fp4_prepare_weights(a, dst, dst_bytes, static_cast<cudaStream_t>(stream));
     return nb::tc_prepare_weights(a, dst, dst_bytes, static_cast<cudaStream_t>(stream));
 }
 

@@ -317,7 +317,7 @@ def _run(a, epi, epi_kind, act, wgt=None, wscales=None, keep=None):
     """Launch one GEMM call.  ``keep``: tensors whose pointers sit in ``a`` / ``epi`` and that nothing else references
     (contiguous copies); holding them here keeps their memory from being handed to the scratch allocation below."""
     lib = L.lib()
-    if wgt is not None and not a.fp4 and lib.nb_gemm_w4a4_uses_tcgen05(C.byref(a), epi, epi_kind) == 1:
+    if wgt is not None and lib.nb_gemm_w4a4_uses_tcgen05(C.byref(a), epi, epi_kind) == 1:
         _attach_prepared(a, wgt, wscales)
     need = lib.nb_gemm_w4a4_scratch_bytes(C.byref(a), epi, epi_kind)
     scratch = None

@@ -120,6 +120,35 @@ def test_c_abi_prepared_bytes_and_scratch(cuda_dev):
     # the call no longer keeps the weight side in scratch (the buffer holds the scale order of both tensor-core kernels,
     # a call needs one of them)
     assert 256 * 256 <= need_plain - need_prepared <= nbytes
-    # NVFP4 weights have no prepared form
+    # an NVFP4 weight's prepared form is its block scales in the MMA's chunk layout: 512 bytes per 128 rows and 64 k
     a.fp4 = 1
+    assert lib.nb_gemm_w4a4_prepared_bytes(C.byref(a)) == (256 // 128) * (256 // 64) * 512
+    a.K = 96
     assert lib.nb_gemm_w4a4_prepared_bytes(C.byref(a)) == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 384, 512), (256, 768, 320)])
+def test_nvfp4_prepared_scales_agree_bit_for_bit(cuda_dev, monkeypatch, M, N, K):
+    g = torch.Generator().manual_seed(M + N)
+    dv = lambda t: t.to(cuda_dev)
+    act = dv(torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, generator=g))
+    wgt = dv(torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g))
+    asc = dv((torch.rand(K // 16, M, generator=g) * 0.05 + 0.01).to(torch.float8_e4m3fn))
+    wsc = dv((torch.rand(K // 16, N, generator=g) * 0.05 + 0.01).to(torch.float8_e4m3fn))
+    wcs = dv((torch.rand(N, generator=g) * 0.5 + 0.5).to(T))
+
+    def call(disabled):
+        if disabled:
+            monkeypatch.setenv("NUNCHAKU_B200_PREPARED_WEIGHTS_MB", "0")
+        else:
+            monkeypatch.delenv("NUNCHAKU_B200_PREPARED_WEIGHTS_MB", raising=False)
+        return G.gemm_w4a4(act, wgt, None, asc, wsc, wcscales=wcs, alpha=0.75, fp4=True, out_dtype=T)
+
+    G.clear_prepared_weights()
+    ref = call(True)
+    assert not G._PREPARED
+    first, second = call(False), call(False)
+    assert len(G._PREPARED) == 1
+    assert torch.equal(ref, first) and torch.equal(ref, second)
+    assert L.device_status(cuda_dev) == 0
+    G.clear_prepared_weights()
