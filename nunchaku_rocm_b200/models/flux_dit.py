@@ -98,6 +98,17 @@ class _FeedForward(nn.Module):
         return fused_gelu_mlp(x, self.fc1, self.fc2)
 
 
+_SIDE_STREAMS: dict = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    """The second stream of a device (one per device and process), on which a double block's text stream runs."""
+    key = torch.device(device).index
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device)
+    return _SIDE_STREAMS[key]
+
+
 class FluxDoubleBlock(nn.Module):
     def __init__(self, cfg: FluxDiTConfig, device):
         super().__init__()
@@ -117,31 +128,45 @@ class FluxDoubleBlock(nn.Module):
         cfg = self.cfg
         B, S_img, _ = hidden_states.shape
         S_txt = encoder_hidden_states.shape[1]
-        norm_h, gate_msa, shift_mlp, scale_mlp, gate_mlp = self.norm1(hidden_states, temb)
-        norm_e, c_gate_msa, c_shift_mlp, c_scale_mlp, c_gate_mlp = self.norm1_context(encoder_hidden_states, temb)
-
-        # joint attention over [text; image] (attention_processors/flux.py:71-110)
+        # The text stream of a block (512 tokens per image: launches that fill a fraction of the GPU) runs on a second
+        # CUDA stream beside the image stream; the two meet at the joint attention and at the end of the block.  Every
+        # tensor that crosses streams is a local of this function, so it outlives the join that follows its last use.
+        main = torch.cuda.current_stream(hidden_states.device)
+        side = _side_stream(hidden_states.device)
+        qkv = txt_qkv = None
         if B == 1:
             # both projections write their rows of one buffer: the concatenation of the reference without the copy
             qkv = torch.empty(1, S_txt + S_img, 3 * cfg.hidden, dtype=hidden_states.dtype, device=hidden_states.device)
-            fused_qkv_norm_rottary(norm_e, self.add_qkv_proj, self.norm_added_q, self.norm_added_k, rotary_txt, output=qkv[0, :S_txt])
+
+        # joint attention over [text; image] (attention_processors/flux.py:71-110)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            norm_e, c_gate_msa, c_shift_mlp, c_scale_mlp, c_gate_mlp = self.norm1_context(encoder_hidden_states, temb)
+            if B == 1:
+                fused_qkv_norm_rottary(norm_e, self.add_qkv_proj, self.norm_added_q, self.norm_added_k, rotary_txt, output=qkv[0, :S_txt])
+            else:
+                txt_qkv = fused_qkv_norm_rottary(norm_e, self.add_qkv_proj, self.norm_added_q, self.norm_added_k, rotary_txt)
+        norm_h, gate_msa, shift_mlp, scale_mlp, gate_mlp = self.norm1(hidden_states, temb)
+        if B == 1:
             fused_qkv_norm_rottary(norm_h, self.to_qkv, self.norm_q, self.norm_k, rotary_img, output=qkv[0, S_txt:])
-        else:
-            qkv = torch.cat([fused_qkv_norm_rottary(norm_e, self.add_qkv_proj, self.norm_added_q, self.norm_added_k, rotary_txt),
-                             fused_qkv_norm_rottary(norm_h, self.to_qkv, self.norm_q, self.norm_k, rotary_img)], dim=1)
-        attn = _attention(qkv, cfg)
-        context_attn, attn = attn[:, :S_txt], attn[:, S_txt:]
-        attn = self.to_out(attn)
-        context_attn = self.to_add_out(context_attn)
+        main.wait_stream(side)
+        if B != 1:
+            qkv = torch.cat([txt_qkv, fused_qkv_norm_rottary(norm_h, self.to_qkv, self.norm_q, self.norm_k, rotary_img)], dim=1)
+        attn_all = _attention(qkv, cfg)
 
         ss = self.norm1.scale_shift
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            context_attn = self.to_add_out(attn_all[:, :S_txt])
+            txt_states = gated_residual(encoder_hidden_states, c_gate_msa, context_attn)
+            norm_e2 = layernorm_modulate(txt_states, c_scale_mlp, c_shift_mlp, scale_add=ss)
+            txt_out = gated_residual(txt_states, c_gate_mlp, self.ff_context(norm_e2))
+        attn = self.to_out(attn_all[:, S_txt:])
         hidden_states = gated_residual(hidden_states, gate_msa, attn)
         norm_h = layernorm_modulate(hidden_states, scale_mlp, shift_mlp, scale_add=ss)
         hidden_states = gated_residual(hidden_states, gate_mlp, self.ff(norm_h))
-
-        encoder_hidden_states = gated_residual(encoder_hidden_states, c_gate_msa, context_attn)
-        norm_e = layernorm_modulate(encoder_hidden_states, c_scale_mlp, c_shift_mlp, scale_add=ss)
-        encoder_hidden_states = gated_residual(encoder_hidden_states, c_gate_mlp, self.ff_context(norm_e))
+        main.wait_stream(side)
+        encoder_hidden_states = txt_out
         return encoder_hidden_states, hidden_states
 
 

@@ -28,6 +28,7 @@ import torch.nn.functional as F
 from ..ops.dispatch import scaled_dot_product_attention
 from ..ops.elementwise import gated_residual, layernorm_modulate
 from ..ops.fused import fused_gelu_mlp, fused_qkv_norm_rottary
+from .flux_dit import _side_stream
 from .linear import AWQW4A16Linear, SVDQW4A4Linear
 
 
@@ -109,31 +110,48 @@ class QwenBlock(nn.Module):
         B, S_img, C = hidden_states.shape
         S_txt = encoder_hidden_states.shape[1]
         img_freqs, txt_freqs = rotary_table(img_freqs), rotary_table(txt_freqs)  # (no-op when the model already did it)
-        img_mod1, img_mod2 = self.img_mod(temb)
-        txt_mod1, txt_mod2 = self.txt_mod(temb)
-        img_m, img_gate1 = self._modulate(hidden_states, img_mod1)
-        txt_m, txt_gate1 = self._modulate(encoder_hidden_states, txt_mod1)
-
-        # joint attention over [text; image]: both projections write their rows of one buffer, per-head RMSNorm + RoPE of
-        # Q and K run in the projection's epilogue
+        # The text stream of a block (256 tokens: small launches that fill a fraction of the GPU) runs on a second CUDA
+        # stream beside the image stream; the two meet at the joint attention and at the end of the block.  Every tensor
+        # that crosses streams is a local of this function, so it outlives the join that follows its last use.
+        main = torch.cuda.current_stream(hidden_states.device)
+        side = _side_stream(hidden_states.device)  # (shared with the FLUX blocks)
         nq, nk, naq, nak = (SimpleNamespace(weight=w) for w in (self.norm_q, self.norm_k, self.norm_added_q, self.norm_added_k))
+        qkv = txt_qkv = None
         if B == 1:
             qkv = torch.empty(1, S_txt + S_img, 3 * C, dtype=hidden_states.dtype, device=hidden_states.device)
-            fused_qkv_norm_rottary(txt_m, self.add_qkv_proj, naq, nak, txt_freqs, output=qkv[0, :S_txt])
+
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            txt_mod1, txt_mod2 = self.txt_mod(temb)
+            txt_m, txt_gate1 = self._modulate(encoder_hidden_states, txt_mod1)
+            # joint attention over [text; image]: both projections write their rows of one buffer, per-head RMSNorm + RoPE
+            # of Q and K run in the projection's epilogue
+            if B == 1:
+                fused_qkv_norm_rottary(txt_m, self.add_qkv_proj, naq, nak, txt_freqs, output=qkv[0, :S_txt])
+            else:
+                txt_qkv = fused_qkv_norm_rottary(txt_m, self.add_qkv_proj, naq, nak, txt_freqs)
+        img_mod1, img_mod2 = self.img_mod(temb)
+        img_m, img_gate1 = self._modulate(hidden_states, img_mod1)
+        if B == 1:
             fused_qkv_norm_rottary(img_m, self.to_qkv, nq, nk, img_freqs, output=qkv[0, S_txt:])
-        else:
-            qkv = torch.cat([fused_qkv_norm_rottary(txt_m, self.add_qkv_proj, naq, nak, txt_freqs),
-                             fused_qkv_norm_rottary(img_m, self.to_qkv, nq, nk, img_freqs)], dim=1)
+        main.wait_stream(side)
+        if B != 1:
+            qkv = torch.cat([txt_qkv, fused_qkv_norm_rottary(img_m, self.to_qkv, nq, nk, img_freqs)], dim=1)
         q, k, v = (t.view(B, S_txt + S_img, cfg.heads, cfg.head_dim).transpose(1, 2) for t in qkv.chunk(3, dim=-1))
         attn = scaled_dot_product_attention(q, k, v).transpose(1, 2).flatten(2, 3)  # (B, S, H D)
-        txt_attn, img_attn = self.to_add_out(attn[:, :S_txt]), self.to_out(attn[:, S_txt:])
 
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            txt_attn = self.to_add_out(attn[:, :S_txt])
+            txt_states = gated_residual(encoder_hidden_states, txt_gate1, txt_attn)
+            txt_m2, txt_gate2 = self._modulate(txt_states, txt_mod2)
+            txt_out = gated_residual(txt_states, txt_gate2, self.txt_mlp(txt_m2))
+        img_attn = self.to_out(attn[:, S_txt:])
         hidden_states = gated_residual(hidden_states, img_gate1, img_attn)
-        encoder_hidden_states = gated_residual(encoder_hidden_states, txt_gate1, txt_attn)
         img_m2, img_gate2 = self._modulate(hidden_states, img_mod2)
         hidden_states = gated_residual(hidden_states, img_gate2, self.img_mlp(img_m2))
-        txt_m2, txt_gate2 = self._modulate(encoder_hidden_states, txt_mod2)
-        encoder_hidden_states = gated_residual(encoder_hidden_states, txt_gate2, self.txt_mlp(txt_m2))
+        main.wait_stream(side)
+        encoder_hidden_states = txt_out
         return encoder_hidden_states, hidden_states
 
 

@@ -234,3 +234,28 @@ def test_qwen_image_block_matches_the_oracle_chain(cuda_dev):
     print("\nQwen-Image block parity (relative Frobenius error vs the oracle chain)", errs)
     for k, v in errs.items():
         assert v <= 3e-2, (k, v)
+
+
+def test_text_stream_on_a_second_cuda_stream_changes_nothing(cuda_dev, monkeypatch):
+    # the blocks run their text stream on a second CUDA stream: the same forward with everything on one stream must give
+    # the same bits (a missing dependency between the streams would show here, or as a run-to-run difference)
+    from nunchaku_rocm_b200.models import flux_dit, qwen_dit
+
+    fcfg = flux_dit.FluxDiTConfig(n_double=2, n_single=1)
+    fmodel = flux_dit.FluxDiT(fcfg, device=cuda_dev).random_init(seed=6)
+    fstep = flux_dit.GraphedStep(fmodel, batch=1, txt_tokens=512, grid=32, seed=2)
+    qcfg = qwen_dit.QwenDiTConfig(n_blocks=2)
+    qmodel = qwen_dit.QwenDiT(qcfg, device=cuda_dev).random_init(seed=7)
+    qstep = qwen_dit.GraphedQwenStep(qmodel, batch=1, img_tokens=1024, txt_tokens=256)
+    with torch.no_grad():
+        two = [fstep._forward().clone(), qstep._forward().clone()]
+        again = [fstep._forward().clone(), qstep._forward().clone()]
+        replay = [fstep.step().clone(), qstep.step().clone()]
+        one_stream = lambda device: torch.cuda.current_stream(device)
+        monkeypatch.setattr(flux_dit, "_side_stream", one_stream)
+        monkeypatch.setattr(qwen_dit, "_side_stream", one_stream)
+        one = [fstep._forward().clone(), qstep._forward().clone()]
+    torch.cuda.synchronize(cuda_dev)
+    for a, b, c, d in zip(two, again, replay, one):
+        assert torch.isfinite(a.float()).all()
+        assert torch.equal(a, b) and torch.equal(a, c) and torch.equal(a, d)
