@@ -366,7 +366,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         // tcgen05.ld.16x256b.x4 hands a thread, for one 16-lane block and 32 columns, rows {gid, gid + 8} and the column
         // pairs 8 j + 2 tig + {0, 1}, j = 0..3: register 4 j + 2 rs + e.
         // (Everything the K loop does not need is computed after it: the loop runs with 64 accumulators, one 16-register
-        // chunk and 12 scale registers out of 112, and a spill inside it costs more than any of this arithmetic.)
+        // chunk and 16 scale registers out of 112, and a spill inside it costs more than any of this arithmetic.)
         const int q = warp & 3;                    // TMEM lane quarter this warp may read (warp id mod 4)
         const int cq = (warp - CTRL_WARPS) >> 2;   // 64-column slice of the tile
         const int gid = lane >> 2, tig = lane & 3;
@@ -397,6 +397,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             // measured: 8 % faster with the drain alone, slower inside the whole kernel on long K loops.)
             auto drain_group = [&](uint32_t taddr, uint32_t st, uint32_t rem_bar, int g, uint32_t next_bar, uint32_t next_par) {
 #pragma unroll
+                uint64_t ap4[4];  // the row scales of both lane blocks: fetched with the first two chunks, used by all four
+#pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
                     uint64_t wp[4];
 #pragma unroll
@@ -405,8 +407,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         tmem_ld_16x256b_x4(taddr + ((uint32_t)(lb * 16) << 16) + ch * 32, v);
                         // the scales are fetched while the chunk is on its way (shared memory answers slowly while the tensor
                         // cores read their operands from it), as 64-bit pairs: the form the packed arithmetic takes
-                        uint64_t ap[2];
-                        lds2x64(st + as_off + lb * 128, ap[0], ap[1]);
+                        if (ch == 0) lds2x64(st + as_off + lb * 128, ap4[2 * lb], ap4[2 * lb + 1]);
+                        const uint64_t ap[2] = {ap4[2 * lb], ap4[2 * lb + 1]};
                         if (lb == 0) {
                             lds2x64(st + ws_off + ch * 128, wp[0], wp[1]);
                             lds2x64(st + ws_off + ch * 128 + 16, wp[2], wp[3]);
