@@ -185,9 +185,16 @@ class FluxSingleBlock(nn.Module):
     def forward(self, hidden_states, temb, rotary):
         residual = hidden_states
         norm_h, gate = self.norm(hidden_states, temb)
-        mlp = fused_gelu_mlp(norm_h, self.mlp_fc1, self.mlp_fc2)
+        # the MLP branch and the attention branch meet only in the final sum: the MLP runs on the second stream, so the
+        # partly filled last waves of one branch's kernels overlap the other's
+        main = torch.cuda.current_stream(hidden_states.device)
+        side = _side_stream(hidden_states.device)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            mlp = fused_gelu_mlp(norm_h, self.mlp_fc1, self.mlp_fc2)
         qkv = fused_qkv_norm_rottary(norm_h, self.to_qkv, self.norm_q, self.norm_k, rotary)
         attn = self.to_out(_attention(qkv, self.cfg))
+        main.wait_stream(side)
         return gated_residual(residual, gate, attn, mlp)
 
 
