@@ -74,9 +74,15 @@ class _AdaLayerNormZero(nn.Module):
         self.n, self.dim, self.scale_shift = n, dim, scale_shift
         self.linear = AWQW4A16Linear(dim, n * dim, bias=True, group_size=64, torch_dtype=dtype, device=device)
 
-    def forward(self, x: torch.Tensor, emb: torch.Tensor):
+    def modulation(self, emb: torch.Tensor) -> torch.Tensor:
+        """The ``(n, B, dim)`` modulation vectors: they depend on the time embedding only, so a model may compute every
+        block's ahead of the blocks (:func:`modulations_ahead`)."""
         e = self.linear(F.silu(emb))
-        parts = e.view(e.shape[0], -1, self.n).permute(2, 0, 1)  # (n, B, dim)
+        return e.view(e.shape[0], -1, self.n).permute(2, 0, 1)
+
+    def forward(self, x: torch.Tensor, emb: torch.Tensor, parts: torch.Tensor | None = None):
+        if parts is None:
+            parts = self.modulation(emb)
         # LayerNorm (no affine) * (scale + scale_shift) + shift in one pass; the second modulation's scale comes back without
         # its scale_shift, which the block's own layernorm_modulate call adds
         norm = layernorm_modulate(x, parts[1], parts[0], scale_add=self.scale_shift)
@@ -101,12 +107,36 @@ class _FeedForward(nn.Module):
 _SIDE_STREAMS: dict = {}
 
 
-def _side_stream(device) -> "torch.cuda.Stream":
-    """The second stream of a device (one per device and process), on which a double block's text stream runs."""
-    key = torch.device(device).index
+def _side_stream(device, which: str = "text") -> "torch.cuda.Stream":
+    """A further stream of a device (one per name, device and process): "text" carries a block's text stream (or a single
+    block's MLP branch), "mod" the modulation vectors computed ahead of the blocks."""
+    key = (torch.device(device).index, which)
     if key not in _SIDE_STREAMS:
         _SIDE_STREAMS[key] = torch.cuda.Stream(device)
     return _SIDE_STREAMS[key]
+
+
+def modulations_ahead(temb: torch.Tensor, per_block) -> list:
+    """Every block's modulation vectors on a stream of their own, ahead of the blocks: they depend on ``temb`` only, and
+    the small AWQ GEMVs and element-wise launches that make them would otherwise sit between the large kernels of each
+    block.  ``per_block``: one callable per block, ``temb ->`` that block's modulation tensors.  Returns ``[(tensors,
+    event)]``; the caller waits for a block's event before the block and keeps the list alive until it has joined the
+    stream again (:func:`join_modulations`)."""
+    main = torch.cuda.current_stream(temb.device)
+    ms = _side_stream(temb.device, "mod")
+    ms.wait_stream(main)
+    out = []
+    with torch.cuda.stream(ms):
+        for fn in per_block:
+            t = fn(temb)
+            ev = torch.cuda.Event()
+            ev.record(ms)
+            out.append((t, ev))
+    return out
+
+
+def join_modulations(device) -> None:
+    torch.cuda.current_stream(device).wait_stream(_side_stream(device, "mod"))
 
 
 class FluxDoubleBlock(nn.Module):
@@ -124,8 +154,9 @@ class FluxDoubleBlock(nn.Module):
         self.to_add_out = SVDQW4A4Linear(h, h, rank=cfg.rank, torch_dtype=T, device=device)
         self.ff, self.ff_context = _FeedForward(cfg, device), _FeedForward(cfg, device)
 
-    def forward(self, hidden_states, encoder_hidden_states, temb, rotary_img, rotary_txt):
+    def forward(self, hidden_states, encoder_hidden_states, temb, rotary_img, rotary_txt, mods=None):
         cfg = self.cfg
+        mod_img, mod_txt = mods if mods is not None else (None, None)
         B, S_img, _ = hidden_states.shape
         S_txt = encoder_hidden_states.shape[1]
         # The text stream of a block (512 tokens per image: launches that fill a fraction of the GPU) runs on a second
@@ -141,12 +172,12 @@ class FluxDoubleBlock(nn.Module):
         # joint attention over [text; image] (attention_processors/flux.py:71-110)
         side.wait_stream(main)
         with torch.cuda.stream(side):
-            norm_e, c_gate_msa, c_shift_mlp, c_scale_mlp, c_gate_mlp = self.norm1_context(encoder_hidden_states, temb)
+            norm_e, c_gate_msa, c_shift_mlp, c_scale_mlp, c_gate_mlp = self.norm1_context(encoder_hidden_states, temb, mod_txt)
             if B == 1:
                 fused_qkv_norm_rottary(norm_e, self.add_qkv_proj, self.norm_added_q, self.norm_added_k, rotary_txt, output=qkv[0, :S_txt])
             else:
                 txt_qkv = fused_qkv_norm_rottary(norm_e, self.add_qkv_proj, self.norm_added_q, self.norm_added_k, rotary_txt)
-        norm_h, gate_msa, shift_mlp, scale_mlp, gate_mlp = self.norm1(hidden_states, temb)
+        norm_h, gate_msa, shift_mlp, scale_mlp, gate_mlp = self.norm1(hidden_states, temb, mod_img)
         if B == 1:
             fused_qkv_norm_rottary(norm_h, self.to_qkv, self.norm_q, self.norm_k, rotary_img, output=qkv[0, S_txt:])
         main.wait_stream(side)
@@ -182,9 +213,9 @@ class FluxSingleBlock(nn.Module):
         self.norm_q, self.norm_k = _HeadRMSNorm(cfg.head_dim, T, device), _HeadRMSNorm(cfg.head_dim, T, device)
         self.to_out = SVDQW4A4Linear(h, h, rank=cfg.rank, torch_dtype=T, device=device)
 
-    def forward(self, hidden_states, temb, rotary):
+    def forward(self, hidden_states, temb, rotary, mods=None):
         residual = hidden_states
-        norm_h, gate = self.norm(hidden_states, temb)
+        norm_h, gate = self.norm(hidden_states, temb, mods)
         # the MLP branch and the attention branch meet only in the final sum: the MLP runs on the second stream, so the
         # partly filled last waves of one branch's kernels overlap the other's
         main = torch.cuda.current_stream(hidden_states.device)
@@ -285,11 +316,20 @@ class FluxDiT(nn.Module):
         encoder_hidden_states = self.context_embedder(encoder_hidden_states)
         rot_txt, rot_img, rot_all = rotary if rotary is not None else self.rotary_tables(txt_ids, img_ids)
         n_txt = encoder_hidden_states.shape[1]
-        for block in self.transformer_blocks:
-            encoder_hidden_states, hidden_states = block(hidden_states, encoder_hidden_states, temb, rot_img, rot_txt)
+        main = torch.cuda.current_stream(temb.device)
+        mods = modulations_ahead(
+            temb,
+            [lambda t, b=b: (b.norm1.modulation(t), b.norm1_context.modulation(t)) for b in self.transformer_blocks]
+            + [lambda t, b=b: b.norm.modulation(t) for b in self.single_transformer_blocks])
+        nd = len(self.transformer_blocks)
+        for i, block in enumerate(self.transformer_blocks):
+            main.wait_event(mods[i][1])
+            encoder_hidden_states, hidden_states = block(hidden_states, encoder_hidden_states, temb, rot_img, rot_txt, mods[i][0])
         hidden_states = torch.cat([encoder_hidden_states, hidden_states], dim=1)
-        for block in self.single_transformer_blocks:
-            hidden_states = block(hidden_states, temb, rot_all)
+        for i, block in enumerate(self.single_transformer_blocks):
+            main.wait_event(mods[nd + i][1])
+            hidden_states = block(hidden_states, temb, rot_all, mods[nd + i][0])
+        join_modulations(temb.device)
         hidden_states = hidden_states[:, n_txt:]
         scale, shift = self.norm_out_linear(F.silu(temb)).chunk(2, dim=1)
         hidden_states = layernorm_modulate(hidden_states, scale, shift, scale_add=1.0)

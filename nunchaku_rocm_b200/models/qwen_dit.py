@@ -28,7 +28,7 @@ import torch.nn.functional as F
 from ..ops.dispatch import scaled_dot_product_attention
 from ..ops.elementwise import gated_residual, layernorm_modulate
 from ..ops.fused import fused_gelu_mlp, fused_qkv_norm_rottary
-from .flux_dit import _side_stream
+from .flux_dit import _side_stream, join_modulations, modulations_ahead
 from .linear import AWQW4A16Linear, SVDQW4A4Linear
 
 
@@ -105,7 +105,7 @@ class QwenBlock(nn.Module):
         shift, scale, gate = mod.chunk(3, dim=-1)
         return layernorm_modulate(x, scale, shift, scale_add=1.0), gate
 
-    def forward(self, hidden_states, encoder_hidden_states, temb, img_freqs, txt_freqs):
+    def forward(self, hidden_states, encoder_hidden_states, temb, img_freqs, txt_freqs, mods=None):
         cfg = self.cfg
         B, S_img, C = hidden_states.shape
         S_txt = encoder_hidden_states.shape[1]
@@ -122,7 +122,7 @@ class QwenBlock(nn.Module):
 
         side.wait_stream(main)
         with torch.cuda.stream(side):
-            txt_mod1, txt_mod2 = self.txt_mod(temb)
+            txt_mod1, txt_mod2 = mods[1] if mods is not None else self.txt_mod(temb)
             txt_m, txt_gate1 = self._modulate(encoder_hidden_states, txt_mod1)
             # joint attention over [text; image]: both projections write their rows of one buffer, per-head RMSNorm + RoPE
             # of Q and K run in the projection's epilogue
@@ -130,7 +130,7 @@ class QwenBlock(nn.Module):
                 fused_qkv_norm_rottary(txt_m, self.add_qkv_proj, naq, nak, txt_freqs, output=qkv[0, :S_txt])
             else:
                 txt_qkv = fused_qkv_norm_rottary(txt_m, self.add_qkv_proj, naq, nak, txt_freqs)
-        img_mod1, img_mod2 = self.img_mod(temb)
+        img_mod1, img_mod2 = mods[0] if mods is not None else self.img_mod(temb)
         img_m, img_gate1 = self._modulate(hidden_states, img_mod1)
         if B == 1:
             fused_qkv_norm_rottary(img_m, self.to_qkv, nq, nk, img_freqs, output=qkv[0, S_txt:])
@@ -217,8 +217,12 @@ class QwenDiT(nn.Module):
         e = self.txt_in(encoder_hidden_states)
         temb = self.time_in(_timestep_embedding(timestep * 1000.0).to(cfg.dtype))
         img_freqs, txt_freqs = rotary_table(img_freqs), rotary_table(txt_freqs)
-        for blk in self.blocks:
-            e, h = blk(h, e, temb, img_freqs, txt_freqs)
+        main = torch.cuda.current_stream(temb.device)
+        mods = modulations_ahead(temb, [lambda t, b=b: (b.img_mod(t), b.txt_mod(t)) for b in self.blocks])
+        for i, blk in enumerate(self.blocks):
+            main.wait_event(mods[i][1])
+            e, h = blk(h, e, temb, img_freqs, txt_freqs, mods[i][0])
+        join_modulations(temb.device)
         scale, shift = self.norm_out_linear(F.silu(temb)).chunk(2, dim=1)
         h = layernorm_modulate(h, scale, shift, scale_add=1.0)
         return self.proj_out(h)

@@ -237,8 +237,8 @@ def test_qwen_image_block_matches_the_oracle_chain(cuda_dev):
 
 
 def test_text_stream_on_a_second_cuda_stream_changes_nothing(cuda_dev, monkeypatch):
-    # the blocks run their text stream on a second CUDA stream: the same forward with everything on one stream must give
-    # the same bits (a missing dependency between the streams would show here, or as a run-to-run difference)
+    # the blocks run their text stream on a second CUDA stream and the models compute the modulation vectors ahead on a third:
+    # the same forward with everything on one stream must give the same bits (a missing dependency between the streams would show here, or as a run-to-run difference)
     from nunchaku_rocm_b200.models import flux_dit, qwen_dit
 
     fcfg = flux_dit.FluxDiTConfig(n_double=2, n_single=1)
@@ -251,7 +251,7 @@ def test_text_stream_on_a_second_cuda_stream_changes_nothing(cuda_dev, monkeypat
         two = [fstep._forward().clone(), qstep._forward().clone()]
         again = [fstep._forward().clone(), qstep._forward().clone()]
         replay = [fstep.step().clone(), qstep.step().clone()]
-        one_stream = lambda device: torch.cuda.current_stream(device)
+        one_stream = lambda device, which="text": torch.cuda.current_stream(device)
         monkeypatch.setattr(flux_dit, "_side_stream", one_stream)
         monkeypatch.setattr(qwen_dit, "_side_stream", one_stream)
         one = [fstep._forward().clone(), qstep._forward().clone()]
