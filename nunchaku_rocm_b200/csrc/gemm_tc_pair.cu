@@ -396,7 +396,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             // latency is the arithmetic of the other three warps of the scheduler.  (Two loads of 64 columns per group were
             // measured: 8 % faster with the drain alone, slower inside the whole kernel on long K loops.)
             auto drain_group = [&](uint32_t taddr, uint32_t st, uint32_t rem_bar, int g, uint32_t next_bar, uint32_t next_par) {
-#pragma unroll
                 uint64_t ap4[4];  // the row scales of both lane blocks: fetched with the first two chunks, used by all four
 #pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
