@@ -8,11 +8,12 @@
 // more than 8 (probabilities stay below 2^8), which makes the rescaling of the output accumulator a rare event.
 //
 // Two launches:
-//  1. `attn_prepack_kernel`: Q' = T(q * scale * log2 e) as (B H, Tq rounded up to 128, 128), and V transposed to
-//     (B H, 128, Tkv rounded up to 8) so that both MMAs read K-major operands; pad rows / columns are zero.
+//  1. `attn_prepack_vt_kernel`: V transposed to (B H, 128, Tkv rounded up to 8) so that both MMAs read K-major operands;
+//     pad columns are zero.
 //  2. `attention_tc_kernel`: a CTA owns 128 query rows of one (batch, head) and walks the keys in tiles of 128.
-//       warp 0    TMA producer: Q' once; K tiles straight from the caller's strided tensor (4-D tensor map) and
-//                 V^T tiles through two-stage rings (128-byte swizzle, no multicast).
+//       warp 0    TMA producer: the Q tile once and K tiles straight from the caller's strided tensors (4-D tensor maps;
+//                 rows past the end read as zeros), V^T tiles; K and V^T through two-stage rings (128-byte swizzle, no
+//                 multicast).  The softmax warps turn the Q tile into Q' = T(q * scale * log2 e) in place before the first MMA.
 //       warp 1    MMA issuer for the scores: S_j = Q' K_j^T (8 MMAs, N = 128) into one of two score slots, so the tensor
 //                 pipe works on the next scores while the CUDA cores do the softmax of the current tile.
 //       warp 10   MMA issuer for O += P_j V_j, with P read from tensor memory as the A operand.
@@ -41,14 +42,15 @@ constexpr int OFF_BAR = OFF_XCH + 6 * 128 * 4;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
 constexpr uint32_t TM_S = 0, TM_O = 256, TM_P = 384;
 
-enum { B_Q = 0, B_KF = 1, B_KE = 3, B_VF = 5, B_VE = 7, B_SF = 9, B_SE = 11, B_PF = 13, B_PV = 15, B_XM = 17, B_COUNT = 21 };
+enum { B_Q = 0, B_KF = 1, B_KE = 3, B_VF = 5, B_VE = 7, B_SF = 9, B_SE = 11, B_PF = 13, B_PV = 15, B_XM = 17, B_QS = 21, B_COUNT = 22 };
 enum { E_PROD = 0x210, E_MMA = 0x230, E_SM = 0x240 };
 
 struct Params {
     void* o;
     int Tq, Tkv, H;
     long long stride_ob, stride_om;
-    int tq_pad;  // rows of Q' per (batch, head)
+    int tq_pad;  // query rows per (batch, head) rounded up to whole tiles
+    float qscale;  // softmax scale x log2(e): applied to the Q tile in shared memory, rounded to T (the reference's rounding point)
     int* status;
 };
 
@@ -109,7 +111,7 @@ __device__ __forceinline__ float ex2(float x) {
 template <typename T>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                    const __grid_constant__ CUtensorMap tm_v, const int4 kperm, const Params p) {
+                    const __grid_constant__ CUtensorMap tm_v, const int4 kperm, const int4 qperm, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t s_base = smem_u32(smem);
@@ -121,6 +123,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
     if (threadIdx.x == 0) {
         mbar_init(bar(B_Q), 1);
+        mbar_init(bar(B_QS), SM_WARPS);
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar(B_KF + i), 1); mbar_init(bar(B_KE + i), 1);
             mbar_init(bar(B_VF + i), 1); mbar_init(bar(B_VE + i), 1);
@@ -149,8 +152,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         if (lane == 0) {
             tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
             mbar_expect_tx(bar(B_Q), TILE);
-            tma_load_2d(s_base + OFF_Q, &tm_q, bar(B_Q), 0, bh * p.tq_pad + m0);
-            tma_load_2d(s_base + OFF_Q + TILE / 2, &tm_q, bar(B_Q), 64, bh * p.tq_pad + m0);
+            {
+                // Q from the caller's strided (B, H, T, D) view, like K below; rows past Tq read as zeros
+                int c[4];
+                c[0] = 0;
+                c[qperm.x] = m0; c[qperm.y] = head; c[qperm.z] = batch;
+                tma_load_4d(s_base + OFF_Q, &tm_q, bar(B_Q), 0, c[1], c[2], c[3]);
+                tma_load_4d(s_base + OFF_Q + TILE / 2, &tm_q, bar(B_Q), 64, c[1], c[2], c[3]);
+            }
             bool ok = true;
             for (int j = 0; j < NT && ok; ++j) {
                 const int s = j & 1;
@@ -187,7 +196,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         {
             const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
             const uint32_t idesc = umma_idesc(1u, fmt, fmt, 128);
-            bool ok = mbar_wait_warp(bar(B_Q), 0, abort_s, E_MMA | 1);
+            bool ok = mbar_wait_warp(bar(B_QS), 0, abort_s, E_MMA | 1);  // the Q tile has landed and been scaled
             const uint64_t dq = desc_sw128(s_base + OFF_Q), dk0 = desc_sw128(s_base + OFF_K);
             for (int j = 0; j < NT && ok; ++j) {
                 const int b = j & 1;
@@ -244,7 +253,29 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         float* xsum = reinterpret_cast<float*>(smem + OFF_XCH) + 4 * 128;  // [half][128]
         float m_used = -INFINITY, l = 0.f;
         uint32_t xph = 0;
-        bool ok = true;
+        bool ok = mbar_wait_warp(bar(B_Q), 0, abort_s, E_SM | 7);
+        if (ok) {
+            // Q' = T(q * scale * log2 e), in place on the tile the TMA load put into shared memory (element-wise, so the
+            // swizzle does not matter): 2048 16-byte units over the 256 softmax threads
+            const int st = (warp - 2) * 32 + lane;
+#pragma unroll
+            for (int i = 0; i < TILE / 16 / (SM_WARPS * 32); ++i) {
+                uint4* u = reinterpret_cast<uint4*>(smem + OFF_Q) + st + i * (SM_WARPS * 32);
+                const uint4 raw = *u;
+                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+                uint32_t z[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = unpack2<T>(w[e]);
+                    z[e] = pack2<T>(f.x * p.qscale, f.y * p.qscale);
+                }
+                *u = make_uint4(z[0], z[1], z[2], z[3]);
+            }
+            // the tensor cores read shared memory through the async proxy: make these generic-proxy writes visible to it
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_QS));
+        }
         for (int j = 0; j < NT && ok; ++j) {
             const int b = j & 1;
             const uint32_t par = (j >> 1) & 1;
@@ -374,32 +405,6 @@ struct PrepackParams {
     long long stride_qb, stride_qh, stride_qm, stride_vb, stride_vh, stride_vn;
 };
 
-template <typename T>
-__global__ void __launch_bounds__(256) attn_prepack_q_kernel(const PrepackParams p) {
-    const long long tid = (long long)blockIdx.x * 256 + threadIdx.x;  // one 16-byte unit of Q'
-    const long long total = (long long)p.B * p.H * p.tq_pad * (HD / 8);
-    if (tid >= total) return;
-    const int u = (int)(tid % (HD / 8));
-    const long long r = tid / (HD / 8);
-    const int m = (int)(r % p.tq_pad);
-    const int bh = (int)(r / p.tq_pad);
-    uint4 o = make_uint4(0, 0, 0, 0);
-    if (m < p.Tq) {
-        const T* src = static_cast<const T*>(p.q) + (long long)(bh / p.H) * p.stride_qb + (long long)(bh % p.H) * p.stride_qh +
-                       (long long)m * p.stride_qm + u * 8;
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-        uint32_t z[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = unpack2<T>(w[i]);
-            z[i] = pack2<T>(f.x * p.qscale, f.y * p.qscale);
-        }
-        o = make_uint4(z[0], z[1], z[2], z[3]);
-    }
-    reinterpret_cast<uint4*>(p.qs)[tid] = o;
-}
-
 // one block transposes 64 keys x 64 d of one (batch, head)
 template <typename T>
 __global__ void __launch_bounds__(256) attn_prepack_vt_kernel(const PrepackParams p) {
@@ -456,6 +461,30 @@ static bool make_map(CUtensorMap* m, CUtensorMapDataType dt, int rank, const voi
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// A 4-D tensor map over the caller's strided (B, H, T, D) view of Q or K (element strides; D contiguous): the outer
+// dimensions sorted by stride, as the encoder wants them; `perm` = the coordinate slot of (row, head, batch).
+static bool make_view_map(CUtensorMap* m, int4* perm, CUtensorMapDataType t16, const void* base, int T_, int H, int B,
+                          long long stride_t, long long stride_h, long long stride_b, int box_rows) {
+    struct Dim { cuuint64_t size, stride; int role; } d[3] = {{(cuuint64_t)T_, (cuuint64_t)stride_t * 2, 0},
+                                                               {(cuuint64_t)H, (cuuint64_t)stride_h * 2, 1},
+                                                               {(cuuint64_t)B, (cuuint64_t)stride_b * 2, 2}};
+    std::stable_sort(d, d + 3, [](const Dim& x, const Dim& y) { return x.stride < y.stride; });
+    cuuint64_t dims[4] = {HD, d[0].size, d[1].size, d[2].size};
+    cuuint64_t str[3] = {d[0].stride, d[1].stride, d[2].stride};
+    cuuint32_t box[4] = {64, 1, 1, 1};
+    int pos[3];
+    for (int i = 0; i < 3; ++i) {
+        pos[d[i].role] = i + 1;
+        if (d[i].role == 0) box[i + 1] = (cuuint32_t)box_rows;
+    }
+    *perm = make_int4(pos[0], pos[1], pos[2], 0);
+    // a dimension of size 1 may carry any stride; give it a valid one.  (A zero or unaligned stride on a larger dimension --
+    // a view expanded over heads or batch -- never gets here: attn_tc_unsupported_reason refuses it.)
+    for (int i = 0; i < 3; ++i)
+        if (dims[i + 1] == 1 && (str[i] == 0 || str[i] % 16)) str[i] = 16;
+    return make_map(m, t16, 4, base, dims, str, box);
+}
+
 static inline size_t up256(size_t x) { return (x + 255) & ~size_t(255); }
 struct Scratch { size_t qs, vt, total; int tq_pad, tkv_pad; };
 static Scratch scratch_layout(const nb_attn_args* a) {
@@ -464,7 +493,7 @@ static Scratch scratch_layout(const nb_attn_args* a) {
     s.tkv_pad = (a->Tkv + 7) / 8 * 8;
     const size_t bh = (size_t)a->B * a->H;
     s.qs = 0;
-    s.vt = up256(bh * s.tq_pad * HD * 2);
+    s.vt = 0;  // (Q is read from the caller's view: only V^T lives here)
     s.total = s.vt + up256(bh * HD * s.tkv_pad * 2);
     return s;
 }
@@ -482,9 +511,6 @@ static int launch_t(const nb_attn_args* a, cudaStream_t s) {
     pp.stride_qb = a->stride_qb; pp.stride_qh = a->stride_qh; pp.stride_qm = a->stride_qm;
     pp.stride_vb = a->stride_vb; pp.stride_vh = a->stride_vh; pp.stride_vn = a->stride_vn;
     const long long bh = (long long)a->B * a->H;
-    const long long q_units = bh * sc.tq_pad * (HD / 8);
-    attn_prepack_q_kernel<T><<<(unsigned)((q_units + 255) / 256), 256, 0, s>>>(pp);
-    NB_CUDA_CHECK(cudaGetLastError());
     attn_prepack_vt_kernel<T><<<dim3((a->Tkv + 63) / 64, HD / 64, (unsigned)bh), 256, 0, s>>>(pp);
     NB_CUDA_CHECK(cudaGetLastError());
 
@@ -492,12 +518,8 @@ static int launch_t(const nb_attn_args* a, cudaStream_t s) {
                                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUtensorMap tm_q, tm_k, tm_v;
     bool ok;
-    {
-        cuuint64_t dims[2] = {HD, (cuuint64_t)bh * sc.tq_pad};
-        cuuint64_t str[1] = {HD * 2};
-        cuuint32_t box[2] = {64, BM};
-        ok = make_map(&tm_q, t16, 2, pp.qs, dims, str, box);
-    }
+    int4 qperm;
+    ok = make_view_map(&tm_q, &qperm, t16, a->q, a->Tq, a->H, a->B, a->stride_qm, a->stride_qh, a->stride_qb, BM);
     {
         cuuint64_t dims[2] = {(cuuint64_t)sc.tkv_pad, (cuuint64_t)bh * HD};
         cuuint64_t str[1] = {(cuuint64_t)sc.tkv_pad * 2};
@@ -505,37 +527,18 @@ static int launch_t(const nb_attn_args* a, cudaStream_t s) {
         ok = ok && make_map(&tm_v, t16, 2, pp.vt, dims, str, box);
     }
     int4 kperm;
-    {
-        // K from the caller's strided (B, H, T, D) view: the outer dimensions sorted by stride, as the encoder wants them
-        struct Dim { cuuint64_t size, stride; int role; } d[3] = {{(cuuint64_t)a->Tkv, (cuuint64_t)a->stride_kn * 2, 0},
-                                                                   {(cuuint64_t)a->H, (cuuint64_t)a->stride_kh * 2, 1},
-                                                                   {(cuuint64_t)a->B, (cuuint64_t)a->stride_kb * 2, 2}};
-        std::stable_sort(d, d + 3, [](const Dim& x, const Dim& y) { return x.stride < y.stride; });
-        cuuint64_t dims[4] = {HD, d[0].size, d[1].size, d[2].size};
-        cuuint64_t str[3] = {d[0].stride, d[1].stride, d[2].stride};
-        cuuint32_t box[4] = {64, 1, 1, 1};
-        int pos[3];
-        for (int i = 0; i < 3; ++i) {
-            pos[d[i].role] = i + 1;
-            if (d[i].role == 0) box[i + 1] = BN;
-        }
-        kperm = make_int4(pos[0], pos[1], pos[2], 0);
-        // a dimension of size 1 may carry any stride; give it a valid one.  (A zero or unaligned stride on a larger
-        // dimension -- K expanded over heads or batch -- never gets here: attn_tc_unsupported_reason refuses it.)
-        for (int i = 0; i < 3; ++i)
-            if (dims[i + 1] == 1 && (str[i] == 0 || str[i] % 16)) str[i] = 16;
-        ok = ok && make_map(&tm_k, t16, 4, a->k, dims, str, box);
-    }
+    ok = ok && make_view_map(&tm_k, &kperm, t16, a->k, a->Tkv, a->H, a->B, a->stride_kn, a->stride_kh, a->stride_kb, BN);
     if (!ok) return NB_ERR_UNSUPPORTED;
 
     Params p = {};
     p.o = a->o; p.Tq = a->Tq; p.Tkv = a->Tkv; p.H = a->H;
     p.stride_ob = a->stride_ob; p.stride_om = a->stride_om;
     p.tq_pad = sc.tq_pad;
+    p.qscale = pp.qscale;
     p.status = static_cast<int*>(a->status);
     auto kern = attention_tc_kernel<T>;
     NB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    kern<<<dim3(sc.tq_pad / BM, a->H, a->B), NTHREADS, SMEM_BYTES, s>>>(tm_q, tm_k, tm_v, kperm, p);
+    kern<<<dim3(sc.tq_pad / BM, a->H, a->B), NTHREADS, SMEM_BYTES, s>>>(tm_q, tm_k, tm_v, kperm, qperm, p);
     NB_CUDA_CHECK(cudaGetLastError());
     return NB_OK;
 }
@@ -555,6 +558,11 @@ const char* attn_tc_unsupported_reason(const nb_attn_args* a) {
     for (int i = 0; i < 3; ++i)
         if (kn[i] > 1 && (ks[i] <= 0 || ks[i] % 8)) return "K stride (broadcast or unaligned view)";
     if (!aligned16(a->k)) return "K alignment";
+    const long long qs[3] = {a->stride_qm, a->stride_qh, a->stride_qb};
+    const int qn[3] = {a->Tq, a->H, a->B};
+    for (int i = 0; i < 3; ++i)
+        if (qn[i] > 1 && (qs[i] <= 0 || qs[i] % 8)) return "Q stride (broadcast or unaligned view)";
+    if (!aligned16(a->q)) return "Q alignment";
     return nullptr;
 }
 int64_t attn_tc_scratch_bytes(const nb_attn_args* a) { return (int64_t)atc::scratch_layout(a).total; }
