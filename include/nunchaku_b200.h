@@ -258,7 +258,8 @@ typedef struct nb_attn_args {
     int32_t impl;          /* NB_IMPL_AUTO: tcgen05 kernel for D = 128, else the mma.sync kernel; NB_IMPL_GENERIC: mma.sync */
 } nb_attn_args;
 int nb_attention(const nb_attn_args* args, void* stream);
-/* Scratch the call needs: the tcgen05 kernel keeps the pre-scaled Q and the transposed V there; 0 for the mma.sync kernel. */
+/* Scratch the call needs: 0 for both kernels at present (Q, K and V are read in place from the caller's views); callers still
+ * ask, so that a kernel that needs some can be added without touching them. */
 int64_t nb_attention_scratch_bytes(const nb_attn_args* args);
 
 /*

@@ -230,7 +230,7 @@ def main():
                 q, k, v = (qkv[:, :, j].permute(0, 2, 1, 3) for j in range(3))  # (B, H, T, D) strided views
                 sets.append(dict(q=q, k=k, v=v, o=torch.empty(B, Tn, H * D, dtype=T, device=dev)))
             ms, best = time_ms(lambda p: attention_fp16(p["q"], p["k"], p["v"], p["o"], D ** -0.5), sets, args.iters, args.warmup)
-            emit("attn_prepack kernels + attention_tc_kernel", f"B={B} H={H} T={Tn} D={D} bf16", ms, best, 4.0 * B * H * Tn * Tn * D, "TFLOP/s", "tensor",
+            emit("attention_tc_kernel", f"B={B} H={H} T={Tn} D={D} bf16", ms, best, 4.0 * B * H * Tn * Tn * D, "TFLOP/s", "tensor",
                  bf16, src)
 
 

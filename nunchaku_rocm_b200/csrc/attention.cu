@@ -8,7 +8,7 @@
 // fragments, the 16 x 64 score tile and the 16 x D output accumulator in registers.  K and V tiles of 64
 // keys are double-buffered in shared memory with cp.async, in 16-byte units XOR-swizzled by the row so that
 // ldmatrix reads are conflict-free.  The matrix products run on mma.sync.m16n8k16.  This kernel takes the calls the
-// tcgen05 kernel does not (head dimension 64, unaligned outputs, callers without scratch).
+// tcgen05 kernel does not (head dimension 64, unaligned outputs, views broadcast over heads or batch).
 #include "nb_common.cuh"
 
 namespace nb {
@@ -247,6 +247,7 @@ static bool attn_fits_tc(const nb_attn_args* a) {
     return a->impl != NB_IMPL_GENERIC && attn_common_ok(a) && attn_tc_unsupported_reason(a) == nullptr;
 }
 static bool attn_scratch_ok(const nb_attn_args* a) {
+    if (attn_tc_scratch_bytes(a) == 0) return true;  // (the kernel reads Q, K and V in place)
     return a->scratch && a->scratch_bytes >= attn_tc_scratch_bytes(a) && (reinterpret_cast<uintptr_t>(a->scratch) & 255) == 0;
 }
 }  // namespace nb
@@ -259,8 +260,7 @@ extern "C" int64_t nb_attention_scratch_bytes(const nb_attn_args* a) {
 extern "C" int nb_attention(const nb_attn_args* a, void* stream) {
     using namespace nb;
     NB_REQUIRE(a && a->q && a->k && a->v && a->o);
-    // tcgen05 kernel when the call fits it and brings its scratch; a caller that passes none (NB_IMPL_AUTO) gets the
-    // mma.sync kernel, which needs no scratch
+    // tcgen05 kernel when the call fits it (and brings the scratch it asks for: none at present)
     if (a->B > 0 && a->H > 0 && attn_fits_tc(a) && attn_scratch_ok(a))
         return launch_attention_tc(a, static_cast<cudaStream_t>(stream));
     if (a->impl == NB_IMPL_TCGEN05) return attn_fits_tc(a) ? NB_ERR_INVALID : NB_ERR_UNSUPPORTED;

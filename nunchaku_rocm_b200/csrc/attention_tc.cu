@@ -7,13 +7,11 @@
 // the result beyond fp32 rounding: the running maximum a row subtracts is only raised when the true maximum has grown by
 // more than 8 (probabilities stay below 2^8), which makes the rescaling of the output accumulator a rare event.
 //
-// Two launches:
-//  1. `attn_prepack_vt_kernel`: V transposed to (B H, 128, Tkv rounded up to 8) so that both MMAs read K-major operands;
-//     pad columns are zero.
-//  2. `attention_tc_kernel`: a CTA owns 128 query rows of one (batch, head) and walks the keys in tiles of 128.
-//       warp 0    TMA producer: the Q tile once and K tiles straight from the caller's strided tensors (4-D tensor maps;
-//                 rows past the end read as zeros), V^T tiles; K and V^T through two-stage rings (128-byte swizzle, no
-//                 multicast).  The softmax warps turn the Q tile into Q' = T(q * scale * log2 e) in place before the first MMA.
+// One launch, no scratch: a CTA owns 128 query rows of one (batch, head) and walks the keys in tiles of 128.
+//       warp 0    TMA producer: the Q tile once, K and V tiles through two-stage rings, all straight from the caller's
+//                 strided tensors (4-D tensor maps, 128-byte swizzle, no multicast; rows past the end read as zeros).
+//                 The softmax warps turn the Q tile into Q' = T(q * scale * log2 e) in place before the first MMA; V is
+//                 consumed as it lies (head dimension contiguous) as an MN-major B operand, K as a K-major one.
 //       warp 1    MMA issuer for the scores: S_j = Q' K_j^T (8 MMAs, N = 128) into one of two score slots, so the tensor
 //                 pipe works on the next scores while the CUDA cores do the softmax of the current tile.
 //       warp 10   MMA issuer for O += P_j V_j, with P read from tensor memory as the A operand.
@@ -58,6 +56,17 @@ __device__ __forceinline__ uint64_t desc_sw128(uint32_t smem_addr) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
     d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// The same 128-byte-swizzled tile read as an MN-major operand (the 64 values of a 128-byte row run along M / N, the rows
+// along K): 8-row groups 1024 bytes apart along K, the two 64-wide halves of the tile half a tile apart along N.
+__device__ __forceinline__ uint64_t desc_sw128_mn(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+    d |= (uint64_t)((TILE / 2) >> 4) << 16;
     d |= (uint64_t)(1024 >> 4) << 32;
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)2 << 61;
@@ -111,7 +120,7 @@ __device__ __forceinline__ float ex2(float x) {
 template <typename T>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                    const __grid_constant__ CUtensorMap tm_v, const int4 kperm, const int4 qperm, const Params p) {
+                    const __grid_constant__ CUtensorMap tm_v, const int4 kperm, const int4 qperm, const int4 vperm, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t s_base = smem_u32(smem);
@@ -177,8 +186,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 }
                 if (j >= 2 && !mbar_wait(bar(B_PV + s), par, abort_s, E_PROD | 2, 50)) { ok = false; break; }
                 mbar_expect_tx(bar(B_VF + s), TILE);
-                tma_load_2d(s_base + OFF_V + s * TILE, &tm_v, bar(B_VF + s), j * BN, bh * HD);
-                tma_load_2d(s_base + OFF_V + s * TILE + TILE / 2, &tm_v, bar(B_VF + s), j * BN + 64, bh * HD);
+                {
+                    // V as it lies in the caller's view: 128 keys x (two halves of) 64 head-dimension values
+                    int c[4];
+                    c[0] = 0;
+                    c[vperm.x] = j * BN; c[vperm.y] = head; c[vperm.z] = batch;
+                    tma_load_4d(s_base + OFF_V + s * TILE, &tm_v, bar(B_VF + s), 0, c[1], c[2], c[3]);
+                    tma_load_4d(s_base + OFF_V + s * TILE + TILE / 2, &tm_v, bar(B_VF + s), 64, c[1], c[2], c[3]);
+                }
             }
             if (!ok) {
                 // let copies already in flight land before the CTA goes away (bounded)
@@ -221,8 +236,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         // ================================ MMA issuer: P V ================================
         {
             const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-            const uint32_t idesc = umma_idesc(1u, fmt, fmt, 128);
-            const uint64_t dv0 = desc_sw128(s_base + OFF_V);
+            // V is the B operand with its N dimension (the head dimension) contiguous in shared memory: "MN-major"
+            const uint32_t idesc = umma_idesc(1u, fmt, fmt, 128) | (1u << 16);
+            const uint64_t dv0 = desc_sw128_mn(s_base + OFF_V);
             bool ok = true;
             for (int i = 0; i < NT && ok; ++i) {
                 const int b = i & 1;
@@ -234,11 +250,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     const uint64_t dv = dv0 + (uint64_t)(b * (TILE >> 4));
                     const uint32_t pa = tmem_base + TM_P + b * 64;
 #pragma unroll
-                    for (int kh = 0; kh < 2; ++kh)
-#pragma unroll
-                        for (int st = 0; st < 4; ++st)
-                            mma_f16_ts(tmem_base + TM_O, pa + (kh * 4 + st) * 8, dv + kh * 1024 + st * 2, idesc,
-                                       (i > 0 || kh || st) ? 1u : 0u);
+                    for (int ks = 0; ks < 8; ++ks)  // 16 keys per MMA: 16 rows of 128 bytes further on
+                        mma_f16_ts(tmem_base + TM_O, pa + ks * 8, dv + ks * (16 * 128 >> 4), idesc, (i > 0 || ks) ? 1u : 0u);
                     tc_commit(bar(B_PV + b));
                 }
             }
@@ -396,46 +409,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 }
 
 // ------------------------------------------------------------------------------------------------
-// pre-pass: Q' = T(q * scale * log2 e) with zero pad rows; V^T with zero pad columns
-// ------------------------------------------------------------------------------------------------
-struct PrepackParams {
-    const void* q; const void* v; void* qs; void* vt;
-    int B, H, Tq, Tkv, tq_pad, tkv_pad;
-    float qscale;
-    long long stride_qb, stride_qh, stride_qm, stride_vb, stride_vh, stride_vn;
-};
-
-// one block transposes 64 keys x 64 d of one (batch, head)
-template <typename T>
-__global__ void __launch_bounds__(256) attn_prepack_vt_kernel(const PrepackParams p) {
-    __shared__ uint16_t tile[64][64 + 2];
-    const int k0 = blockIdx.x * 64, d0 = blockIdx.y * 64, bh = blockIdx.z;
-    const uint16_t* v = reinterpret_cast<const uint16_t*>(p.v) + (long long)(bh / p.H) * p.stride_vb + (long long)(bh % p.H) * p.stride_vh;
-    for (int i = threadIdx.x; i < 64 * 8; i += 256) {
-        const int kr = i >> 3, u = i & 7;
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (k0 + kr < p.Tkv) raw = __ldg(reinterpret_cast<const uint4*>(v + (long long)(k0 + kr) * p.stride_vn + d0 + u * 8));
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            tile[kr][u * 8 + 2 * e] = (uint16_t)(w[e] & 0xFFFFu);
-            tile[kr][u * 8 + 2 * e + 1] = (uint16_t)(w[e] >> 16);
-        }
-    }
-    __syncthreads();
-    uint16_t* vt = reinterpret_cast<uint16_t*>(p.vt) + ((long long)bh * HD + d0) * p.tkv_pad;
-    for (int i = threadIdx.x; i < 64 * 8; i += 256) {
-        const int dr = i >> 3, u = i & 7;
-        if (k0 + u * 8 < p.tkv_pad) {
-            uint32_t w[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) w[e] = (uint32_t)tile[u * 8 + 2 * e][dr] | ((uint32_t)tile[u * 8 + 2 * e + 1][dr] << 16);
-            *reinterpret_cast<uint4*>(vt + (long long)dr * p.tkv_pad + k0 + u * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-    }
-}
-
-// ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -485,34 +458,10 @@ static bool make_view_map(CUtensorMap* m, int4* perm, CUtensorMapDataType t16, c
     return make_map(m, t16, 4, base, dims, str, box);
 }
 
-static inline size_t up256(size_t x) { return (x + 255) & ~size_t(255); }
-struct Scratch { size_t qs, vt, total; int tq_pad, tkv_pad; };
-static Scratch scratch_layout(const nb_attn_args* a) {
-    Scratch s;
-    s.tq_pad = (a->Tq + BM - 1) / BM * BM;
-    s.tkv_pad = (a->Tkv + 7) / 8 * 8;
-    const size_t bh = (size_t)a->B * a->H;
-    s.qs = 0;
-    s.vt = 0;  // (Q is read from the caller's view: only V^T lives here)
-    s.total = s.vt + up256(bh * HD * s.tkv_pad * 2);
-    return s;
-}
 
 template <typename T>
 static int launch_t(const nb_attn_args* a, cudaStream_t s) {
-    const Scratch sc = scratch_layout(a);
-    if (!a->scratch || a->scratch_bytes < (int64_t)sc.total || (reinterpret_cast<uintptr_t>(a->scratch) & 255))
-        return NB_ERR_INVALID;
-    uint8_t* base = static_cast<uint8_t*>(a->scratch);
-    PrepackParams pp;
-    pp.q = a->q; pp.v = a->v; pp.qs = base + sc.qs; pp.vt = base + sc.vt;
-    pp.B = a->B; pp.H = a->H; pp.Tq = a->Tq; pp.Tkv = a->Tkv; pp.tq_pad = sc.tq_pad; pp.tkv_pad = sc.tkv_pad;
-    pp.qscale = a->scale * 1.4426950408889634f;
-    pp.stride_qb = a->stride_qb; pp.stride_qh = a->stride_qh; pp.stride_qm = a->stride_qm;
-    pp.stride_vb = a->stride_vb; pp.stride_vh = a->stride_vh; pp.stride_vn = a->stride_vn;
-    const long long bh = (long long)a->B * a->H;
-    attn_prepack_vt_kernel<T><<<dim3((a->Tkv + 63) / 64, HD / 64, (unsigned)bh), 256, 0, s>>>(pp);
-    NB_CUDA_CHECK(cudaGetLastError());
+    const int tq_pad = (a->Tq + BM - 1) / BM * BM;  // (Q, K and V are read in place: the kernel needs no scratch)
 
     const CUtensorMapDataType t16 = std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -520,12 +469,8 @@ static int launch_t(const nb_attn_args* a, cudaStream_t s) {
     bool ok;
     int4 qperm;
     ok = make_view_map(&tm_q, &qperm, t16, a->q, a->Tq, a->H, a->B, a->stride_qm, a->stride_qh, a->stride_qb, BM);
-    {
-        cuuint64_t dims[2] = {(cuuint64_t)sc.tkv_pad, (cuuint64_t)bh * HD};
-        cuuint64_t str[1] = {(cuuint64_t)sc.tkv_pad * 2};
-        cuuint32_t box[2] = {64, HD};
-        ok = ok && make_map(&tm_v, t16, 2, pp.vt, dims, str, box);
-    }
+    int4 vperm;
+    ok = ok && make_view_map(&tm_v, &vperm, t16, a->v, a->Tkv, a->H, a->B, a->stride_vn, a->stride_vh, a->stride_vb, BN);
     int4 kperm;
     ok = ok && make_view_map(&tm_k, &kperm, t16, a->k, a->Tkv, a->H, a->B, a->stride_kn, a->stride_kh, a->stride_kb, BN);
     if (!ok) return NB_ERR_UNSUPPORTED;
@@ -533,12 +478,12 @@ static int launch_t(const nb_attn_args* a, cudaStream_t s) {
     Params p = {};
     p.o = a->o; p.Tq = a->Tq; p.Tkv = a->Tkv; p.H = a->H;
     p.stride_ob = a->stride_ob; p.stride_om = a->stride_om;
-    p.tq_pad = sc.tq_pad;
-    p.qscale = pp.qscale;
+    p.tq_pad = tq_pad;
+    p.qscale = a->scale * 1.4426950408889634f;
     p.status = static_cast<int*>(a->status);
     auto kern = attention_tc_kernel<T>;
     NB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    kern<<<dim3(sc.tq_pad / BM, a->H, a->B), NTHREADS, SMEM_BYTES, s>>>(tm_q, tm_k, tm_v, kperm, qperm, p);
+    kern<<<dim3(tq_pad / BM, a->H, a->B), NTHREADS, SMEM_BYTES, s>>>(tm_q, tm_k, tm_v, kperm, qperm, vperm, p);
     NB_CUDA_CHECK(cudaGetLastError());
     return NB_OK;
 }
@@ -563,9 +508,13 @@ const char* attn_tc_unsupported_reason(const nb_attn_args* a) {
     for (int i = 0; i < 3; ++i)
         if (qn[i] > 1 && (qs[i] <= 0 || qs[i] % 8)) return "Q stride (broadcast or unaligned view)";
     if (!aligned16(a->q)) return "Q alignment";
+    const long long vs[3] = {a->stride_vn, a->stride_vh, a->stride_vb};
+    for (int i = 0; i < 3; ++i)
+        if (kn[i] > 1 && (vs[i] <= 0 || vs[i] % 8)) return "V stride (broadcast or unaligned view)";
+    if (!aligned16(a->v)) return "V alignment";
     return nullptr;
 }
-int64_t attn_tc_scratch_bytes(const nb_attn_args* a) { return (int64_t)atc::scratch_layout(a).total; }
+int64_t attn_tc_scratch_bytes(const nb_attn_args* a) { (void)a; return 0; }
 int launch_attention_tc(const nb_attn_args* a, cudaStream_t s) {
     return a->dtype == NB_DTYPE_BF16 ? atc::launch_t<__nv_bfloat16>(a, s) : atc::launch_t<__half>(a, s);
 }
