@@ -22,6 +22,7 @@ struct EwParams {
     long long stride_xr, stride_yr, stride_y2r, stride_or;  // elements between rows
     long long stride_ab, stride_ad;                          // scale / shift / gate: elements between batches, between channels
     float scale_add, eps;
+    int vec_ab;  // scale / shift / gate are contiguous along the channels and 16-byte aligned: read them 8 at a time
 };
 
 template <typename T>
@@ -77,13 +78,22 @@ __global__ void __launch_bounds__(128) layernorm_modulate_kernel(const EwParams 
 #pragma unroll
     for (int u = 0; u < U; ++u) {
         const int c0 = (u * 128 + t) * 8;
-        float o[8];
+        float o[8], sv[8], hv[8];
+        if (p.vec_ab) {
+            widen<T>(__ldg(reinterpret_cast<const uint4*>(sc + c0)), sv);
+            widen<T>(__ldg(reinterpret_cast<const uint4*>(sh + c0)), hv);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                sv[j] = to_f32<T>(__ldg(sc + (long long)(c0 + j) * p.stride_ad));
+                hv[j] = to_f32<T>(__ldg(sh + (long long)(c0 + j) * p.stride_ad));
+            }
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             // layer_norm -> T, scale + scale_add -> T, product -> T, sum -> T
-            const float s = rnd<T>(to_f32<T>(__ldg(sc + (long long)(c0 + j) * p.stride_ad)) + p.scale_add);
-            const float h = to_f32<T>(__ldg(sh + (long long)(c0 + j) * p.stride_ad));
-            o[j] = rnd<T>(rnd<T>((v[u][j] - mean) * rstd) * s) + h;
+            const float s = rnd<T>(sv[j] + p.scale_add);
+            o[j] = rnd<T>(rnd<T>((v[u][j] - mean) * rstd) * s) + hv[j];
         }
         reinterpret_cast<uint4*>(out)[u * 128 + t] = narrow<T>(o);
     }
@@ -107,8 +117,15 @@ __global__ void __launch_bounds__(256) gated_residual_kernel(const EwParams p) {
             for (int j = 0; j < 8; ++j) yv[j] = rnd<T>(yv[j] + zv[j]);
         }
         const T* g = static_cast<const T*>(p.a) + (long long)bidx * p.stride_ab + (long long)u * 8 * p.stride_ad;
+        float gv[8];
+        if (p.vec_ab) {
+            widen<T>(__ldg(reinterpret_cast<const uint4*>(g)), gv);
+        } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rnd<T>(to_f32<T>(__ldg(g + (long long)j * p.stride_ad)) * yv[j]) + xv[j];
+            for (int j = 0; j < 8; ++j) gv[j] = to_f32<T>(__ldg(g + (long long)j * p.stride_ad));
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rnd<T>(gv[j] * yv[j]) + xv[j];
         reinterpret_cast<uint4*>(static_cast<T*>(p.out) + (long long)row * p.stride_or)[u] = narrow<T>(o);
     }
 }
@@ -145,6 +162,7 @@ extern "C" int nb_layernorm_modulate(const void* x, const void* scale, const voi
     p.rows = rows; p.rows_per_batch = rows_per_batch; p.dim = dim;
     p.stride_xr = stride_xr; p.stride_or = stride_or; p.stride_ab = stride_sb; p.stride_ad = stride_sd;
     p.scale_add = scale_add; p.eps = eps;
+    p.vec_ab = stride_sd == 1 && stride_sb % 8 == 0 && aligned16(scale) && aligned16(shift);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return dtype == NB_DTYPE_BF16 ? launch_ln<__nv_bfloat16>(p, s) : launch_ln<__half>(p, s);
 }
@@ -165,6 +183,7 @@ extern "C" int nb_gated_residual(const void* x, const void* gate, const void* y,
     p.rows = rows; p.rows_per_batch = rows_per_batch; p.dim = dim;
     p.stride_xr = stride_xr; p.stride_yr = stride_yr; p.stride_y2r = stride_y2r; p.stride_or = stride_or;
     p.stride_ab = stride_gb; p.stride_ad = stride_gd;
+    p.vec_ab = stride_gd == 1 && stride_gb % 8 == 0 && aligned16(gate);
     const long long units = (long long)rows * (dim / 8);
     int sms = 148;
     int dev = 0;

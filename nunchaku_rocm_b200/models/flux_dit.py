@@ -78,7 +78,8 @@ class _AdaLayerNormZero(nn.Module):
         """The ``(n, B, dim)`` modulation vectors: they depend on the time embedding only, so a model may compute every
         block's ahead of the blocks (:func:`modulations_ahead`)."""
         e = self.linear(F.silu(emb))
-        return e.view(e.shape[0], -1, self.n).permute(2, 0, 1)
+        # (n, B, dim), contiguous along dim: the element-wise kernels then read the vectors 16 bytes at a time
+        return e.view(e.shape[0], -1, self.n).permute(2, 0, 1).contiguous()
 
     def forward(self, x: torch.Tensor, emb: torch.Tensor, parts: torch.Tensor | None = None):
         if parts is None:
